@@ -1,0 +1,151 @@
+// Plain structs shared by the host runtime and the sm_100a kernels.
+//
+// Device collectives run as ONE kernel per rank.  The point-to-point
+// algorithms (ring, Rabenseifner) are expressed as a small per-rank program of
+// `Op`s that the host compiles once per (algorithm, length, world size) and a
+// generic kernel interprets; every op is a fused
+//   wait-for-peer -> load (+ add) (+ scale) (+ cast) -> store local / store to
+//   the peer's staging slot over NVLink -> post flag / return credit
+// step.  This replaces the reference's per-chunk host loop of
+// cudaMemcpyAsync + reduce kernel + cudaMemcpyAsync + ibv_post_send
+// (ibcomm/allreduce_cuda_impl.h:103-299, 470-707).
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#ifdef __CUDACC__
+#define IBCOMM_HD __host__ __device__
+#else
+#define IBCOMM_HD
+#endif
+
+namespace ibcomm {
+
+constexpr int kMaxRanks = 8;       // one NVSwitch box
+constexpr int kMaxChannels = 128;  // CTAs per rank a collective may use
+constexpr int kExecThreads = 512;  // threads per channel CTA
+
+// ---- control page at the start of every rank's arena (peer-writable) ----
+// All words are 64-bit, written by exactly one remote rank and polled locally.
+// Values only grow: (call sequence << 32) | count.
+struct ControlPage {
+  // bar[c][s]: rank s announces "my channel c reached barrier point v".
+  uint64_t bar[kMaxChannels][kMaxRanks];
+  // inflag[c][s]: number of transfers rank s has completed into my staging.
+  uint64_t inflag[kMaxChannels][kMaxRanks];
+  // credit[c][d]: number of my transfers rank d has consumed.
+  uint64_t credit[kMaxChannels][kMaxRanks];
+  // Point-to-point mailbox counters, one per source / destination rank.
+  uint64_t p2p_flag[kMaxRanks];
+  uint64_t p2p_credit[kMaxRanks];
+  // Set (to the call sequence) by any rank that gave up; polled by waiters.
+  uint64_t abort_seq;
+  uint64_t pad_[7];
+  // One-shot allreduce flags: [parity][cta][source].
+  uint64_t oneshot_flag[2][kMaxChannels][kMaxRanks];
+};
+
+// ---- error report written by a kernel whose bounded wait ran out ----
+enum DeviceStatusCode : uint32_t {
+  kStatusOk = 0,
+  kStatusWaitTimeout = 1,   // a flag did not arrive within the limit
+  kStatusPeerAbort = 2,     // a peer (or another CTA) reported failure
+  kStatusBadProgram = 3,    // self-check of an op failed (index out of range)
+};
+enum DeviceWaitKind : uint32_t { kWaitBarrier = 1, kWaitData = 2, kWaitCredit = 3, kWaitP2p = 4, kWaitOneShot = 5 };
+
+struct DeviceStatus {
+  uint32_t code;      // DeviceStatusCode; first failure wins
+  uint32_t kind;      // DeviceWaitKind
+  int32_t rank;
+  int32_t peer;
+  int32_t channel;
+  int32_t op_index;
+  uint64_t expected;
+  uint64_t seen;
+  uint64_t seq;
+};
+
+// ---- per-step trace record (optional) ----
+struct DeviceTraceRec {
+  uint64_t t_wait_done;  // %globaltimer when the op's waits were satisfied
+  uint64_t t_done;       // %globaltimer when the op's flags were posted
+};
+
+// ---- program ops ----
+enum OpSrc : uint8_t { kSrcNone = 0, kSrcSend = 1, kSrcRecv = 2, kSrcStage = 3 };
+enum OpFlags : uint8_t {
+  kOpScale = 1,        // multiply by ExecParams::scale before storing
+  kOpStoreLocal = 2,   // store to recvbuf[range]
+  kOpStoreRemote = 4,  // store to peer_out's staging slot
+};
+
+struct Op {
+  uint8_t src_a;     // OpSrc
+  uint8_t src_b;     // OpSrc (added to src_a); kSrcNone = plain copy
+  uint8_t flags;     // OpFlags
+  int8_t peer_in;    // rank whose transfer feeds kSrcStage, -1 if none
+  int8_t peer_out;   // rank that receives the remote store, -1 if none
+  uint8_t region_in;   // staging region index on my side (one per in-peer)
+  uint8_t region_out;  // staging region index on peer_out's side
+  uint8_t pad_;
+  uint32_t slot_in;    // staging slot index inside region_in
+  uint32_t slot_out;   // staging slot index inside region_out
+  uint32_t wait_in;      // wait until inflag[ch][peer_in] >= base + wait_in   (0 = no wait)
+  uint32_t wait_credit;  // wait until credit[ch][peer_out] >= base + wait_credit (0 = no wait)
+  uint32_t post_out;     // then peer_out.inflag[ch][me] = base + post_out     (0 = no post)
+  uint32_t post_credit;  // and  peer_in.credit[ch][me] = base + post_credit   (0 = no post)
+  uint64_t elem_begin;   // chunk range in elements of the message
+  uint64_t elem_count;
+};
+
+// Geometry of the staging area a program runs in.
+struct StageLayout {
+  uint64_t offset;       // byte offset of the area inside the arena
+  uint64_t slot_bytes;   // bytes of one slot (multiple of 128)
+  uint32_t slots;        // slots per region
+  uint32_t regions;      // number of regions (= distinct in-peers)
+};
+
+// Elements [*lo, *hi) of a `count`-element chunk that channel `c` of `nch`
+// handles.  Slices start on multiples of kSliceAlign elements so that a slice
+// is 16-byte aligned in every element type whenever its chunk is.
+constexpr uint32_t kSliceAlign = 64;
+IBCOMM_HD inline void ChannelSlice(uint64_t count, int nch, int c, uint64_t* lo, uint64_t* hi) {
+  uint64_t per = (count + static_cast<uint64_t>(nch) - 1) / static_cast<uint64_t>(nch);
+  per = (per + kSliceAlign - 1) / kSliceAlign * kSliceAlign;
+  uint64_t b = per * static_cast<uint64_t>(c);
+  if (b > count) b = count;
+  uint64_t e = b + per;
+  if (e > count) e = count;
+  *lo = b;
+  *hi = e;
+}
+
+struct PeerTable {
+  unsigned char* arena[kMaxRanks];  // every rank's arena as mapped here
+  unsigned char* mc_arena;          // multicast alias of the arenas, or null
+};
+
+struct ExecParams {
+  int32_t rank;
+  int32_t world_size;
+  int32_t dtype;       // DType of the user buffers
+  int32_t wire;        // DType on the wire / in staging
+  PeerTable peers;
+  const void* sendbuf;
+  void* recvbuf;
+  uint64_t len_elements;
+  double scale;
+  const Op* ops;
+  int32_t num_ops;
+  int32_t trace_capacity;  // records per channel, 0 = tracing off
+  StageLayout stage;
+  uint64_t seq;          // call sequence number (same on every rank)
+  uint64_t timeout_ns;   // limit of every wait
+  DeviceStatus* status;  // host-visible
+  DeviceTraceRec* trace; // [channel][trace_capacity]
+};
+
+}  // namespace ibcomm

@@ -1,0 +1,71 @@
+// Schedule compiler: turns (algorithm, rank, world size, chunk ranges) into the
+// per-rank op program the device executor interprets (see device_types.h).
+//
+// Ring (reference ibcomm/allreduce_cuda_impl.h:35-301): reduce-scatter then
+// all-gather around the ring r-1 -> r -> r+1, chunk-pipelined; after the
+// reduce-scatter rank r owns the reduced block of rank r+1, and inside a
+// block chunk ids descend.  The wire order is position-major (the i-th chunk
+// of every block travels before the (i+1)-th of any), which keeps the
+// schedule deadlock-free with as few as two staging slots.
+//
+// Rabenseifner (reference :326-717): recursive halving with the partner
+// rank ^ (1 << s), nearest first, the lower rank giving away the front part;
+// recursive doubling in mirror order; every rank-block moves as its pipeline
+// chunks.  World sizes that are not a power of two are folded first: ranks
+// below 2 * (ws - 2^k) pair up, swap halves and add, the even rank hands its
+// half over and sits out, and gets the result back at the end.
+#pragma once
+
+#include <string>
+#include <vector>
+
+#include "ibcomm/communicator.h"
+#include "ibcomm/device_types.h"
+
+namespace ibcomm {
+
+struct ProgramRequest {
+  Algo algo = Algo::kRing;
+  int rank = 0;
+  int world_size = 1;
+  std::vector<Range> ranges;      // pipeline chunks of the message, in elements
+  size_t wire_elem_bytes = 4;     // element size in staging
+  uint64_t stage_offset = 0;      // where the staging area starts in the arena
+  uint64_t stage_bytes = 0;       // how large it is
+  bool apply_scale = false;
+};
+
+struct Program {
+  std::vector<Op> ops;
+  StageLayout stage{};
+  std::vector<int> in_peers;  // region index -> source rank, for this rank
+  // Transfers per peer over the whole program, for tests and credit audits.
+  uint32_t sent_to[kMaxRanks] = {0};
+  uint32_t received_from[kMaxRanks] = {0};
+};
+
+// Ordered list of the ranks that store into `rank`'s staging area.  The index
+// in this list is the staging region the sender must address.
+std::vector<int> InPeers(Algo algo, int rank, int world_size);
+// Regions every rank reserves (the maximum of InPeers over ranks).
+int NumRegions(Algo algo, int world_size);
+
+// Largest chunk, in elements.
+size_t MaxChunkElems(const std::vector<Range>& ranges);
+// Staging geometry for a request; slots == 0 means the area is too small for
+// two slots per region and the caller has to cut smaller chunks.
+StageLayout PlanStage(const ProgramRequest& req);
+
+Program BuildProgram(const ProgramRequest& req);
+
+// Chunk cut used by the device paths: the reference's rules and exit codes
+// (SplitBuffer), but when IBCOMM_CHUNKSIZE is unset the chunk length is
+// rounded up to a multiple of 128 bytes so that every chunk starts on a
+// vector boundary, and chunks are cut again (each into the same number of
+// pieces, which keeps block boundaries) until one fits `max_chunk_bytes`.
+std::vector<Range> SplitForDevice(size_t len_elements, size_t elem_bytes, size_t world_size,
+                                  int64_t env_chunk_bytes, size_t max_chunk_bytes);
+
+std::string DescribeOp(const Op& op);
+
+}  // namespace ibcomm
