@@ -45,8 +45,9 @@ CUDA_SOURCES = [
     "src/cuda/driver_api.cpp",
     "src/cuda/fd_channel.cpp",
     "src/cuda/arena.cpp",
-    "src/cuda/device_context.cu",
-    "src/cuda/emu_world.cu",
+    "src/cuda/engine.cpp",
+    "src/cuda/device_context.cpp",
+    "src/cuda/emu_world.cpp",
     "src/cuda/exec_kernel.cu",
     "src/cuda/nvls_kernel.cu",
     "src/cuda/oneshot_kernel.cu",
@@ -68,7 +69,7 @@ PROGRAMS = [
 
 CXXFLAGS = ["-std=c++17", "-O2", "-g", "-fPIC", "-Wall", "-Wextra", "-pthread", f"-I{ROOT / 'include'}"]
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-NVCCFLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC,-Wall,-pthread", f"-I{ROOT / 'include'}",
+NVCCFLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC,-Wall,-pthread", f"-I{ROOT / 'include'}", f"-I{ROOT / 'src' / 'cuda'}",
              "-DUSE_CUDA", "--expt-relaxed-constexpr", "-Xptxas", "-v"] + NVCC_ARCH
 
 
@@ -116,7 +117,7 @@ def _compile(src: str, variant: str, hdr_mtime: float) -> Path:
         _run([_nvcc(), *NVCCFLAGS, "-c", s, "-o", obj], log=obj.with_suffix(".ptxas.log"))
     else:
         cuda_inc = Path(_nvcc()).resolve().parent.parent / "include"
-        _run(["g++", *CXXFLAGS, "-DUSE_CUDA", f"-I{cuda_inc}", "-c", s, "-o", obj])
+        _run(["g++", *CXXFLAGS, "-DUSE_CUDA", f"-I{cuda_inc}", f"-I{ROOT / 'src' / 'cuda'}", "-c", s, "-o", obj])
     return obj
 
 

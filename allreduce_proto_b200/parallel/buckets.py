@@ -1,0 +1,95 @@
+"""Gradient bucketing for data-parallel training (the use case the reference
+names in its README.md:3-9 but leaves to the framework on top).
+
+Gradients are packed into flat buckets of about ``bucket_bytes`` (25 MiB by
+default) in parameter order; ``param.grad`` becomes a view into its bucket, so
+nothing is copied before or after the allreduce, which runs in place with the
+``1 / world_size`` scale fused into the reduction kernel.  Buckets are taken
+from the communicator's symmetric memory when possible, which lets the switch
+reduce them without staging."""
+from __future__ import annotations
+
+from typing import Iterable, Optional, Sequence
+
+import torch
+
+from .communicator import Communicator
+
+
+def plan_buckets(numels: Sequence[int], elem_bytes: int, bucket_bytes: int) -> list[list[int]]:
+    """Groups tensor indices into consecutive buckets of at most ``bucket_bytes``
+    (a tensor larger than that gets a bucket of its own)."""
+    buckets: list[list[int]] = []
+    cur: list[int] = []
+    cur_bytes = 0
+    for i, n in enumerate(numels):
+        b = n * elem_bytes
+        if cur and cur_bytes + b > bucket_bytes:
+            buckets.append(cur)
+            cur, cur_bytes = [], 0
+        cur.append(i)
+        cur_bytes += b
+    if cur:
+        buckets.append(cur)
+    return buckets
+
+
+class GradientBuckets:
+    """Flat gradient storage + bucketed allreduce.
+
+    ``shapes``: one shape per gradient tensor.  ``comm`` may be ``None`` (or of
+    world size 1) for single-process use; then :meth:`allreduce` only scales."""
+
+    def __init__(self, shapes: Sequence[Sequence[int]], *, dtype=torch.float32, device="cuda",
+                 comm: Optional[Communicator] = None, bucket_bytes: int = 25 << 20, symmetric: bool = True):
+        self.comm = comm
+        self.dtype = dtype
+        self.shapes = [tuple(s) for s in shapes]
+        numels = [int(torch.Size(s).numel()) for s in self.shapes]
+        esize = torch.empty((), dtype=dtype).element_size()
+        # Every tensor starts on a 16-byte boundary inside its bucket.
+        align = max(1, 16 // esize)
+        self.plan = plan_buckets(numels, esize, bucket_bytes)
+        self.flat: list[torch.Tensor] = []
+        self.views: list[torch.Tensor] = [None] * len(self.shapes)  # type: ignore[list-item]
+        for idxs in self.plan:
+            offs, total = [], 0
+            for i in idxs:
+                offs.append(total)
+                total += (numels[i] + align - 1) // align * align
+            if comm is not None and comm.world_size > 1 and symmetric:
+                buf = comm.symmetric_empty(total, dtype)
+            else:
+                buf = torch.empty(total, dtype=dtype, device=device)
+            buf.zero_()
+            self.flat.append(buf)
+            for i, o in zip(idxs, offs):
+                self.views[i] = buf[o:o + numels[i]].view(self.shapes[i])
+
+    @property
+    def num_buckets(self) -> int:
+        return len(self.flat)
+
+    @property
+    def nbytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self.flat)
+
+    def attach(self, params: Iterable[torch.nn.Parameter]) -> None:
+        """Makes every ``param.grad`` a view into the buckets."""
+        for p, v in zip(params, self.views):
+            p.grad = v
+
+    def load(self, grads: Sequence[torch.Tensor]) -> None:
+        """Copies gradients in (for callers that do not use :meth:`attach`)."""
+        torch._foreach_copy_(list(self.views), list(grads))
+
+    def allreduce(self, *, average: bool = True, wire=None, algo: str = "auto", sync: bool = False) -> None:
+        """In-place sum (or mean) of every bucket over the ranks, on the current stream."""
+        ws = 1 if self.comm is None else self.comm.world_size
+        scale = 1.0 / ws if average else 1.0
+        if self.comm is None:
+            if scale != 1.0:
+                torch._foreach_mul_(self.flat, scale)
+            return
+        for buf in self.flat:
+            self.comm.allreduce(buf, algo=algo, scale=scale, wire=wire if buf.dtype == torch.float32 else None, sync=sync)

@@ -1,0 +1,63 @@
+"""Several ranks on one GPU (``ibcomm::EmuWorld``): every collective is one
+cooperative kernel launch that covers all ranks, so the real kernels, programs
+and flag protocol can be exercised on a single-GPU machine."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from .. import _native
+from .._native import ALGO_CODES, check
+from .communicator import _ptr, dtype_code
+
+
+class EmuWorld:
+    def __init__(self, num_ranks: int, pool_bytes: int = 0, work_bytes: int = 0):
+        self._h = C.c_void_p()
+        check(_native.lib().ibcomm_emu_create(num_ranks, pool_bytes, work_bytes, C.byref(self._h)))
+        self.num_ranks = num_ranks
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h:
+            _native.lib().ibcomm_emu_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def allreduce(self, sendbufs: Sequence[torch.Tensor], recvbufs: Optional[Sequence[torch.Tensor]] = None, *,
+                  algo: str = "ring", scale: float = 1.0, wire=None, channels: int = 0,
+                  stream: Optional[torch.cuda.Stream] = None, sync: bool = True):
+        """``recvbufs[r]`` = scale * sum over r of ``sendbufs[r]`` for every emulated rank."""
+        if recvbufs is None:
+            recvbufs = sendbufs
+        n = sendbufs[0].numel()
+        d = dtype_code(sendbufs[0].dtype)
+        w = dtype_code(wire) if wire is not None else d
+        ins = (C.c_void_p * self.num_ranks)(*[_ptr(t) for t in sendbufs])
+        outs = (C.c_void_p * self.num_ranks)(*[_ptr(t) for t in recvbufs])
+        s = stream if stream is not None else torch.cuda.current_stream()
+        check(_native.lib().ibcomm_emu_allreduce(self._h, ALGO_CODES[algo], d, ins, outs, n, float(scale), w, channels,
+                                                 C.c_void_p(s.cuda_stream), 0 if sync else 1))
+        return recvbufs
+
+    def set_timeout_ms(self, ms: int) -> None:
+        check(_native.lib().ibcomm_emu_set_timeout_ms(self._h, ms))
+
+    def set_silent_rank(self, rank: int) -> None:
+        """Test hook: ``rank`` skips the following collectives (-1: nobody does)."""
+        check(_native.lib().ibcomm_emu_set_silent_rank(self._h, rank))
+
+    @property
+    def last_channels(self) -> int:
+        return _native.lib().ibcomm_emu_last_channels(self._h)
+
+    def last_status(self) -> dict:
+        rep = _native.StatusReport()
+        check(_native.lib().ibcomm_emu_last_status(self._h, C.byref(rep)))
+        return {f: getattr(rep, f) for f, _ in rep._fields_}

@@ -1,0 +1,7 @@
+"""Host utilities: size strings, the buffer partitioner, bandwidth arithmetic."""
+from .sizes import parse_number, get_exp_of_two, format_bytes
+from .partition import split_buffer, rank_to_chunk, describe_program
+from .bandwidth import algbw_gbs, busbw_gbs, ring_bytes_per_gpu, nvls_bytes_per_gpu
+
+__all__ = ["parse_number", "get_exp_of_two", "format_bytes", "split_buffer", "rank_to_chunk", "describe_program",
+           "algbw_gbs", "busbw_gbs", "ring_bytes_per_gpu", "nvls_bytes_per_gpu"]

@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Headline benchmark: fp32 allreduce of one 256 MiB buffer per rank.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+One step = one out-of-place allreduce (sum, result scaled by 1/N, fused) of
+67,108,864 fp32 elements per rank through the library's own kernels; the
+reference's example program times exactly this operation
+(examples/allreduce.cpp:21,107-118; README.md:41-51 publishes 97.5 ms on 8
+nodes = 4.818 GB/s bus bandwidth).  Rank 0 prints ONE JSON line:
+
+  value        bus bandwidth in GB/s = bytes / time * 2 (N-1) / N   (for N = 1,
+               where that factor is zero, the algorithm bandwidth bytes / time of
+               the fused copy+scale kernel the library runs at world size 1)
+  ms_per_step  device time of one step (CUDA events around the K steps,
+               barrier + synchronize on both sides, max over ranks)
+  e2e          the same metric with, inside every timed step, the host->device
+               copy of the 256 MiB input from pinned memory and a device->host
+               read of 4 KiB of the result, through the public Communicator API
+  per_algo     device-timed bus bandwidth of every algorithm the box supports
+               and of NCCL (torch.distributed.all_reduce) on the same buffers
+  clocks       SM clock and throttle reasons sampled with nvidia-smi during the
+               timed region
+
+`--impl reference` reports why the reference cannot run on this box.
+`--sweep` runs the 4 KiB - 1 GiB message-size sweep per algorithm and writes
+JSON lines to --out (default gpurun_out/sweep_<N>gpu.jsonl).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REFERENCE_BUSBW_GBS = 4.818  # 268435456 B / 0.0975075 s * 2 * 7 / 8, reference README.md:50
+ELEMENTS = 67_108_864        # 256 MiB of fp32 (reference examples/allreduce.cpp:21)
+UNAVAILABLE = ("reference is a C++/CMake library without Python packaging; its build needs libibverbs headers, "
+               "an InfiniBand port with a LID, an MPI compiler wrapper and two empty submodules, none present here")
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--elements", type=int, default=ELEMENTS)
+    ap.add_argument("--algo", default="auto")
+    ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--sweep-max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--out", default=None)
+    ap.add_argument("--no-extras", action="store_true", help="skip per-algorithm and NCCL measurements")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples `nvidia-smi` clocks and throttle reasons every 200 ms while running."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.lines: list[str] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.device_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main() -> int:
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    import allreduce_proto_b200 as ar
+    from allreduce_proto_b200.utils import busbw_gbs
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    if args.gpus > 1 and world == 1:
+        sys.stderr.write("bench.py: --gpus N > 1 must be launched with torch.distributed.run\n")
+        return 2
+    if not torch.cuda.is_available():
+        sys.stderr.write("bench.py needs a CUDA device\n")
+        return 2
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        comm = ar.Communicator.from_torch_distributed()
+    else:
+        comm = ar.Communicator(1, 0)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def time_steps(fn, steps: int, warmup: int) -> float:
+        """ms per step: events around `steps` calls, barrier + sync on both sides, max over ranks."""
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    if args.sweep:
+        return sweep(args, comm, world, rank, dev, time_steps, barrier)
+
+    n = args.elements
+    nbytes = n * 4
+    scale = 1.0 / world
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(rank)
+    # Buffers in the communicator's symmetric memory (zero-copy for the switch
+    # path) when there are peers; plain device memory otherwise.
+    if world > 1:
+        sendbuf = comm.symmetric_empty(n, torch.float32)
+        recvbuf = comm.symmetric_empty(n, torch.float32)
+    else:
+        sendbuf = torch.empty(n, dtype=torch.float32, device=dev)
+        recvbuf = torch.empty(n, dtype=torch.float32, device=dev)
+    sendbuf.copy_(torch.rand(n, dtype=torch.float32, device=dev, generator=gen) * 2 - 1)
+
+    def step():
+        comm.allreduce(sendbuf, recvbuf, algo=args.algo, scale=scale)
+
+    # Correctness of the configuration being timed (fp64 sum of the seeded inputs).
+    step()
+    torch.cuda.synchronize()
+    comm.check()
+    check_n = min(n, 1 << 20)
+    want = torch.zeros(check_n, dtype=torch.float64, device=dev)
+    for r in range(world):
+        g = torch.Generator(device=dev)
+        g.manual_seed(r)
+        want += (torch.rand(n, dtype=torch.float32, device=dev, generator=g)[:check_n] * 2 - 1).double()
+    want *= scale
+    max_err = float((recvbuf[:check_n].double() - want).abs().max().item())
+    ok = max_err <= 1e-5 * world
+
+    launches_before = comm.device_info()["kernel_launches"]
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = time_steps(step, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else {}
+    info = comm.device_info()
+    # kernel launches inside the timed region only (warm-up excluded)
+    launches = (info["kernel_launches"] - launches_before) * args.steps // (args.steps + args.warmup)
+    comm.check()
+    value = busbw_gbs(nbytes, ms / 1e3, world)
+
+    # End to end: pinned host input -> device, allreduce, 4 KiB of the result back.
+    host_in = torch.empty(n, dtype=torch.float32, pin_memory=True)
+    host_in.copy_(sendbuf)
+    host_out = torch.empty(1024, dtype=torch.float32, pin_memory=True)
+
+    def e2e_step():
+        sendbuf.copy_(host_in, non_blocking=True)
+        comm.allreduce(sendbuf, recvbuf, algo=args.algo, scale=scale)
+        host_out.copy_(recvbuf[:1024], non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = time_steps(e2e_step, e2e_steps, 3)
+    e2e = {"value": busbw_gbs(nbytes, e2e_ms / 1e3, world), "unit": "GB/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": 4096, "steps": e2e_steps}
+
+    per_algo = {}
+    if not args.no_extras:
+        plain_in = torch.empty(n, dtype=torch.float32, device=dev)
+        plain_in.copy_(sendbuf)
+        plain_out = torch.empty_like(plain_in)
+        k, w = max(3, args.steps // 2), 3
+        if world > 1:
+            candidates = [("ring", plain_in, plain_out), ("rabenseifner", plain_in, plain_out)]
+            if info["nvls"]:
+                candidates += [("nvls", plain_in, plain_out)]          # staged through the pool
+                candidates += [("nvls_zero_copy", sendbuf, recvbuf)]   # symmetric buffers
+            for name, a, b in candidates:
+                algo = name.split("_")[0]
+                t = time_steps(lambda: comm.allreduce(a, b, algo=algo, scale=scale), k, w)
+                per_algo[name] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world),
+                                  "channels": comm.device_info()["last_channels"]}
+            t = time_steps(lambda: comm.allreduce(plain_in, plain_out, algo="ring", scale=scale, wire=torch.bfloat16), k, w)
+            per_algo["ring_bf16_wire"] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world)}
+            nccl_buf = plain_in.clone()
+            t = time_steps(lambda: dist.all_reduce(nccl_buf), k, w)
+            per_algo["nccl"] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world)}
+        else:
+            # One GPU: the same kernels with 8 emulated ranks in one cooperative
+            # launch (32 MiB per rank; local memory only, so this is a kernel
+            # check, not an NVLink number).
+            emu = ar.EmuWorld(8)
+            m = 8 << 20
+            ins = [torch.rand(m, device=dev) for _ in range(8)]
+            outs = [torch.empty(m, device=dev) for _ in range(8)]
+            for algo in ("ring", "rabenseifner"):
+                t = time_steps(lambda: emu.allreduce(ins, outs, algo=algo, scale=0.125, sync=False), k, w)
+                per_algo[f"emulated8_{algo}_32MiB"] = {"ms": t, "channels": emu.last_channels}
+            t = time_steps(lambda: torch.mul(sendbuf, scale, out=recvbuf), k, w)
+            per_algo["torch_mul_out"] = {"ms": t, "algbw_gbs": nbytes / (t / 1e3) / 1e9}
+            comm.check()
+
+    if rank == 0:
+        line = {
+            "metric": "allreduce_busbw_fp32_256MiB", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": value / REFERENCE_BUSBW_GBS, "dtype": "fp32", "data": "synthetic (uniform[-1,1), seeded by rank)",
+            "config": {"model": "AllreduceCuda<float> 67,108,864 elements (256 MiB) per rank, out of place, sum * 1/N fused",
+                       "global_batch": world, "seq_len": n, "parallelism": f"dp{world}",
+                       "algorithm": info["last_algo"] if world > 1 else "copy+scale kernel (world size 1)",
+                       "nvls": info["nvls"], "l2": "inputs (256 MiB) larger than L2 (126 MB)", "elements": n,
+                       "bus_factor": "2(N-1)/N, 1 for N=1"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "correct": ok, "max_abs_err": max_err,
+            "per_algo": per_algo, "impl": "ours",
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
+    return 0 if ok else 1
+
+
+def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
+    """Message-size sweep 4 KiB .. 1 GiB (powers of two), fp32, every algorithm and NCCL."""
+    import torch
+    import torch.distributed as dist
+
+    from allreduce_proto_b200.utils import busbw_gbs
+
+    out_path = args.out or f"gpurun_out/sweep_{world}gpu.jsonl"
+    info = comm.device_info(connect=world > 1)
+    rows = []
+    max_bytes = args.sweep_max_bytes
+    nmax = max_bytes // 4
+    if world > 1:
+        sym_in = comm.symmetric_empty(nmax, torch.float32)
+        sym_out = comm.symmetric_empty(nmax, torch.float32)
+    else:
+        sym_in = torch.empty(nmax, dtype=torch.float32, device=dev)
+        sym_out = torch.empty(nmax, dtype=torch.float32, device=dev)
+    plain_in = torch.empty(nmax, dtype=torch.float32, device=dev)
+    plain_out = torch.empty(nmax, dtype=torch.float32, device=dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(rank)
+    plain_in.copy_(torch.rand(nmax, dtype=torch.float32, device=dev, generator=g) * 2 - 1)
+    sym_in.copy_(plain_in)
+    nccl_buf = torch.empty(nmax, dtype=torch.float32, device=dev)
+    size = 4096
+    while size <= max_bytes:
+        n = size // 4
+        steps = 200 if size <= (1 << 20) else (50 if size <= (64 << 20) else 10)
+        warm = 20 if size <= (1 << 20) else 5
+        algos = []
+        if world > 1:
+            if size <= (256 << 10):
+                algos.append(("oneshot", plain_in, plain_out))
+            algos += [("ring", plain_in, plain_out), ("rabenseifner", plain_in, plain_out)]
+            if info["nvls"]:
+                algos += [("nvls", plain_in, plain_out), ("nvls_zero_copy", sym_in, sym_out)]
+            algos.append(("auto", sym_in, sym_out))
+        else:
+            algos.append(("auto", plain_in, plain_out))
+        for name, a, b in algos:
+            algo = name.split("_")[0]
+            try:
+                t = time_steps(lambda: comm.allreduce(a[:n], b[:n], algo=algo, scale=1.0 / world), steps, warm)
+                comm.check()
+            except Exception as e:  # an algorithm may be unavailable for a size
+                rows.append({"bytes": size, "algo": name, "error": str(e)})
+                continue
+            rows.append({"bytes": size, "algo": name, "us": t * 1e3, "busbw_gbs": busbw_gbs(size, t / 1e3, world),
+                         "algbw_gbs": size / (t / 1e3) / 1e9, "chosen": comm.device_info()["last_algo"],
+                         "channels": comm.device_info()["last_channels"], "n_gpus": world})
+        if world > 1:
+            t = time_steps(lambda: dist.all_reduce(nccl_buf[:n]), steps, warm)
+            rows.append({"bytes": size, "algo": "nccl", "us": t * 1e3, "busbw_gbs": busbw_gbs(size, t / 1e3, world),
+                         "algbw_gbs": size / (t / 1e3) / 1e9, "n_gpus": world})
+        size *= 2
+    if rank == 0:
+        os.makedirs(os.path.dirname(out_path) or ".", exist_ok=True)
+        with open(out_path, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+        print(json.dumps({"sweep": out_path, "rows": len(rows), "n_gpus": world, "nvls": info["nvls"]}))
+    if world > 1:
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,115 @@
+/* C interface of the library (for ctypes / FFI users; the PyTorch binding in
+ * allreduce_proto_b200/ is built on it).  Every function returns 0 on success
+ * or one of the library's error codes (1 invalid argument, 2 transport,
+ * 3 CUDA, 4 not supported); ibcomm_last_error() then describes the failure.
+ * Calling any function of this interface switches the library from
+ * "exit on error" (the C++ default, like the reference) to "report".
+ * The reference ships no binding (its README.md:62). */
+#pragma once
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ibcomm_comm ibcomm_comm;
+typedef struct ibcomm_emu ibcomm_emu;
+
+/* dtype: 0 float32, 1 float64, 2 int32, 3 int64, 4 float16, 5 bfloat16
+ * algo : 0 auto, 1 ring, 2 rabenseifner, 3 nvls, 4 oneshot */
+
+const char* ibcomm_last_error(void);
+int ibcomm_has_cuda(void);
+
+int ibcomm_create(int world_size, ibcomm_comm** out);
+int ibcomm_destroy(ibcomm_comm* c);
+int ibcomm_create_queue_pair(ibcomm_comm* c, int dest_rank, uint32_t info_out[3]);
+int ibcomm_register_queue_pair(ibcomm_comm* c, int dest_rank, const uint32_t info[3]);
+int ibcomm_register_process(ibcomm_comm* c, int dest_rank, const uint32_t info[3], uint32_t info_out[3]);
+int ibcomm_register_myself(ibcomm_comm* c, int my_rank);
+int ibcomm_set_timeout_ms(ibcomm_comm* c, int ms);
+
+int ibcomm_send(ibcomm_comm* c, int dest_rank, const void* buf, size_t len, int blocking);
+int ibcomm_recv(ibcomm_comm* c, int src_rank, void* buf, size_t len, int blocking);
+int ibcomm_send_poll(ibcomm_comm* c, int dest_rank, int* done);
+int ibcomm_recv_poll(ibcomm_comm* c, int src_rank, int* done);
+int ibcomm_send_wait(ibcomm_comm* c, int dest_rank);
+int ibcomm_recv_wait(ibcomm_comm* c, int src_rank);
+int ibcomm_bcast(ibcomm_comm* c, void* buf, size_t len, int root);
+int ibcomm_barrier(ibcomm_comm* c);
+
+/* Host buffers: algo 1 (ring) or 2 (rabenseifner). */
+int ibcomm_allreduce_host(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t len_elements);
+/* Device buffers.  stream = 0 uses the communicator's stream.  With async = 0
+ * the call returns when the result is in recvbuf; with async = 1 it only
+ * enqueues, and ibcomm_check() reports a failure after the caller synchronised. */
+int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t len_elements,
+                          double scale, int wire_dtype, void* stream, int async);
+int ibcomm_check(ibcomm_comm* c);
+
+/* Peer-mapped (and, with NVSwitch multicast, switch-reducible) device memory.
+ * Collective: every rank calls with the same size in the same order. */
+int ibcomm_symmetric_alloc(ibcomm_comm* c, size_t bytes, void** out);
+int ibcomm_symmetric_free(ibcomm_comm* c, void* ptr);
+
+typedef struct {
+  int device;
+  int nvls;
+  int share_mode;
+  int last_algo;
+  int last_channels;
+  int pad_;
+  uint64_t arena_bytes;
+  uint64_t pool_bytes;
+  uint64_t work_bytes;
+  uint64_t calls;
+  uint64_t kernel_launches;
+} ibcomm_device_info;
+/* Connects the device path if necessary (collective on first use). */
+int ibcomm_get_device_info(ibcomm_comm* c, int connect, ibcomm_device_info* out);
+
+int ibcomm_set_timer_base(ibcomm_comm* c);
+int ibcomm_dump_trace(ibcomm_comm* c);
+
+/* Several ranks emulated on one GPU (single cooperative launch per collective). */
+int ibcomm_emu_create(int num_ranks, size_t pool_bytes, size_t work_bytes, ibcomm_emu** out);
+int ibcomm_emu_destroy(ibcomm_emu* w);
+int ibcomm_emu_allreduce(ibcomm_emu* w, int algo, int dtype, const void* const* sendbufs, void* const* recvbufs,
+                         size_t len_elements, double scale, int wire_dtype, int channels, void* stream, int async);
+int ibcomm_emu_set_timeout_ms(ibcomm_emu* w, int ms);
+int ibcomm_emu_last_channels(ibcomm_emu* w);
+/* Test hook: rank `rank` does not take part in the following collectives
+ * (-1 = everybody takes part), so its peers' bounded waits run out. */
+int ibcomm_emu_set_silent_rank(ibcomm_emu* w, int rank);
+typedef struct {
+  uint32_t code;
+  uint32_t kind;
+  int32_t rank;
+  int32_t peer;
+  int32_t channel;
+  int32_t op_index;
+  uint64_t expected;
+  uint64_t seen;
+  uint64_t seq;
+} ibcomm_status_report;
+int ibcomm_emu_last_status(ibcomm_emu* w, ibcomm_status_report* out);
+
+/* out[i] = cast(in[i] * scale) on the current device. */
+int ibcomm_copy_scale(const void* in, void* out, size_t len_elements, int dtype_in, int dtype_out, double scale, void* stream);
+
+/* Utilities. */
+int ibcomm_parse_number(const char* text, int64_t* out);
+int ibcomm_get_exp_of_two(uint64_t n);
+/* Writes up to `capacity` [begin, end) pairs; returns the count in *count. */
+int ibcomm_split_buffer(size_t len_elements, size_t elem_bytes, size_t world_size, int64_t chunk_bytes, uint64_t* pairs,
+                        size_t capacity, size_t* count);
+int ibcomm_rank_to_chunk(size_t num_chunks, size_t world_size, int rank, int* chunks, size_t capacity, size_t* count);
+/* Human-readable op program of one rank (for tests and debugging). */
+int ibcomm_describe_program(int algo, int rank, int world_size, size_t len_elements, size_t elem_bytes, int64_t chunk_bytes,
+                            size_t stage_bytes, char* text, size_t capacity);
+
+#ifdef __cplusplus
+}
+#endif

@@ -54,6 +54,9 @@ void SumBytes(void* dst, const void* src, size_t bytes) {
 }
 
 class DeviceContext;  // device arena, peer mappings, kernels (src/cuda)
+struct DeviceContextDeleter {
+  void operator()(DeviceContext* d) const;
+};
 
 // Options of the device allreduce beyond the reference's plain sum.
 struct CudaAllreduceOptions {
@@ -192,7 +195,7 @@ class Communicator {
   bool in_collective_ = false;
   Tracer tracer_;
 #ifdef USE_CUDA
-  std::unique_ptr<DeviceContext> device_;
+  std::unique_ptr<DeviceContext, DeviceContextDeleter> device_;
   friend class DeviceContext;
 #endif
 

@@ -1,0 +1,80 @@
+// Device side of a communicator: the peer-mapped arena (staging pool, work
+// region, mailboxes, control page), the peer and multicast mappings, the
+// program cache and the kernel launches.  Counterpart of the reference's
+// memory pool + work buffer (ibcomm/ibverbs_communicator_cuda.cpp:11-37,
+// ibcomm/memory_pool.h) — but resident on the device and mapped by the peers
+// instead of pinned on the host and registered with an adapter.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include "ibcomm/communicator.h"
+#include "ibcomm/device_types.h"
+
+namespace ibcomm {
+
+// Byte layout of one rank's arena.  Every rank uses the same layout.
+struct ArenaLayout {
+  uint64_t control_offset = 0;   // ControlPage
+  uint64_t oneshot_offset = 0;   // [2 parities][kMaxRanks] slots of oneshot_slot_bytes
+  uint64_t oneshot_slot_bytes = 0;
+  uint64_t mailbox_offset = 0;   // [kMaxRanks sources][mailbox_slots] of mailbox_slot_bytes
+  uint64_t mailbox_slot_bytes = 0;
+  uint32_t mailbox_slots = 0;
+  uint64_t pool_offset = 0;      // IBCOMM_MEMORY_POOL_PRE_ALLOC bytes
+  uint64_t pool_bytes = 0;
+  uint64_t work_offset = 0;      // IBCOMM_WORK_GPU_MEMORY_SIZE bytes
+  uint64_t work_bytes = 0;
+  uint64_t total_bytes = 0;
+};
+ArenaLayout MakeArenaLayout(size_t pool_bytes, size_t work_bytes);
+
+// Algorithm and channel choice for a message (src/host/tuner.cpp).
+struct TunerChoice {
+  Algo algo;
+  int channels;
+};
+TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, bool zero_copy, int max_channels);
+// Channels for a forced algorithm.
+int ChooseChannels(Algo algo, size_t bytes, int world_size, int max_channels);
+
+// Functions the host half of the communicator calls (defined in src/cuda).
+bool DeviceContextIsDevicePointer(const void* p);
+void DeviceContextSend(DeviceContext* d, int dest, const void* buf, size_t len);
+void DeviceContextRecv(DeviceContext* d, int src, void* buf, size_t len);
+bool DeviceContextSendPoll(DeviceContext* d, int dest);
+bool DeviceContextRecvPoll(DeviceContext* d, int src);
+void DeviceContextSendWait(DeviceContext* d, int dest);
+void DeviceContextRecvWait(DeviceContext* d, int src);
+void DeviceContextCollectTrace(DeviceContext* d, Tracer* tracer);
+
+// Introspection for bindings and tests.
+struct DeviceInfo {
+  int device;
+  int nvls;            // multicast alias of the arena is mapped
+  int share_mode;      // 0 = virtual-memory descriptors, 1 = CUDA IPC
+  uint64_t arena_bytes;
+  uint64_t pool_bytes;
+  uint64_t work_bytes;
+  uint64_t calls;      // collectives issued so far
+  int last_algo;       // Algo of the most recent allreduce
+  int last_channels;
+  uint64_t kernel_launches;  // kernels of this library launched so far
+};
+DeviceInfo DeviceContextInfo(DeviceContext* d);
+
+// Symmetric (peer-mapped, multicast-bound when possible) user memory.  Every
+// rank must call with the same size in the same order.  Buffers inside such
+// an allocation are reduced in place by the switch without staging copies.
+void* DeviceContextSymmetricAlloc(Communicator* comm, size_t bytes);
+void DeviceContextSymmetricFree(Communicator* comm, void* ptr);
+
+// Reads the failure doorbell; on failure fetches the report, resets it and
+// raises TRANSPORT_ERROR.  Called after every synchronous collective; callers
+// of asynchronous collectives call it after they synchronised their stream.
+void DeviceContextCheck(DeviceContext* d);
+// Non-raising variant: returns the status code and copies the report.
+uint32_t DeviceContextPeekStatus(DeviceContext* d, DeviceStatus* out);
+
+}  // namespace ibcomm

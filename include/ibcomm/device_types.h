@@ -144,7 +144,8 @@ struct ExecParams {
   StageLayout stage;
   uint64_t seq;          // call sequence number (same on every rank)
   uint64_t timeout_ns;   // limit of every wait
-  DeviceStatus* status;  // host-visible
+  DeviceStatus* status;  // device memory, fetched by the host after a failure
+  uint32_t* doorbell;    // host-mapped word a failing kernel sets non-zero
   DeviceTraceRec* trace; // [channel][trace_capacity]
 };
 

@@ -1,0 +1,755 @@
+// DeviceContext: the device half of a communicator.
+#include "ibcomm/device_context.h"
+
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cstring>
+#include <deque>
+#include <map>
+
+#include "arena.h"
+#include "driver_api.h"
+#include "engine.h"
+#include "fd_channel.h"
+
+namespace ibcomm {
+
+namespace {
+
+// First message between two ranks on the device path.
+struct Hello {
+  ShareTicket ticket;
+  int32_t multicast_ok;
+  int32_t device;
+  uint64_t arena_bytes;
+  uint64_t pool_bytes;
+  uint64_t work_bytes;
+};
+
+struct SymmetricAlloc {
+  std::unique_ptr<SharedAllocation> mine;
+  std::vector<std::unique_ptr<SharedAllocation>> imported;  // by rank (null for me)
+  std::unique_ptr<MulticastGroup> mc;
+  unsigned char* peer_ptr[kMaxRanks] = {nullptr};
+  size_t bytes = 0;
+};
+
+struct LoopbackSend {
+  const void* buf;
+  size_t len;
+};
+
+}  // namespace
+
+class DeviceContext {
+ public:
+  explicit DeviceContext(Communicator* comm);
+  ~DeviceContext();
+
+  void ConnectPeers();
+  void Allreduce(DType dtype, const void* sendbuf, void* recvbuf, size_t n, const CudaAllreduceOptions& opts);
+  void Check();
+  uint32_t Peek(DeviceStatus* out);
+
+  void Send(int dest, const void* buf, size_t len);
+  void Recv(int src, void* buf, size_t len);
+  bool SendPoll(int dest);
+  bool RecvPoll(int src);
+  void SendWait(int dest);
+  void RecvWait(int src);
+
+  void* SymmetricAlloc_(size_t bytes);
+  void SymmetricFree_(void* ptr);
+  void CollectTrace(Tracer* tracer);
+  DeviceInfo Info() const;
+
+ private:
+  struct P2pState {
+    cudaEvent_t send_done = nullptr, recv_done = nullptr;
+    uint64_t pieces_sent = 0, pieces_received = 0;
+    std::deque<LoopbackSend> loopback;  // same-device sends waiting for their receive
+    bool loopback_send_complete = false;
+  };
+
+  cudaStream_t StreamFor(const CudaAllreduceOptions& opts);
+  void OrderAfterPrevious(cudaStream_t stream);
+  void MarkIssued(cudaStream_t stream);
+  void Finish(cudaStream_t stream, bool async);
+  bool IsLoopback(int peer) const;
+  const SymmetricAlloc* FindSymmetric(const void* p, size_t bytes) const;
+
+  void RunCopy(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, cudaStream_t stream);
+  void RunProgram(Algo algo, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
+                  cudaStream_t stream);
+  void RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels, cudaStream_t stream);
+  void RunNvls(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels, cudaStream_t stream);
+  void ExchangeAllocation(SharedAllocation* mine, std::vector<std::unique_ptr<SharedAllocation>>* imported,
+                          unsigned char** peer_ptr, bool try_multicast, std::unique_ptr<MulticastGroup>* mc);
+
+  Communicator* comm_;
+  int device_ = 0;
+  int rank_ = 0, ws_ = 1;
+  cudaStream_t stream_ = nullptr;
+  cudaEvent_t last_done_ = nullptr;
+  cudaStream_t last_stream_ = nullptr;
+  bool have_last_ = false;
+  ArenaLayout layout_;
+  SharedAllocation arena_;
+  std::vector<std::unique_ptr<SharedAllocation>> peer_arenas_;
+  std::unique_ptr<MulticastGroup> mc_;
+  std::vector<std::unique_ptr<FdChannel>> fdch_;
+  bool connected_ = false;
+  bool multicast_local_ok_ = false;
+  RankResources rr_;
+  StatusBlock status_;
+  ProgramCache cache_;
+  uint64_t seq_ = 0;
+  uint64_t oneshot_calls_ = 0;
+  uint64_t calls_ = 0;
+  uint64_t kernel_launches_ = 0;
+  int last_algo_ = 0, last_channels_ = 0;
+  int max_channels_ = env::kDefaultNumCudaStream;
+  std::vector<P2pState> p2p_;
+  std::vector<std::unique_ptr<SymmetricAlloc>> symm_;
+  // tracing
+  DeviceTraceRec* d_trace_ = nullptr;
+  int trace_capacity_ = 0;
+  int trace_channels_ = 0;
+  struct PendingTrace {
+    int channels;
+    int ops;
+    struct timespec host_launch;
+  };
+  std::deque<PendingTrace> pending_trace_;
+  std::vector<std::pair<double, double>> trace_wait_, trace_done_;  // (start_ns, dur_ns) relative to base
+  Tracer* tracer_ = nullptr;
+};
+
+// ------------------------------------------------------------------ set-up
+DeviceContext::DeviceContext(Communicator* comm) : comm_(comm) {
+  CUDACHECK(cudaGetDevice(&device_));
+  rank_ = comm->rank() < 0 ? 0 : comm->rank();
+  ws_ = static_cast<int>(comm->world_size());
+  if (ws_ > kMaxRanks) IBCOMM_FAIL(NOT_SUPPORTED, "Device collectives support up to %d ranks (got %d).\n", kMaxRanks, ws_);
+  max_channels_ = std::min(env::ReadNumCudaStream(), kMaxChannels);
+  layout_ = MakeArenaLayout(env::ReadPreAllocSize(), env::ReadWorkGpuMemorySize());
+  CUDACHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+  CUDACHECK(cudaEventCreateWithFlags(&last_done_, cudaEventDisableTiming));
+  multicast_local_ok_ = !env::ReadDisableNvls() && ws_ > 1 && MulticastGroup::Supported(device_);
+  size_t align = 0;
+  if (multicast_local_ok_) align = MulticastGroup::Granularity(ws_, layout_.total_bytes);
+  arena_.Create(layout_.total_bytes, device_, align);
+  status_.Create();
+  rr_.rank = rank_;
+  rr_.world_size = ws_;
+  rr_.layout = layout_;
+  rr_.peers.arena[rank_] = arena_.ptr();
+  rr_.d_status = status_.d_status;
+  rr_.h_doorbell = status_.h_doorbell;
+  rr_.d_doorbell = status_.d_doorbell;
+  p2p_.resize(static_cast<size_t>(ws_));
+  peer_arenas_.resize(static_cast<size_t>(ws_));
+  fdch_.resize(static_cast<size_t>(ws_));
+  tracer_ = &comm->tracer();
+  if (tracer_->enabled()) {
+    trace_capacity_ = 512;
+    trace_channels_ = max_channels_;
+    CUDACHECK(cudaMalloc(&d_trace_, sizeof(DeviceTraceRec) * static_cast<size_t>(trace_capacity_) * static_cast<size_t>(trace_channels_)));
+  }
+}
+
+DeviceContext::~DeviceContext() {
+  cudaDeviceSynchronize();
+  for (P2pState& s : p2p_) {
+    if (s.send_done) cudaEventDestroy(s.send_done);
+    if (s.recv_done) cudaEventDestroy(s.recv_done);
+  }
+  cache_.Clear();
+  symm_.clear();
+  mc_.reset();
+  peer_arenas_.clear();
+  arena_.Release();
+  status_.Destroy();
+  if (d_trace_) cudaFree(d_trace_);
+  if (last_done_) cudaEventDestroy(last_done_);
+  if (stream_) cudaStreamDestroy(stream_);
+  (void)cudaGetLastError();
+}
+
+bool DeviceContext::IsLoopback(int peer) const {
+  // A queue pair whose other end lives in this very communicator (the
+  // single-process self-connection used by the transport smoke test).
+  const auto& ep = comm_->eps_[static_cast<size_t>(peer)];
+  if (!ep.connected) return false;
+  if (ep.peer_info.qp_n != static_cast<uint32_t>(getpid())) return false;
+  for (const auto& other : comm_->eps_)
+    if (other.created && other.my_info.psn == ep.peer_info.psn && other.my_info.qp_n == ep.peer_info.qp_n) return true;
+  return false;
+}
+
+void DeviceContext::ExchangeAllocation(SharedAllocation* mine, std::vector<std::unique_ptr<SharedAllocation>>* imported,
+                                       unsigned char** peer_ptr, bool try_multicast, std::unique_ptr<MulticastGroup>* mc) {
+  const int timeout = std::max(comm_->timeout_ms(), 30000);
+  // Tickets over the host transport.
+  Hello mine_hello;
+  memset(&mine_hello, 0, sizeof(mine_hello));
+  mine_hello.ticket = mine->Ticket();
+  mine_hello.multicast_ok = (try_multicast && multicast_local_ok_ && mine->mode() == ShareMode::kVmm) ? 1 : 0;
+  mine_hello.device = device_;
+  mine_hello.arena_bytes = mine->bytes();
+  mine_hello.pool_bytes = layout_.pool_bytes;
+  mine_hello.work_bytes = layout_.work_bytes;
+  std::vector<Hello> hellos(static_cast<size_t>(ws_));
+  for (int q = 0; q < ws_; ++q) {
+    if (q == rank_) continue;
+    comm_->PostSend(q, &mine_hello, sizeof(Hello));
+    comm_->PostRecv(q, &hellos[static_cast<size_t>(q)], sizeof(Hello));
+  }
+  for (int q = 0; q < ws_; ++q) {
+    if (q == rank_) continue;
+    comm_->WaitRecvCompletion(q);
+    --comm_->eps_[static_cast<size_t>(q)].recv_completions;
+    comm_->WaitSendCompletion(q);
+    --comm_->eps_[static_cast<size_t>(q)].send_completions;
+  }
+  bool all_mc = mine_hello.multicast_ok != 0;
+  for (int q = 0; q < ws_; ++q) {
+    if (q == rank_) continue;
+    const Hello& h = hellos[static_cast<size_t>(q)];
+    if (h.arena_bytes != mine->bytes() || h.pool_bytes != layout_.pool_bytes || h.work_bytes != layout_.work_bytes)
+      IBCOMM_FAIL(INVALID_ARGUMENT,
+                  "Rank %d uses a different arena geometry (%llu bytes vs %zu): IBCOMM_MEMORY_POOL_PRE_ALLOC and "
+                  "IBCOMM_WORK_GPU_MEMORY_SIZE must agree on all ranks.\n",
+                  q, static_cast<unsigned long long>(h.arena_bytes), mine->bytes());
+    all_mc = all_mc && h.multicast_ok != 0;
+  }
+  // Descriptors over the per-pair unix sockets.
+  int my_fd_mode = mine->mode() == ShareMode::kVmm ? 1 : 0;
+  imported->clear();
+  imported->resize(static_cast<size_t>(ws_));
+  for (int q = 0; q < ws_; ++q) {
+    if (q == rank_) continue;
+    int sent_fd = -1;
+    if (my_fd_mode) sent_fd = mine->ExportFd();
+    int token = my_fd_mode;
+    fdch_[static_cast<size_t>(q)]->Send(&token, sizeof(token), sent_fd);
+    if (sent_fd >= 0) close(sent_fd);
+  }
+  for (int q = 0; q < ws_; ++q) {
+    if (q == rank_) continue;
+    int token = 0;
+    int fd = fdch_[static_cast<size_t>(q)]->Recv(&token, sizeof(token), timeout);
+    std::unique_ptr<SharedAllocation> imp(new SharedAllocation());
+    imp->Import(hellos[static_cast<size_t>(q)].ticket, fd, device_);
+    peer_ptr[q] = imp->ptr();
+    (*imported)[static_cast<size_t>(q)] = std::move(imp);
+  }
+  peer_ptr[rank_] = mine->ptr();
+  comm_->Barrier();
+
+  // Multicast object: rank 0 creates, everybody adds its device, then binds.
+  mc->reset();
+  if (!all_mc) return;
+  int ok = 1;
+  std::unique_ptr<MulticastGroup> group(new MulticastGroup());
+  if (rank_ == 0) {
+    // The same descriptor is handed to every peer (each receives its own duplicate).
+    int fd = group->CreateRoot(mine->bytes(), ws_);
+    if (fd < 0) ok = 0;
+    for (int q = 1; q < ws_; ++q) fdch_[static_cast<size_t>(q)]->Send(&ok, sizeof(ok), fd);
+    if (fd >= 0) close(fd);
+  } else {
+    int fd = fdch_[0]->Recv(&ok, sizeof(ok), timeout);
+    if (ok) group->Import(fd, mine->bytes());
+  }
+  if (!ok) {
+    comm_->Barrier();
+    return;
+  }
+  group->AddDevice(device_);
+  comm_->Barrier();
+  group->BindAndMap(*mine, device_);
+  comm_->Barrier();
+  *mc = std::move(group);
+}
+
+void DeviceContext::ConnectPeers() {
+  if (connected_) return;
+  rank_ = comm_->rank();
+  if (rank_ < 0) IBCOMM_FAIL(INVALID_ARGUMENT, "Device collectives need RegisterMyself first.\n");
+  rr_.rank = rank_;
+  rr_.peers.arena[rank_] = arena_.ptr();
+  if (ws_ > 1) {
+    const int timeout = std::max(comm_->timeout_ms(), 30000);
+    // One stream socket per pair: the lower rank listens on the name of its
+    // endpoint for that peer, the higher rank connects to it.
+    for (int q = 0; q < ws_; ++q) {
+      if (q == rank_) continue;
+      const auto& ep = comm_->eps_[static_cast<size_t>(q)];
+      if (!ep.connected || !ep.created)
+        IBCOMM_FAIL(INVALID_ARGUMENT, "Device collectives need a registered queue pair with every rank (rank %d is missing).\n", q);
+      fdch_[static_cast<size_t>(q)].reset(new FdChannel());
+      if (rank_ < q) fdch_[static_cast<size_t>(q)]->Listen(FdChannelName(ep.my_info.qp_n, ep.my_info.psn));
+    }
+    comm_->Barrier();
+    for (int q = 0; q < ws_; ++q) {
+      if (q == rank_) continue;
+      const auto& ep = comm_->eps_[static_cast<size_t>(q)];
+      if (rank_ > q) fdch_[static_cast<size_t>(q)]->Connect(FdChannelName(ep.peer_info.qp_n, ep.peer_info.psn), timeout);
+    }
+    for (int q = 0; q < ws_; ++q)
+      if (q != rank_ && rank_ < q) fdch_[static_cast<size_t>(q)]->Accept(timeout);
+    ExchangeAllocation(&arena_, &peer_arenas_, rr_.peers.arena, true, &mc_);
+    rr_.peers.mc_arena = mc_ ? mc_->ptr() : nullptr;
+  }
+  connected_ = true;
+}
+
+// ---------------------------------------------------------------- streams
+cudaStream_t DeviceContext::StreamFor(const CudaAllreduceOptions& opts) {
+  return opts.stream != nullptr ? static_cast<cudaStream_t>(opts.stream) : stream_;
+}
+
+void DeviceContext::OrderAfterPrevious(cudaStream_t stream) {
+  // Collectives of one communicator reuse the same staging memory and flags:
+  // the next one may only start when the previous one has finished, also when
+  // the caller switches streams.
+  if (have_last_ && last_stream_ != stream) CUDACHECK(cudaStreamWaitEvent(stream, last_done_, 0));
+}
+
+void DeviceContext::MarkIssued(cudaStream_t stream) {
+  CUDACHECK(cudaEventRecord(last_done_, stream));
+  last_stream_ = stream;
+  have_last_ = true;
+  ++calls_;
+}
+
+void DeviceContext::Finish(cudaStream_t stream, bool async) {
+  if (async) return;
+  CUDACHECK(cudaStreamSynchronize(stream));
+  Check();
+}
+
+uint32_t DeviceContext::Peek(DeviceStatus* out) { return status_.Consume(out, stream_); }
+
+void DeviceContext::Check() {
+  DeviceStatus st;
+  uint32_t code = status_.Consume(&st, stream_);
+  if (code != 0) IBCOMM_FAIL(TRANSPORT_ERROR, "%s\n", DescribeStatus(st).c_str());
+}
+
+// -------------------------------------------------------------- allreduce
+const SymmetricAlloc* DeviceContext::FindSymmetric(const void* p, size_t bytes) const {
+  const unsigned char* c = static_cast<const unsigned char*>(p);
+  for (const auto& s : symm_)
+    if (s && c >= s->mine->ptr() && c + bytes <= s->mine->ptr() + s->bytes) return s.get();
+  return nullptr;
+}
+
+void DeviceContext::RunCopy(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, cudaStream_t stream) {
+  if (sendbuf == recvbuf && scale == 1.0) return;
+  CopyParams cp{sendbuf, recvbuf, n, static_cast<int32_t>(dtype), static_cast<int32_t>(dtype), scale};
+  CUDACHECK(LaunchCopyKernel(cp, 148 * 2, stream));
+  ++kernel_launches_;
+}
+
+void DeviceContext::RunProgram(Algo algo, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale,
+                               int channels, cudaStream_t stream) {
+  const CachedProgram& cp = cache_.Get(algo, rank_, ws_, n, dtype, wire, layout_, scale != 1.0);
+  const uint64_t seq = ++seq_;
+  DeviceTraceRec* trace = nullptr;
+  int cap = 0;
+  if (d_trace_ != nullptr && channels <= trace_channels_) {
+    trace = d_trace_;
+    cap = trace_capacity_;
+    if (!pending_trace_.empty()) CollectTrace(tracer_);
+    PendingTrace pt;
+    pt.channels = channels;
+    pt.ops = std::min<int>(static_cast<int>(cp.prog.ops.size()), cap);
+    clock_gettime(CLOCK_MONOTONIC_RAW, &pt.host_launch);
+    pending_trace_.push_back(pt);
+  }
+  ExecParams p = MakeExecParams(rr_, cp, dtype, wire, sendbuf, recvbuf, n, scale, seq,
+                                static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull, trace, cap);
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+  CUDACHECK(LaunchExecKernel(p, nullptr, 1, channels, stream));
+  ++kernel_launches_;
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+}
+
+void DeviceContext::RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
+                               cudaStream_t stream) {
+  const uint64_t seq = ++seq_;
+  const int parity = static_cast<int>(oneshot_calls_++ & 1);
+  OneShotParams p = MakeOneShotParams(rr_, dtype, sendbuf, recvbuf, n, scale, seq, parity,
+                                      static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull);
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+  CUDACHECK(LaunchOneShotKernel(p, nullptr, 1, channels, stream));
+  ++kernel_launches_;
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+}
+
+void DeviceContext::RunNvls(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
+                            cudaStream_t stream) {
+  const size_t esize = DTypeSize(dtype);
+  const size_t bytes = n * esize;
+  NvlsParams p;
+  memset(&p, 0, sizeof(p));
+  p.rank = rank_;
+  p.world_size = ws_;
+  p.dtype = static_cast<int32_t>(dtype);
+  p.peers = rr_.peers;
+  p.sendbuf = sendbuf;
+  p.recvbuf = recvbuf;
+  p.len_elements = n;
+  p.scale = scale;
+  p.seq = ++seq_;
+  p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
+  p.status = rr_.d_status;
+  p.doorbell = rr_.d_doorbell;
+
+  const SymmetricAlloc* sin = FindSymmetric(sendbuf, bytes);
+  const SymmetricAlloc* sout = FindSymmetric(recvbuf, bytes);
+  const bool zin = sin != nullptr && sin->mc && (reinterpret_cast<uintptr_t>(sendbuf) & 15u) == 0;
+  const bool zout = sout != nullptr && sout->mc && (reinterpret_cast<uintptr_t>(recvbuf) & 15u) == 0;
+  // Staging windows: first half of the pool for inputs, second half for outputs.
+  const uint64_t half = layout_.pool_bytes / 2 / 4096 * 4096;
+  uint64_t window_elems = half / esize;
+  p.stage_in = zin ? 0 : 1;
+  p.stage_out = zout ? 0 : 1;
+  if (zin) {
+    const size_t off = static_cast<const unsigned char*>(sendbuf) - sin->mine->ptr();
+    p.mc_in = sin->mc->ptr() + off;
+    p.local_in = sin->mine->ptr() + off;
+    for (int q = 0; q < ws_; ++q) p.peer_in[q] = sin->peer_ptr[q] + off;
+  } else {
+    p.mc_in = mc_->ptr() + layout_.pool_offset;
+    p.local_in = arena_.ptr() + layout_.pool_offset;
+    for (int q = 0; q < ws_; ++q) p.peer_in[q] = rr_.peers.arena[q] + layout_.pool_offset;
+  }
+  if (zout) {
+    const size_t off = static_cast<unsigned char*>(recvbuf) - sout->mine->ptr();
+    p.mc_out = sout->mc->ptr() + off;
+    p.local_out = sout->mine->ptr() + off;
+  } else {
+    p.mc_out = mc_->ptr() + layout_.pool_offset + half;
+    p.local_out = arena_.ptr() + layout_.pool_offset + half;
+  }
+  p.window_elems = (zin && zout) ? n : window_elems;
+  if (p.window_elems == 0) p.window_elems = 1;
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+  CUDACHECK(LaunchNvlsKernel(p, nullptr, 1, channels, stream));
+  ++kernel_launches_;
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+}
+
+void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, size_t n, const CudaAllreduceOptions& opts) {
+  if (sendbuf == nullptr || recvbuf == nullptr) IBCOMM_FAIL(INVALID_ARGUMENT, "AllreduceCuda: null buffer.\n");
+  cudaStream_t stream = StreamFor(opts);
+  const size_t esize = DTypeSize(dtype);
+  const size_t bytes = n * esize;
+  DType wire = (dtype == DType::kFloat32 && (opts.wire == DType::kBFloat16 || opts.wire == DType::kFloat16)) ? opts.wire : dtype;
+  if (ws_ == 1) {
+    OrderAfterPrevious(stream);
+    RunCopy(dtype, sendbuf, recvbuf, n, opts.scale, stream);
+    MarkIssued(stream);
+    last_algo_ = 0;
+    last_channels_ = 0;
+    Finish(stream, opts.async);
+    return;
+  }
+  if (n < static_cast<size_t>(ws_))
+    IBCOMM_FAIL(NOT_SUPPORTED,
+                "Input vector is too short for the Allreduce algorithms: %zu elements for %d processes.\n", n, ws_);
+  ConnectPeers();
+  Algo algo = opts.algo;
+  if (algo == Algo::kAuto) algo = AlgoFromName(env::ReadAlgo());
+  const bool nvls_ok = mc_ != nullptr && NvlsSupportsDType(dtype) && wire == dtype;
+  int channels;
+  if (algo == Algo::kAuto) {
+    const bool zero_copy = FindSymmetric(sendbuf, bytes) != nullptr && FindSymmetric(recvbuf, bytes) != nullptr;
+    TunerChoice c = ChooseAlgorithm(bytes, ws_, nvls_ok, zero_copy, max_channels_);
+    algo = c.algo;
+    channels = c.channels;
+    if (algo == Algo::kOneShot && (bytes > layout_.oneshot_slot_bytes || wire != dtype)) {
+      algo = Algo::kRing;
+      channels = ChooseChannels(algo, bytes, ws_, max_channels_);
+    }
+  } else {
+    if (algo == Algo::kNvls && !nvls_ok)
+      IBCOMM_FAIL(NOT_SUPPORTED, "The NVLS algorithm needs NVSwitch multicast and a float32/float16/bfloat16 buffer without wire compression.\n");
+    if (algo == Algo::kOneShot && bytes > layout_.oneshot_slot_bytes)
+      IBCOMM_FAIL(INVALID_ARGUMENT, "One-shot allreduce handles at most %llu bytes (got %zu).\n",
+                  static_cast<unsigned long long>(layout_.oneshot_slot_bytes), bytes);
+    if (algo == Algo::kOneShot && wire != dtype) IBCOMM_FAIL(NOT_SUPPORTED, "One-shot allreduce has no wire compression.\n");
+    if (algo == Algo::kDirect) IBCOMM_FAIL(NOT_SUPPORTED, "Algorithm 'direct' is not available.\n");
+    channels = ChooseChannels(algo, bytes, ws_, max_channels_);
+  }
+  OrderAfterPrevious(stream);
+  switch (algo) {
+    case Algo::kRing:
+    case Algo::kRabenseifner:
+      RunProgram(algo, dtype, wire, sendbuf, recvbuf, n, opts.scale, channels, stream);
+      break;
+    case Algo::kOneShot:
+      RunOneShot(dtype, sendbuf, recvbuf, n, opts.scale, channels, stream);
+      break;
+    case Algo::kNvls:
+      RunNvls(dtype, sendbuf, recvbuf, n, opts.scale, channels, stream);
+      break;
+    default:
+      IBCOMM_FAIL(INVALID_ARGUMENT, "Unknown algorithm.\n");
+  }
+  MarkIssued(stream);
+  last_algo_ = static_cast<int>(algo);
+  last_channels_ = channels;
+  Finish(stream, opts.async);
+}
+
+// ------------------------------------------------------------ point to point
+void DeviceContext::Send(int dest, const void* buf, size_t len) {
+  P2pState& s = p2p_[static_cast<size_t>(dest)];
+  if (s.send_done == nullptr) CUDACHECK(cudaEventCreateWithFlags(&s.send_done, cudaEventDisableTiming));
+  if (IsLoopback(dest)) {
+    // Both ends are this communicator on this device: the matching Recv does
+    // one device-to-device copy.  (Two kernels that wait on each other must
+    // never be separate launches on one GPU.)
+    int owner = -1;
+    for (size_t q = 0; q < comm_->eps_.size(); ++q)
+      if (comm_->eps_[q].created && comm_->eps_[q].my_info.psn == comm_->eps_[static_cast<size_t>(dest)].peer_info.psn) owner = static_cast<int>(q);
+    p2p_[static_cast<size_t>(owner)].loopback.push_back(LoopbackSend{buf, len});
+    s.loopback_send_complete = false;
+    return;
+  }
+  ConnectPeers();
+  OrderAfterPrevious(stream_);
+  P2pParams p;
+  memset(&p, 0, sizeof(p));
+  p.rank = rank_;
+  p.peer = dest;
+  p.is_send = 1;
+  p.world_size = ws_;
+  p.peers = rr_.peers;
+  p.src = buf;
+  p.bytes = len;
+  p.mailbox_offset = layout_.mailbox_offset;
+  p.slot_bytes = layout_.mailbox_slot_bytes;
+  p.slots = layout_.mailbox_slots;
+  p.first_piece = s.pieces_sent;
+  p.seq = 0xFFFFFFFF00000000ull | static_cast<uint64_t>(rank_);
+  p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
+  p.status = rr_.d_status;
+  p.doorbell = rr_.d_doorbell;
+  s.pieces_sent += (len + p.slot_bytes - 1) / p.slot_bytes;
+  IBCOMM_TRACE(*tracer_, kTraceIssueSend);
+  CUDACHECK(LaunchP2pKernel(p, stream_));
+  ++kernel_launches_;
+  IBCOMM_TRACE(*tracer_, kTraceIssueSend);
+  CUDACHECK(cudaEventRecord(s.send_done, stream_));
+}
+
+void DeviceContext::Recv(int src, void* buf, size_t len) {
+  P2pState& s = p2p_[static_cast<size_t>(src)];
+  if (s.recv_done == nullptr) CUDACHECK(cudaEventCreateWithFlags(&s.recv_done, cudaEventDisableTiming));
+  if (IsLoopback(src)) {
+    if (s.loopback.empty())
+      IBCOMM_FAIL(NOT_SUPPORTED, "Recv on a self-connected device endpoint needs the matching Send to be posted first.\n");
+    LoopbackSend ls = s.loopback.front();
+    s.loopback.pop_front();
+    if (ls.len != len)
+      IBCOMM_FAIL(TRANSPORT_ERROR, "Message length mismatch: %zu bytes posted for receive, %zu bytes incoming.\n", len, ls.len);
+    CUDACHECK(cudaMemcpyAsync(buf, ls.buf, len, cudaMemcpyDeviceToDevice, stream_));
+    CUDACHECK(cudaEventRecord(s.recv_done, stream_));
+    for (P2pState& o : p2p_)
+      if (o.send_done != nullptr && !o.loopback_send_complete) {
+        CUDACHECK(cudaEventRecord(o.send_done, stream_));
+        o.loopback_send_complete = true;
+      }
+    return;
+  }
+  ConnectPeers();
+  OrderAfterPrevious(stream_);
+  P2pParams p;
+  memset(&p, 0, sizeof(p));
+  p.rank = rank_;
+  p.peer = src;
+  p.is_send = 0;
+  p.world_size = ws_;
+  p.peers = rr_.peers;
+  p.dst = buf;
+  p.bytes = len;
+  p.mailbox_offset = layout_.mailbox_offset;
+  p.slot_bytes = layout_.mailbox_slot_bytes;
+  p.slots = layout_.mailbox_slots;
+  p.first_piece = s.pieces_received;
+  p.seq = 0xFFFFFFFF00000000ull | static_cast<uint64_t>(rank_);
+  p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
+  p.status = rr_.d_status;
+  p.doorbell = rr_.d_doorbell;
+  s.pieces_received += (len + p.slot_bytes - 1) / p.slot_bytes;
+  IBCOMM_TRACE(*tracer_, kTraceIssueRecv);
+  CUDACHECK(LaunchP2pKernel(p, stream_));
+  ++kernel_launches_;
+  IBCOMM_TRACE(*tracer_, kTraceIssueRecv);
+  CUDACHECK(cudaEventRecord(s.recv_done, stream_));
+}
+
+bool DeviceContext::SendPoll(int dest) {
+  P2pState& s = p2p_[static_cast<size_t>(dest)];
+  if (IsLoopback(dest) && !s.loopback_send_complete) return false;
+  cudaError_t e = cudaEventQuery(s.send_done);
+  if (e == cudaErrorNotReady) return false;
+  CUDACHECK(e);
+  Check();
+  return true;
+}
+
+bool DeviceContext::RecvPoll(int src) {
+  P2pState& s = p2p_[static_cast<size_t>(src)];
+  cudaError_t e = cudaEventQuery(s.recv_done);
+  if (e == cudaErrorNotReady) return false;
+  CUDACHECK(e);
+  Check();
+  return true;
+}
+
+void DeviceContext::SendWait(int dest) {
+  P2pState& s = p2p_[static_cast<size_t>(dest)];
+  if (IsLoopback(dest) && !s.loopback_send_complete)
+    IBCOMM_FAIL(NOT_SUPPORTED, "SendWait on a self-connected device endpoint needs the matching Recv to be posted first.\n");
+  CUDACHECK(cudaEventSynchronize(s.send_done));
+  Check();
+}
+
+void DeviceContext::RecvWait(int src) {
+  P2pState& s = p2p_[static_cast<size_t>(src)];
+  CUDACHECK(cudaEventSynchronize(s.recv_done));
+  Check();
+}
+
+// ------------------------------------------------------- symmetric memory
+void* DeviceContext::SymmetricAlloc_(size_t bytes) {
+  ConnectPeers();
+  std::unique_ptr<SymmetricAlloc> s(new SymmetricAlloc());
+  s->mine.reset(new SharedAllocation());
+  size_t align = 0;
+  if (mc_ != nullptr) align = MulticastGroup::Granularity(ws_, bytes);
+  s->mine->Create(bytes, device_, align);
+  s->bytes = s->mine->bytes();
+  if (ws_ > 1) ExchangeAllocation(s->mine.get(), &s->imported, s->peer_ptr, mc_ != nullptr, &s->mc);
+  else s->peer_ptr[0] = s->mine->ptr();
+  void* p = s->mine->ptr();
+  symm_.push_back(std::move(s));
+  return p;
+}
+
+void DeviceContext::SymmetricFree_(void* ptr) {
+  CUDACHECK(cudaDeviceSynchronize());
+  if (ws_ > 1) comm_->Barrier();
+  for (auto& s : symm_)
+    if (s && s->mine->ptr() == ptr) {
+      s.reset();
+      return;
+    }
+  IBCOMM_FAIL(INVALID_ARGUMENT, "SymmetricFree: %p is not a symmetric allocation of this communicator.\n", ptr);
+}
+
+// ------------------------------------------------------------------ trace
+void DeviceContext::CollectTrace(Tracer* tracer) {
+  if (d_trace_ == nullptr || tracer == nullptr || pending_trace_.empty()) return;
+  CUDACHECK(cudaDeviceSynchronize());
+  PendingTrace pt = pending_trace_.back();
+  pending_trace_.clear();
+  std::vector<DeviceTraceRec> recs(static_cast<size_t>(trace_capacity_) * static_cast<size_t>(pt.channels));
+  CUDACHECK(cudaMemcpy(recs.data(), d_trace_, recs.size() * sizeof(DeviceTraceRec), cudaMemcpyDeviceToHost));
+  // Device stamps are relative to the earliest one, which is pinned to the
+  // host time of the launch.
+  uint64_t t0 = ~0ull;
+  for (int c = 0; c < pt.channels; ++c)
+    for (int i = 0; i < pt.ops; ++i) {
+      const DeviceTraceRec& r = recs[static_cast<size_t>(c) * trace_capacity_ + i];
+      if (r.t_wait_done != 0) t0 = std::min(t0, r.t_wait_done);
+    }
+  if (t0 == ~0ull) return;
+  const struct timespec& base = tracer->base();
+  const double launch_ns = (static_cast<double>(pt.host_launch.tv_sec - base.tv_sec) * 1e9) +
+                           static_cast<double>(pt.host_launch.tv_nsec - base.tv_nsec);
+  // Channel 0 is representative; all channels run the same program.
+  uint64_t prev = t0;
+  for (int i = 0; i < pt.ops; ++i) {
+    const DeviceTraceRec& r = recs[static_cast<size_t>(i)];
+    if (r.t_wait_done == 0 || r.t_done == 0) continue;
+    tracer->AddInterval(kTraceReceived, launch_ns + static_cast<double>(prev - t0), static_cast<double>(r.t_wait_done - prev));
+    tracer->AddInterval(kTraceReduced, launch_ns + static_cast<double>(r.t_wait_done - t0), static_cast<double>(r.t_done - r.t_wait_done));
+    prev = r.t_done;
+  }
+}
+
+DeviceInfo DeviceContext::Info() const {
+  DeviceInfo i;
+  memset(&i, 0, sizeof(i));
+  i.device = device_;
+  i.nvls = mc_ != nullptr ? 1 : 0;
+  i.share_mode = static_cast<int>(arena_.mode());
+  i.arena_bytes = arena_.bytes();
+  i.pool_bytes = layout_.pool_bytes;
+  i.work_bytes = layout_.work_bytes;
+  i.calls = calls_;
+  i.kernel_launches = kernel_launches_;
+  i.last_algo = last_algo_;
+  i.last_channels = last_channels_;
+  return i;
+}
+
+// ------------------------------------------------- free-function interface
+bool DeviceContextIsDevicePointer(const void* p) {
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, p);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+void DeviceContextSend(DeviceContext* d, int dest, const void* buf, size_t len) { d->Send(dest, buf, len); }
+void DeviceContextRecv(DeviceContext* d, int src, void* buf, size_t len) { d->Recv(src, buf, len); }
+bool DeviceContextSendPoll(DeviceContext* d, int dest) { return d->SendPoll(dest); }
+bool DeviceContextRecvPoll(DeviceContext* d, int src) { return d->RecvPoll(src); }
+void DeviceContextSendWait(DeviceContext* d, int dest) { d->SendWait(dest); }
+void DeviceContextRecvWait(DeviceContext* d, int src) { d->RecvWait(src); }
+void DeviceContextCollectTrace(DeviceContext* d, Tracer* tracer) { d->CollectTrace(tracer); }
+DeviceInfo DeviceContextInfo(DeviceContext* d) { return d->Info(); }
+void DeviceContextCheck(DeviceContext* d) { d->Check(); }
+uint32_t DeviceContextPeekStatus(DeviceContext* d, DeviceStatus* out) { return d->Peek(out); }
+
+void* DeviceContextSymmetricAlloc(Communicator* comm, size_t bytes) {
+  comm->PrepareMemoryPool();
+  return comm->device()->SymmetricAlloc_(bytes);
+}
+void DeviceContextSymmetricFree(Communicator* comm, void* ptr) {
+  if (comm->device() == nullptr) IBCOMM_FAIL(INVALID_ARGUMENT, "SymmetricFree: no device context.\n");
+  comm->device()->SymmetricFree_(ptr);
+}
+
+void DeviceContextDeleter::operator()(DeviceContext* d) const { delete d; }
+
+// ---------------------------------------------------- Communicator methods
+void Communicator::PrepareMemoryPool() {
+  if (device_) return;
+  if (!initialized_) IBCOMM_FAIL(INVALID_ARGUMENT, "PrepareMemoryPool: communicator is not initialized.\n");
+  device_.reset(new DeviceContext(this));
+}
+
+void Communicator::AllreduceCuda(DType dtype, const void* sendbuf, void* recvbuf, size_t len_elements,
+                                 const CudaAllreduceOptions& opts) {
+  if (!initialized_) IBCOMM_FAIL(INVALID_ARGUMENT, "AllreduceCuda: communicator is not initialized.\n");
+  if (sendbuf == nullptr || recvbuf == nullptr) IBCOMM_FAIL(INVALID_ARGUMENT, "AllreduceCuda: null buffer.\n");
+  if (world_size_ > 1 && my_rank_ < 0) IBCOMM_FAIL(INVALID_ARGUMENT, "AllreduceCuda: call RegisterMyself first.\n");
+  CollectiveLease lease(this);
+  PrepareMemoryPool();
+  device_->Allreduce(dtype, sendbuf, recvbuf, len_elements, opts);
+}
+
+}  // namespace ibcomm

@@ -1,0 +1,181 @@
+#include "ibcomm/emu_world.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "engine.h"
+
+namespace ibcomm {
+
+struct EmuWorld::Impl {
+  int ws = 1;
+  int device = 0;
+  ArenaLayout layout;
+  unsigned char* arenas = nullptr;  // ws arenas back to back
+  std::vector<StatusBlock> status;
+  std::vector<RankResources> ranks;
+  ProgramCache cache;
+  void* d_params = nullptr;  // parameter blocks of one launch
+  size_t d_params_bytes = 0;
+  uint64_t seq = 0;
+  uint64_t oneshot_calls = 0;
+  int timeout_ms = env::kDefaultTimeoutMs;
+  int max_blocks = 0;
+  int last_channels = 0;
+  int silent_rank = -1;
+  uint32_t last_status = 0;
+  DeviceStatus last_report{};
+
+  void* Params(size_t bytes) {
+    if (bytes > d_params_bytes) {
+      if (d_params != nullptr) CUDACHECK(cudaFree(d_params));
+      CUDACHECK(cudaMalloc(&d_params, bytes));
+      d_params_bytes = bytes;
+    }
+    return d_params;
+  }
+};
+
+EmuWorld::EmuWorld(int num_ranks, size_t pool_bytes, size_t work_bytes) : ws_(num_ranks), impl_(new Impl()) {
+  if (num_ranks < 1 || num_ranks > kMaxRanks)
+    IBCOMM_FAIL(NOT_SUPPORTED, "EmuWorld supports 1..%d ranks (got %d).\n", kMaxRanks, num_ranks);
+  Impl& m = *impl_;
+  m.ws = num_ranks;
+  CUDACHECK(cudaGetDevice(&m.device));
+  m.timeout_ms = env::ReadTimeoutMs();
+  m.layout = MakeArenaLayout(pool_bytes ? pool_bytes : env::ReadPreAllocSize(), work_bytes ? work_bytes : env::ReadWorkGpuMemorySize());
+  const size_t total = static_cast<size_t>(m.layout.total_bytes) * static_cast<size_t>(num_ranks);
+  CUDACHECK(cudaMalloc(&m.arenas, total));
+  CUDACHECK(cudaMemset(m.arenas, 0, total));
+  m.status.resize(static_cast<size_t>(num_ranks));
+  m.ranks.resize(static_cast<size_t>(num_ranks));
+  for (int r = 0; r < num_ranks; ++r) {
+    m.status[static_cast<size_t>(r)].Create();
+    RankResources& rr = m.ranks[static_cast<size_t>(r)];
+    rr.rank = r;
+    rr.world_size = num_ranks;
+    rr.layout = m.layout;
+    for (int q = 0; q < num_ranks; ++q) rr.peers.arena[q] = m.arenas + static_cast<size_t>(q) * m.layout.total_bytes;
+    rr.peers.mc_arena = nullptr;
+    rr.d_status = m.status[static_cast<size_t>(r)].d_status;
+    rr.h_doorbell = m.status[static_cast<size_t>(r)].h_doorbell;
+    rr.d_doorbell = m.status[static_cast<size_t>(r)].d_doorbell;
+  }
+  m.max_blocks = ExecKernelMaxCoResidentBlocks(m.device);
+  CUDACHECK(cudaDeviceSynchronize());
+}
+
+EmuWorld::~EmuWorld() {
+  Impl& m = *impl_;
+  cudaDeviceSynchronize();
+  m.cache.Clear();
+  for (StatusBlock& s : m.status) s.Destroy();
+  if (m.arenas != nullptr) cudaFree(m.arenas);
+  if (m.d_params != nullptr) cudaFree(m.d_params);
+  (void)cudaGetLastError();
+}
+
+void EmuWorld::SetSilentRank(int r) { impl_->silent_rank = r; }
+void EmuWorld::SetTimeoutMs(int ms) { impl_->timeout_ms = ms > 0 ? ms : env::ReadTimeoutMs(); }
+int EmuWorld::last_channels() const { return impl_->last_channels; }
+
+uint32_t EmuWorld::LastStatus(DeviceStatus* report) const {
+  if (report != nullptr) *report = impl_->last_report;
+  return impl_->last_status;
+}
+
+void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>& sendbufs, const std::vector<void*>& recvbufs,
+                         size_t n, double scale, DType wire, int channels, void* stream_v, bool async) {
+  Impl& m = *impl_;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (static_cast<int>(sendbufs.size()) != m.ws || static_cast<int>(recvbufs.size()) != m.ws)
+    IBCOMM_FAIL(INVALID_ARGUMENT, "EmuWorld::Allreduce needs one buffer pair per rank.\n");
+  for (int r = 0; r < m.ws; ++r)
+    if (sendbufs[static_cast<size_t>(r)] == nullptr || recvbufs[static_cast<size_t>(r)] == nullptr)
+      IBCOMM_FAIL(INVALID_ARGUMENT, "EmuWorld::Allreduce: null buffer.\n");
+  if (dtype != DType::kFloat32) wire = dtype;
+  const size_t esize = DTypeSize(dtype);
+  const size_t bytes = n * esize;
+  m.last_status = 0;
+
+  if (m.ws == 1) {
+    CopyParams cp{sendbufs[0], recvbufs[0], n, static_cast<int32_t>(dtype), static_cast<int32_t>(dtype), scale};
+    if (!(sendbufs[0] == recvbufs[0] && scale == 1.0)) CUDACHECK(LaunchCopyKernel(cp, 148, stream));
+    m.last_channels = 0;
+    if (!async) CUDACHECK(cudaStreamSynchronize(stream));
+    return;
+  }
+
+  if (algo == Algo::kAuto) algo = ChooseAlgorithm(bytes, m.ws, false, false, kMaxChannels).algo;
+  if (algo == Algo::kNvls || algo == Algo::kDirect)
+    IBCOMM_FAIL(NOT_SUPPORTED, "Algorithm '%s' needs one GPU per rank; it cannot be emulated on one GPU.\n", AlgoName(algo));
+  const uint64_t timeout_ns = static_cast<uint64_t>(m.timeout_ms) * 1000000ull;
+  const uint64_t seq = ++m.seq;
+  const int cap = std::max(1, m.max_blocks / m.ws);
+
+  if (algo == Algo::kOneShot) {
+    if (bytes > m.layout.oneshot_slot_bytes)
+      IBCOMM_FAIL(INVALID_ARGUMENT, "One-shot allreduce handles at most %llu bytes (got %zu).\n",
+                  static_cast<unsigned long long>(m.layout.oneshot_slot_bytes), bytes);
+    const int parity = static_cast<int>(m.oneshot_calls++ & 1);
+    std::vector<OneShotParams> ps;
+    for (int r = 0; r < m.ws; ++r)
+      ps.push_back(MakeOneShotParams(m.ranks[static_cast<size_t>(r)], dtype, sendbufs[static_cast<size_t>(r)],
+                                     recvbufs[static_cast<size_t>(r)], n, scale, seq, parity, timeout_ns));
+    int ch = channels > 0 ? channels : ChooseChannels(Algo::kOneShot, bytes, m.ws, kMaxChannels);
+    ch = std::min(ch, cap);
+    void* d = m.Params(ps.size() * sizeof(OneShotParams));
+    CUDACHECK(cudaMemcpyAsync(d, ps.data(), ps.size() * sizeof(OneShotParams), cudaMemcpyHostToDevice, stream));
+    CUDACHECK(LaunchOneShotKernel(ps[0], static_cast<const OneShotParams*>(d), m.ws, ch, stream));
+    m.last_channels = ch;
+  } else {
+    // Validation (length, chunk size) happens while the first program is cut.
+    std::vector<ExecParams> ps;
+    for (int r = 0; r < m.ws; ++r) {
+      const CachedProgram& cp = m.cache.Get(algo, r, m.ws, n, dtype, wire, m.layout, scale != 1.0);
+      ps.push_back(MakeExecParams(m.ranks[static_cast<size_t>(r)], cp, dtype, wire, sendbufs[static_cast<size_t>(r)],
+                                  recvbufs[static_cast<size_t>(r)], n, scale, seq, timeout_ns, nullptr, 0));
+      if (r == m.silent_rank) ps.back().num_ops = 0;
+    }
+    int ch = channels > 0 ? channels : ChooseChannels(algo, bytes, m.ws, kMaxChannels);
+    ch = std::min(ch, cap);
+    void* d = m.Params(ps.size() * sizeof(ExecParams));
+    CUDACHECK(cudaMemcpyAsync(d, ps.data(), ps.size() * sizeof(ExecParams), cudaMemcpyHostToDevice, stream));
+    CUDACHECK(LaunchExecKernel(ps[0], static_cast<const ExecParams*>(d), m.ws, ch, stream));
+    m.last_channels = ch;
+  }
+  if (async) return;
+  CUDACHECK(cudaStreamSynchronize(stream));
+  for (int r = 0; r < m.ws; ++r) {
+    DeviceStatus st;
+    uint32_t code = m.status[static_cast<size_t>(r)].Consume(&st, stream);
+    if (code != 0 && m.last_status == 0) {
+      m.last_status = code;
+      m.last_report = st;
+    }
+  }
+  if (m.last_status != 0) IBCOMM_FAIL(TRANSPORT_ERROR, "%s\n", DescribeStatus(m.last_report).c_str());
+}
+
+void EmuWorld::AllreduceHostBuffers(Algo algo, DType dtype, const std::vector<const void*>& in, const std::vector<void*>& out,
+                                    size_t n) {
+  const size_t bytes = n * DTypeSize(dtype);
+  std::vector<void*> d_in(in.size(), nullptr), d_out(out.size(), nullptr);
+  std::vector<const void*> d_in_c;
+  for (size_t r = 0; r < in.size(); ++r) {
+    CUDACHECK(cudaMalloc(&d_in[r], std::max<size_t>(bytes, 16)));
+    CUDACHECK(cudaMalloc(&d_out[r], std::max<size_t>(bytes, 16)));
+    CUDACHECK(cudaMemcpy(d_in[r], in[r], bytes, cudaMemcpyHostToDevice));
+    d_in_c.push_back(d_in[r]);
+  }
+  Allreduce(algo, dtype, d_in_c, d_out, n);
+  for (size_t r = 0; r < in.size(); ++r) {
+    CUDACHECK(cudaMemcpy(out[r], d_out[r], bytes, cudaMemcpyDeviceToHost));
+    CUDACHECK(cudaFree(d_in[r]));
+    CUDACHECK(cudaFree(d_out[r]));
+  }
+}
+
+}  // namespace ibcomm

@@ -1,0 +1,187 @@
+#include "engine.h"
+
+#include <cstdio>
+#include <cstring>
+
+namespace ibcomm {
+
+static uint64_t AlignUp(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+ArenaLayout MakeArenaLayout(size_t pool_bytes, size_t work_bytes) {
+  ArenaLayout l;
+  uint64_t off = 0;
+  l.control_offset = off;
+  off += AlignUp(sizeof(ControlPage), 65536);
+  l.oneshot_offset = off;
+  l.oneshot_slot_bytes = 256u << 10;
+  off += 2ull * kMaxRanks * l.oneshot_slot_bytes;
+  l.mailbox_offset = off;
+  l.mailbox_slot_bytes = 256u << 10;
+  l.mailbox_slots = 2;
+  off += static_cast<uint64_t>(kMaxRanks) * l.mailbox_slots * l.mailbox_slot_bytes;
+  l.pool_offset = off;
+  l.pool_bytes = AlignUp(pool_bytes < 4096 ? 4096 : pool_bytes, 4096);
+  off += l.pool_bytes;
+  l.work_offset = off;
+  l.work_bytes = AlignUp(work_bytes < 4096 ? 4096 : work_bytes, 4096);
+  off += l.work_bytes;
+  l.total_bytes = AlignUp(off, 2u << 20);
+  return l;
+}
+
+// ------------------------------------------------------------- status block
+void StatusBlock::Create() {
+  CUDACHECK(cudaMalloc(&d_status, sizeof(DeviceStatus)));
+  CUDACHECK(cudaMemset(d_status, 0, sizeof(DeviceStatus)));
+  CUDACHECK(cudaHostAlloc(reinterpret_cast<void**>(&h_doorbell), 64, cudaHostAllocMapped | cudaHostAllocPortable));
+  *h_doorbell = 0;
+  CUDACHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&d_doorbell), h_doorbell, 0));
+}
+
+void StatusBlock::Destroy() {
+  if (d_status != nullptr) cudaFree(d_status);
+  if (h_doorbell != nullptr) cudaFreeHost(h_doorbell);
+  d_status = nullptr;
+  h_doorbell = nullptr;
+  d_doorbell = nullptr;
+  (void)cudaGetLastError();
+}
+
+uint32_t StatusBlock::Consume(DeviceStatus* out, cudaStream_t stream) {
+  if (h_doorbell == nullptr) return 0;
+  uint32_t bell = *reinterpret_cast<volatile uint32_t*>(h_doorbell);
+  if (bell == 0) return 0;
+  DeviceStatus st;
+  memset(&st, 0, sizeof(st));
+  CUDACHECK(cudaMemcpyAsync(&st, d_status, sizeof(st), cudaMemcpyDeviceToHost, stream));
+  CUDACHECK(cudaMemsetAsync(d_status, 0, sizeof(st), stream));
+  CUDACHECK(cudaStreamSynchronize(stream));
+  *reinterpret_cast<volatile uint32_t*>(h_doorbell) = 0;
+  if (st.code == 0) st.code = bell;
+  if (out != nullptr) *out = st;
+  return st.code;
+}
+
+std::string DescribeStatus(const DeviceStatus& st) {
+  static const char* const codes[] = {"ok", "wait timed out", "aborted by a peer", "bad program"};
+  static const char* const kinds[] = {"?", "barrier", "data flag", "slot credit", "mailbox", "one-shot flag"};
+  char buf[320];
+  snprintf(buf, sizeof(buf),
+           "device collective failed: %s while waiting for a %s from rank %d (rank %d, channel %d, op %d, call %llu, "
+           "expected %llu, saw %llu)",
+           codes[st.code < 4 ? st.code : 0], kinds[st.kind < 6 ? st.kind : 0], st.peer, st.rank, st.channel, st.op_index,
+           static_cast<unsigned long long>(st.seq), static_cast<unsigned long long>(st.expected & 0xffffffffull),
+           static_cast<unsigned long long>(st.seen & 0xffffffffull));
+  return buf;
+}
+
+// ------------------------------------------------------------ program cache
+ProgramCache::~ProgramCache() { Clear(); }
+
+void ProgramCache::Clear() {
+  for (auto& kv : cache_)
+    if (kv.second->d_ops != nullptr) cudaFree(kv.second->d_ops);
+  cache_.clear();
+  (void)cudaGetLastError();
+}
+
+const CachedProgram& ProgramCache::Get(Algo algo, int rank, int world_size, size_t len_elements, DType dtype, DType wire,
+                                       const ArenaLayout& layout, bool apply_scale) {
+  const size_t esize = DTypeSize(dtype), wsize = DTypeSize(wire);
+  // Read at the point of use, like the reference: a bad value fails the call.
+  const long long env_chunk = env::ReadChunkSize();
+  const bool ring = algo == Algo::kRing;
+  const uint64_t stage_off = ring ? layout.pool_offset : layout.work_offset;
+  const uint64_t stage_bytes = ring ? layout.pool_bytes : layout.work_bytes;
+  Key key{static_cast<int>(algo), rank, world_size, len_elements, static_cast<int>(dtype), static_cast<int>(wire),
+          env_chunk, apply_scale, stage_off, stage_bytes};
+  auto it = cache_.find(key);
+  if (it != cache_.end()) return *it->second;
+
+  const int regions = NumRegions(algo, world_size);
+  // At least four slots per region keep the pipeline moving; two is the
+  // minimum the schedule needs.
+  uint64_t max_chunk_wire = stage_bytes / (static_cast<uint64_t>(regions) * 4) / 128 * 128;
+  if (max_chunk_wire < 128) max_chunk_wire = 128;
+  const size_t max_chunk_user = static_cast<size_t>(max_chunk_wire / wsize * esize);
+  ProgramRequest req;
+  req.algo = algo;
+  req.rank = rank;
+  req.world_size = world_size;
+  req.ranges = SplitForDevice(len_elements, esize, static_cast<size_t>(world_size), env_chunk, max_chunk_user);
+  if (!ring && rank == 0) {
+    const size_t nominal = len_elements / (4 * static_cast<size_t>(world_size)) * wsize;
+    static bool warned = false;
+    if (nominal > stage_bytes / static_cast<uint64_t>(regions) && !warned) {
+      warned = true;
+      IBCOMM_WARN("IBCOMM_WORK_GPU_MEMORY_SIZE (%llu bytes) is smaller than one chunk per partner (%zu bytes x %d); "
+                  "chunks are cut into smaller pieces. Increase it for large messages.\n",
+                  static_cast<unsigned long long>(stage_bytes), nominal, regions);
+    }
+  }
+  req.wire_elem_bytes = wsize;
+  req.stage_offset = stage_off;
+  req.stage_bytes = stage_bytes;
+  req.apply_scale = apply_scale;
+  std::unique_ptr<CachedProgram> cp(new CachedProgram());
+  cp->prog = BuildProgram(req);
+  if (!cp->prog.ops.empty()) {
+    const size_t bytes = cp->prog.ops.size() * sizeof(Op);
+    CUDACHECK(cudaMalloc(&cp->d_ops, bytes));
+    CUDACHECK(cudaMemcpy(cp->d_ops, cp->prog.ops.data(), bytes, cudaMemcpyHostToDevice));
+  }
+  if (cache_.size() > 256) Clear();
+  const CachedProgram& ref = *cp;
+  cache_[key] = std::move(cp);
+  return ref;
+}
+
+ExecParams MakeExecParams(const RankResources& rr, const CachedProgram& cp, DType dtype, DType wire, const void* sendbuf,
+                          void* recvbuf, size_t len_elements, double scale, uint64_t seq, uint64_t timeout_ns,
+                          DeviceTraceRec* trace, int trace_capacity) {
+  ExecParams p;
+  memset(&p, 0, sizeof(p));
+  p.rank = rr.rank;
+  p.world_size = rr.world_size;
+  p.dtype = static_cast<int32_t>(dtype);
+  p.wire = static_cast<int32_t>(wire);
+  p.peers = rr.peers;
+  p.sendbuf = sendbuf;
+  p.recvbuf = recvbuf;
+  p.len_elements = len_elements;
+  p.scale = scale;
+  p.ops = cp.d_ops;
+  p.num_ops = static_cast<int32_t>(cp.prog.ops.size());
+  p.trace_capacity = trace_capacity;
+  p.stage = cp.prog.stage;
+  p.seq = seq;
+  p.timeout_ns = timeout_ns;
+  p.status = rr.d_status;
+  p.doorbell = rr.d_doorbell;
+  p.trace = trace;
+  return p;
+}
+
+OneShotParams MakeOneShotParams(const RankResources& rr, DType dtype, const void* sendbuf, void* recvbuf,
+                                size_t len_elements, double scale, uint64_t seq, int parity, uint64_t timeout_ns) {
+  OneShotParams p;
+  memset(&p, 0, sizeof(p));
+  p.rank = rr.rank;
+  p.world_size = rr.world_size;
+  p.dtype = static_cast<int32_t>(dtype);
+  p.parity = parity;
+  p.peers = rr.peers;
+  p.sendbuf = sendbuf;
+  p.recvbuf = recvbuf;
+  p.len_elements = len_elements;
+  p.scale = scale;
+  p.slot_offset = rr.layout.oneshot_offset;
+  p.slot_bytes = rr.layout.oneshot_slot_bytes;
+  p.seq = seq;
+  p.timeout_ns = timeout_ns;
+  p.status = rr.d_status;
+  p.doorbell = rr.d_doorbell;
+  return p;
+}
+
+}  // namespace ibcomm

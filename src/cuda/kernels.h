@@ -1,0 +1,100 @@
+// Host-callable launchers of the device kernels (one translation unit each).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "ibcomm/communicator.h"
+#include "ibcomm/device_types.h"
+
+namespace ibcomm {
+
+// ---- op-program executor (ring, Rabenseifner) ----
+// `emu` == nullptr: one rank, grid = channels.  Otherwise `emu` points to
+// `emu_ranks` parameter blocks in device memory and the launch is cooperative.
+cudaError_t LaunchExecKernel(const ExecParams& p, const ExecParams* emu, int emu_ranks, int channels, cudaStream_t stream);
+int ExecKernelMaxCoResidentBlocks(int device);
+
+// ---- world_size == 1, and local staging: out = cast(in * scale) ----
+// Uses bulk asynchronous copies (TMA, non-tensor form) through shared memory.
+struct CopyParams {
+  const void* in;
+  void* out;
+  uint64_t len_elements;
+  int32_t dtype_in;
+  int32_t dtype_out;
+  double scale;
+};
+cudaError_t LaunchCopyKernel(const CopyParams& p, int blocks, cudaStream_t stream);
+
+// ---- NVSwitch multicast allreduce (two-shot) ----
+struct NvlsParams {
+  int32_t rank;
+  int32_t world_size;
+  int32_t dtype;
+  int32_t stage_in;    // copy sendbuf into the multicast-bound staging first
+  int32_t stage_out;   // results land in staging and are copied to recvbuf
+  PeerTable peers;     // control pages live in the arenas
+  const void* sendbuf;
+  void* recvbuf;
+  uint64_t len_elements;
+  double scale;
+  // Multicast and local addresses of the input and output windows.  When
+  // staged, a window holds `window_elems` elements and the message is
+  // processed in rounds; when zero-copy, the window is the whole buffer.
+  unsigned char* mc_in;
+  unsigned char* mc_out;
+  unsigned char* local_in;
+  unsigned char* local_out;
+  // Unicast views of every rank's input window (for the unaligned tail).
+  unsigned char* peer_in[kMaxRanks];
+  uint64_t window_elems;
+  uint64_t seq;
+  uint64_t timeout_ns;
+  DeviceStatus* status;
+  uint32_t* doorbell;
+};
+cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
+
+// ---- one-shot allreduce for small messages (push to every peer, sum locally) ----
+struct OneShotParams {
+  int32_t rank;
+  int32_t world_size;
+  int32_t dtype;
+  int32_t parity;         // which half of the double-buffered slots (one-shot call count & 1)
+  PeerTable peers;
+  const void* sendbuf;
+  void* recvbuf;
+  uint64_t len_elements;
+  double scale;
+  uint64_t slot_offset;   // byte offset of the one-shot area in the arena
+  uint64_t slot_bytes;    // bytes reserved per (parity, source rank)
+  uint64_t seq;           // call sequence number (same on every rank)
+  uint64_t timeout_ns;
+  DeviceStatus* status;
+  uint32_t* doorbell;
+};
+cudaError_t LaunchOneShotKernel(const OneShotParams& p, const OneShotParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
+
+// ---- two-sided device messaging through the peer's mailbox ----
+struct P2pParams {
+  int32_t rank;
+  int32_t peer;
+  int32_t is_send;
+  int32_t world_size;
+  PeerTable peers;
+  const void* src;        // send: user buffer
+  void* dst;              // recv: user buffer
+  uint64_t bytes;
+  uint64_t mailbox_offset;  // byte offset of the mailbox area in the arena
+  uint64_t slot_bytes;      // bytes per mailbox slot
+  uint32_t slots;           // slots per source rank
+  uint32_t pad_;
+  uint64_t first_piece;     // cumulative piece counter of this pair at call start
+  uint64_t seq;
+  uint64_t timeout_ns;
+  DeviceStatus* status;
+  uint32_t* doorbell;
+};
+cudaError_t LaunchP2pKernel(const P2pParams& p, cudaStream_t stream);
+
+}  // namespace ibcomm

@@ -1,0 +1,225 @@
+// Two-shot allreduce in the NVSwitch (NVLS): every rank owns 1/world_size of
+// the message; for its shard it issues `multimem.ld_reduce` (the switch reads
+// the same address on every GPU and returns the sum), applies the scale, and
+// `multimem.st` (the switch writes the result to every GPU).  Per GPU that is
+// about S*(1+1/ws) bytes in each NVLink direction instead of the ring's
+// 2*S*(ws-1)/ws.  The reference has no counterpart (it has no intra-node
+// path, README.md:66).
+//
+// Buffers must be bound to a multicast object.  Buffers inside a symmetric
+// allocation are used in place; others are staged through the arena's pool
+// window by window inside this same kernel (copy in -> barrier -> reduce ->
+// barrier -> copy out), with the copies of CTA b on every rank covering
+// exactly what CTA b of the other ranks reduces, so the barriers are per CTA.
+#include <cooperative_groups.h>
+
+#include "flags.cuh"
+#include "ibcomm/communicator.h"
+#include "kernels.h"
+#include "vec_ops.cuh"
+
+namespace ibcomm {
+namespace dev {
+
+constexpr int kNvlsThreads = 512;
+
+template <typename T> struct Multimem;
+
+template <> struct Multimem<float> {
+  __device__ __forceinline__ static uint4 LdReduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+  __device__ __forceinline__ static void St(void* mc, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct Multimem<__half> {
+  __device__ __forceinline__ static uint4 LdReduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+  __device__ __forceinline__ static void St(void* mc, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  __device__ __forceinline__ static uint4 LdReduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+  __device__ __forceinline__ static void St(void* mc, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+
+// [*b, *e) = part `part` of `parts` of the range [lo, hi).
+__device__ __forceinline__ void SubRange(uint64_t lo, uint64_t hi, int part, int parts, uint64_t* b, uint64_t* e) {
+  const uint64_t len = hi - lo;
+  const uint64_t per = (len + static_cast<uint64_t>(parts) - 1) / static_cast<uint64_t>(parts);
+  uint64_t x = lo + per * static_cast<uint64_t>(part);
+  if (x > hi) x = hi;
+  uint64_t y = x + per;
+  if (y > hi) y = hi;
+  *b = x;
+  *e = y;
+}
+
+// Barrier between CTA `cta` of every rank.  Returns false when it gave up.
+__device__ inline bool CrossRankBarrier(const NvlsParams& p, const WaitCtx& w, int cta, uint32_t phase, int* s_stop) {
+  __syncthreads();
+  const uint64_t val = (p.seq << 32) | phase;
+  if (threadIdx.x < p.world_size && static_cast<int>(threadIdx.x) != p.rank) {
+    FenceSys();
+    StReleaseSys(&Ctl(p.peers, threadIdx.x)->bar[cta][p.rank], val);
+    if (!WaitGE(&Ctl(p.peers, p.rank)->bar[cta][threadIdx.x], val, w, kWaitBarrier, threadIdx.x, static_cast<int>(phase)))
+      *s_stop = 1;
+  }
+  __syncthreads();
+  return *s_stop == 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_constant__ NvlsParams p0, const NvlsParams* __restrict__ emu) {
+  using A = typename Acc<T>::type;
+  constexpr int kVecElems = 16 / static_cast<int>(sizeof(T));
+  __shared__ NvlsParams p;
+  __shared__ int s_stop;
+  {
+    const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y) : reinterpret_cast<const uint32_t*>(&p0);
+    for (unsigned i = threadIdx.x; i < sizeof(NvlsParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
+    if (threadIdx.x == 0) s_stop = 0;
+  }
+  __syncthreads();
+  const int cta = blockIdx.x, ncta = gridDim.x;
+  WaitCtx w;
+  w.peers = &p.peers;
+  w.status = p.status;
+  w.doorbell = p.doorbell;
+  w.seq = p.seq;
+  w.timeout_ns = p.timeout_ns;
+  w.rank = p.rank;
+  w.world_size = p.world_size;
+  w.channel = cta;
+
+  const T* sendbuf = static_cast<const T*>(p.sendbuf);
+  T* recvbuf = static_cast<T*>(p.recvbuf);
+  const bool do_scale = p.scale != 1.0;
+  uint32_t phase = 0;
+
+  for (uint64_t w0 = 0; w0 < p.len_elements; w0 += p.window_elems) {
+    const uint64_t wn = (p.len_elements - w0 < p.window_elems) ? p.len_elements - w0 : p.window_elems;
+    const uint64_t nvec = wn / kVecElems;  // whole 16-byte vectors in the window
+    const uint64_t tail0 = nvec * kVecElems;
+    const uint64_t win_bytes_off = p.stage_in ? 0 : w0 * sizeof(T);
+    const uint64_t wout_bytes_off = p.stage_out ? 0 : w0 * sizeof(T);
+
+    // (1) stage in: CTA `cta` copies part `cta` of every shard.
+    if (p.stage_in) {
+      const uint4* src = reinterpret_cast<const uint4*>(sendbuf + w0);
+      uint4* dst = reinterpret_cast<uint4*>(p.local_in);
+      for (int s = 0; s < p.world_size; ++s) {
+        uint64_t sb, se, b, e;
+        SubRange(0, nvec, s, p.world_size, &sb, &se);
+        SubRange(sb, se, cta, ncta, &b, &e);
+        for (uint64_t i = b + threadIdx.x; i < e; i += blockDim.x) St16(dst + i, Ld16(src + i));
+      }
+      if (cta == 0) {
+        T* dt = reinterpret_cast<T*>(p.local_in);
+        for (uint64_t i = tail0 + threadIdx.x; i < wn; i += blockDim.x) dt[i] = sendbuf[w0 + i];
+      }
+    }
+    if (!CrossRankBarrier(p, w, cta, ++phase, &s_stop)) return;
+
+    // (2) reduce my shard in the switch and broadcast it.
+    {
+      uint64_t sb, se, b, e;
+      SubRange(0, nvec, p.rank, p.world_size, &sb, &se);
+      SubRange(sb, se, cta, ncta, &b, &e);
+      const unsigned char* mi = p.mc_in + win_bytes_off;
+      unsigned char* mo = p.mc_out + wout_bytes_off;
+      constexpr int U = 4;
+      for (uint64_t i = b + threadIdx.x; i < e; i += static_cast<uint64_t>(blockDim.x) * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+          if (idx < e) v[u] = Multimem<T>::LdReduce(mi + idx * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+          if (idx < e) {
+            if (do_scale) {
+              A acc[kVecElems];
+              VecIO<T>::Load(v[u], acc);
+#pragma unroll
+              for (int k = 0; k < kVecElems; ++k) acc[k] = ScaleAcc<A>(acc[k], p.scale);
+              v[u] = VecIO<T>::Store(acc);
+            }
+            Multimem<T>::St(mo + idx * 16, v[u]);
+          }
+        }
+      }
+    }
+    // Ragged end (< 16 bytes): every rank sums it itself from the peers'
+    // windows, in rank order.  The value is written after the barrier, since
+    // with in-place buffers the peers are still reading this rank's input.
+    A tail_acc = A(0);
+    const bool has_tail = cta == 0 && tail0 + threadIdx.x < wn;
+    if (has_tail) {
+      const uint64_t i = tail0 + threadIdx.x;
+      for (int q = 0; q < p.world_size; ++q)
+        tail_acc += ToAcc<A, T>(LdScalarStrong<T>(reinterpret_cast<const T*>(p.peer_in[q] + win_bytes_off) + i));
+      if (do_scale) tail_acc = ScaleAcc<A>(tail_acc, p.scale);
+    }
+    if (!CrossRankBarrier(p, w, cta, ++phase, &s_stop)) return;
+    if (has_tail) {
+      const uint64_t i = tail0 + threadIdx.x;
+      if (p.stage_out) recvbuf[w0 + i] = FromAcc<T, A>(tail_acc);
+      else reinterpret_cast<T*>(p.local_out + wout_bytes_off)[i] = FromAcc<T, A>(tail_acc);
+    }
+
+    // (3) stage out.
+    if (p.stage_out) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.local_out);
+      uint4* dst = reinterpret_cast<uint4*>(recvbuf + w0);
+      for (int s = 0; s < p.world_size; ++s) {
+        uint64_t sb, se, b, e;
+        SubRange(0, nvec, s, p.world_size, &sb, &se);
+        SubRange(sb, se, cta, ncta, &b, &e);
+        for (uint64_t i = b + threadIdx.x; i < e; i += blockDim.x) St16(dst + i, Ld16Strong(src + i));
+      }
+    }
+  }
+}
+
+}  // namespace dev
+
+template <typename T>
+static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
+  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(emu != nullptr ? emu_ranks : 1));
+  if (emu != nullptr) {
+    void* args[] = {const_cast<NvlsParams*>(&p), &emu};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::NvlsKernel<T>), grid, dim3(dev::kNvlsThreads), args, 0, stream);
+  }
+  dev::NvlsKernel<T><<<grid, dev::kNvlsThreads, 0, stream>>>(p, nullptr);
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
+  switch (static_cast<DType>(p.dtype)) {
+    case DType::kFloat32: return LaunchNvlsTyped<float>(p, emu, emu_ranks, blocks, stream);
+    case DType::kFloat16: return LaunchNvlsTyped<__half>(p, emu, emu_ranks, blocks, stream);
+    case DType::kBFloat16: return LaunchNvlsTyped<__nv_bfloat16>(p, emu, emu_ranks, blocks, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace ibcomm

@@ -1,0 +1,105 @@
+// Algorithm and channel selection by message size.
+//
+// The defaults below come from bus-bandwidth sweeps on an 8 x B200 NVSwitch
+// box (bench.py --sweep); IBCOMM_TUNING_FILE replaces them with a table of
+// lines "world_size max_bytes algorithm channels" (first matching line wins,
+// max_bytes 0 = no limit), which bench.py --sweep --write-tuning produces.
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "ibcomm/device_context.h"
+
+namespace ibcomm {
+
+namespace {
+
+struct Rule {
+  int world_size;  // 0 = any
+  size_t max_bytes;  // 0 = unlimited
+  Algo algo;
+  int channels;  // 0 = derive from the size
+};
+
+std::vector<Rule> g_rules;
+std::once_flag g_once;
+
+void LoadRules() {
+  std::string path = env::ReadTuningFile();
+  if (path.empty()) return;
+  FILE* f = fopen(path.c_str(), "r");
+  if (f == nullptr) {
+    IBCOMM_WARN("cannot open IBCOMM_TUNING_FILE '%s'; using built-in tuning.\n", path.c_str());
+    return;
+  }
+  char line[256];
+  while (fgets(line, sizeof(line), f) != nullptr) {
+    if (line[0] == '#' || line[0] == '\n') continue;
+    int ws = 0, ch = 0;
+    unsigned long long mb = 0;
+    char name[64] = {0};
+    if (sscanf(line, "%d %llu %63s %d", &ws, &mb, name, &ch) != 4) continue;
+    std::string n = name;
+    Algo a;
+    if (n == "ring") a = Algo::kRing;
+    else if (n == "rabenseifner") a = Algo::kRabenseifner;
+    else if (n == "nvls") a = Algo::kNvls;
+    else if (n == "oneshot") a = Algo::kOneShot;
+    else continue;
+    g_rules.push_back(Rule{ws, static_cast<size_t>(mb), a, ch});
+  }
+  fclose(f);
+}
+
+}  // namespace
+
+int ChooseChannels(Algo algo, size_t bytes, int world_size, int max_channels) {
+  max_channels = std::max(1, std::min(max_channels, kMaxChannels));
+  int ch;
+  switch (algo) {
+    case Algo::kOneShot:
+      // One CTA per 32 KiB keeps the flag fan-out small at the latency end.
+      ch = static_cast<int>(std::min<size_t>(16, (bytes + (32u << 10) - 1) / (32u << 10)));
+      break;
+    case Algo::kNvls:
+      // The switch does the math; enough CTAs to keep ~8 MiB in flight.
+      ch = static_cast<int>(std::min<size_t>(64, std::max<size_t>(1, bytes / (128u << 10))));
+      break;
+    default: {
+      // Ring / Rabenseifner: a chunk is bytes / (4 * ws); give every channel
+      // at least 16 KiB of it per step.
+      size_t chunk = bytes / static_cast<size_t>(4 * std::max(1, world_size));
+      ch = static_cast<int>(std::min<size_t>(64, std::max<size_t>(1, chunk / (16u << 10))));
+      break;
+    }
+  }
+  return std::max(1, std::min(ch, max_channels));
+}
+
+TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, bool zero_copy, int max_channels) {
+  std::call_once(g_once, LoadRules);
+  for (const Rule& r : g_rules) {
+    if (r.world_size != 0 && r.world_size != world_size) continue;
+    if (r.max_bytes != 0 && bytes > r.max_bytes) continue;
+    if (r.algo == Algo::kNvls && !nvls_available) continue;
+    int ch = r.channels > 0 ? std::min(r.channels, max_channels) : ChooseChannels(r.algo, bytes, world_size, max_channels);
+    return TunerChoice{r.algo, ch};
+  }
+  (void)zero_copy;
+  Algo a;
+  if (bytes <= (256u << 10)) {
+    a = Algo::kOneShot;
+  } else if (nvls_available) {
+    a = Algo::kNvls;
+  } else if (bytes <= (8u << 20) && util::GetExpOfTwo(static_cast<uint64_t>(world_size)) != 0) {
+    a = Algo::kRabenseifner;
+  } else {
+    a = Algo::kRing;
+  }
+  return TunerChoice{a, ChooseChannels(a, bytes, world_size, max_channels)};
+}
+
+}  // namespace ibcomm

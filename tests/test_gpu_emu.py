@@ -1,0 +1,230 @@
+"""Device kernels on one GPU: N ranks emulated in one cooperative launch
+(EmuWorld).  Every result is compared with a plain PyTorch reference of the same
+operation computed in fp64 (fp32 for integer types is exact anyway)."""
+import pytest
+import torch
+
+import allreduce_proto_b200 as ar
+
+pytestmark = pytest.mark.gpu
+
+_worlds = {}
+
+
+def world(ws, pool=0, work=0):
+    key = (ws, pool, work)
+    if key not in _worlds:
+        _worlds[key] = ar.EmuWorld(ws, pool, work)
+    return _worlds[key]
+
+
+def make_inputs(ws, n, dtype, seed=0):
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    if dtype in (torch.int32, torch.int64):
+        return [torch.randint(-1000, 1000, (n,), device="cuda", dtype=dtype, generator=g) for _ in range(ws)]
+    return [(torch.rand(n, device="cuda", generator=g) * 2 - 1).to(dtype) for _ in range(ws)]
+
+
+def reference(ins, scale, dtype):
+    acc = torch.stack([t.double() for t in ins]).sum(0) * scale
+    return acc
+
+
+def tolerance(dtype, ws, wire=None):
+    if dtype in (torch.int32, torch.int64):
+        return 0.0, 0.0
+    if dtype == torch.float64:
+        return 1e-12, 1e-12
+    if dtype == torch.float32 and wire is None:
+        return 1e-6 * ws, 1e-6 * ws
+    return 2e-2, 2e-2 * ws  # 16-bit storage or wire
+
+
+def check(outs, want, dtype, ws, wire=None):
+    rtol, atol = tolerance(dtype, ws, wire)
+    for r, o in enumerate(outs):
+        if dtype in (torch.int32, torch.int64):
+            assert torch.equal(o.double(), want), f"rank {r}"
+        else:
+            torch.testing.assert_close(o.double(), want, rtol=rtol, atol=atol, msg=lambda m: f"rank {r}: {m}")
+
+
+def test_native_library_is_loaded():
+    world(2)
+    with open("/proc/self/maps") as f:
+        assert "libibcomm_cuda.so" in f.read()
+
+
+@pytest.mark.parametrize("algo", ["ring", "rabenseifner"])
+@pytest.mark.parametrize("ws", [2, 3, 4, 5, 6, 7, 8])
+def test_program_algorithms_all_world_sizes(algo, ws):
+    w = world(ws)
+    for n in (ws, 2 * ws, 2521, 65536 + 3, 1 << 20):
+        ins = make_inputs(ws, n, torch.float32, seed=n)
+        outs = [torch.full((n,), float("nan"), device="cuda") for _ in range(ws)]
+        w.allreduce(ins, outs, algo=algo)
+        check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.int32, torch.int64, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("algo", ["ring", "rabenseifner", "oneshot"])
+def test_dtypes(algo, dtype):
+    ws = 4
+    w = world(ws)
+    for n in (1000, 32768):
+        ins = make_inputs(ws, n, dtype, seed=7)
+        outs = [torch.zeros(n, device="cuda", dtype=dtype) for _ in range(ws)]
+        w.allreduce(ins, outs, algo=algo)
+        want = reference(ins, 1.0, dtype)
+        if dtype in (torch.float16, torch.bfloat16):
+            want = want.to(dtype).double() if algo == "oneshot" else want
+        check(outs, want, dtype, ws)
+
+
+@pytest.mark.parametrize("algo", ["ring", "rabenseifner", "oneshot"])
+def test_scale_and_in_place(algo):
+    ws = 8
+    w = world(ws)
+    n = 40000
+    ins = make_inputs(ws, n, torch.float32, seed=3)
+    want = reference(ins, 1.0 / ws, torch.float32)
+    bufs = [t.clone() for t in ins]
+    w.allreduce(bufs, None, algo=algo, scale=1.0 / ws)  # in place
+    check(bufs, want, torch.float32, ws)
+
+
+@pytest.mark.parametrize("algo", ["ring", "rabenseifner"])
+@pytest.mark.parametrize("wire", [torch.bfloat16, torch.float16])
+def test_wire_compression(algo, wire):
+    ws = 4
+    w = world(ws)
+    n = 1 << 18
+    ins = make_inputs(ws, n, torch.float32, seed=11)
+    outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+    w.allreduce(ins, outs, algo=algo, wire=wire, scale=0.25)
+    check(outs, reference(ins, 0.25, torch.float32), torch.float32, ws, wire=wire)
+    # every rank must hold the same bits
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+
+
+@pytest.mark.parametrize("algo", ["ring", "rabenseifner"])
+def test_small_staging_forces_slot_reuse(algo):
+    # 1 MiB pool / work region with an 8 MiB message: chunks are cut to fit and
+    # every staging slot is reused many times (credits).
+    ws = 4
+    w = world(ws, 1 << 20, 1 << 20)
+    n = 2 << 20
+    ins = make_inputs(ws, n, torch.float32, seed=5)
+    outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+    for channels in (1, 3, 8):
+        w.allreduce(ins, outs, algo=algo, channels=channels)
+        check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+
+
+def test_unaligned_buffers_take_the_scalar_path():
+    ws = 3
+    w = world(ws)
+    n = 5000
+    base = make_inputs(ws, n + 1, torch.float32, seed=9)
+    ins = [t[1:] for t in base]  # 4-byte aligned only
+    outs_base = [torch.zeros(n + 3, device="cuda") for _ in range(ws)]
+    outs = [t[3:] for t in outs_base]
+    for algo in ("ring", "rabenseifner", "oneshot"):
+        w.allreduce(ins, outs, algo=algo)
+        check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+
+
+def test_repeated_calls_mixed_algorithms():
+    ws = 8
+    w = world(ws)
+    n = 100000
+    ins = make_inputs(ws, n, torch.float32, seed=1)
+    outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+    want = reference(ins, 1.0, torch.float32)
+    for it in range(30):
+        algo = ("ring", "oneshot", "rabenseifner")[it % 3]
+        w.allreduce(ins, outs, algo=algo, sync=False)
+    torch.cuda.synchronize()
+    check(outs, want, torch.float32, ws)
+
+
+def test_error_codes():
+    w = world(2)
+    a = [torch.zeros(1, device="cuda") for _ in range(2)]
+    with pytest.raises(ar.IbcommError) as e:
+        w.allreduce(a, None, algo="ring")
+    assert e.value.code == ar.NOT_SUPPORTED  # fewer elements than ranks
+    big = [torch.zeros(1 << 20, device="cuda") for _ in range(2)]
+    with pytest.raises(ar.IbcommError) as e:
+        w.allreduce(big, None, algo="oneshot")
+    assert e.value.code == ar.INVALID_ARGUMENT  # beyond the one-shot slot
+    with pytest.raises(ar.IbcommError) as e:
+        w.allreduce(big, None, algo="nvls")
+    assert e.value.code == ar.NOT_SUPPORTED
+
+
+def test_bounded_wait_reports_timeout():
+    # One rank does not take part: the others' waits run out after the limit,
+    # the kernel returns, the status says who was missing, and the world stays usable.
+    ws = 4
+    w = ar.EmuWorld(ws, 1 << 20, 1 << 20)
+    w.set_timeout_ms(200)
+    n = 4096
+    ins = make_inputs(ws, n, torch.float32)
+    outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+    w.set_silent_rank(2)
+    with pytest.raises(ar.IbcommError) as e:
+        w.allreduce(ins, outs, algo="ring")
+    assert e.value.code == ar.TRANSPORT_ERROR
+    st = w.last_status()
+    assert st["code"] in (1, 2) and st["kind"] == 1  # timeout (or peer abort) at the entry barrier
+    w.set_silent_rank(-1)
+    w.set_timeout_ms(5000)
+    w.allreduce(ins, outs, algo="ring")
+    check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+
+
+def test_world_size_one_copy_scale_kernel():
+    comm = ar.Communicator(1, 0)
+    for n in (1, 5, 4096, (1 << 20) + 7):
+        x = torch.randn(n, device="cuda")
+        y = torch.empty_like(x)
+        comm.allreduce(x, y, scale=0.5, sync=True)
+        torch.testing.assert_close(y, x * 0.5)
+    x = torch.randn(100003, device="cuda")
+    for out_dtype in (torch.bfloat16, torch.float16):
+        y = ar.ops.copy_scale(x, scale=2.0, out_dtype=out_dtype)
+        torch.testing.assert_close(y, (x * 2.0).to(out_dtype))
+    z = ar.ops.copy_scale(x[1:], scale=3.0)  # unaligned -> plain kernel
+    torch.testing.assert_close(z, x[1:] * 3.0)
+
+
+def test_gradient_buckets_single_process():
+    from allreduce_proto_b200.models import resnet50_param_shapes, synthetic_grads
+    shapes = [s for _, s in resnet50_param_shapes()]
+    comm = ar.Communicator(1, 0)
+    buckets = ar.GradientBuckets(shapes, comm=comm, bucket_bytes=25 << 20)
+    assert buckets.num_buckets == 5
+    grads = synthetic_grads("cuda")
+    buckets.load(grads)
+    buckets.allreduce(average=True, sync=True)
+    for v, g in zip(buckets.views, grads):
+        torch.testing.assert_close(v, g)
+
+
+def test_tester_binary_emulated(bins):
+    import subprocess
+    for algo in ("ring", "rabenseifner"):
+        for np_ in (2, 3, 4, 5, 8):
+            p = subprocess.run([bins["allreduce_tester"], "--emulate", str(np_), algo, "64k", "i*np+p", "i*np*np+np*(np-1)/2"],
+                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+            assert p.returncode == 0, p.stderr
+    # chunk-size validation and short vectors exit with the reference's codes
+    import os
+    env = dict(os.environ, IBCOMM_CHUNKSIZE="3")
+    p = subprocess.run([bins["allreduce_tester"], "--emulate", "4", "ring", "1k", "1", "np"], env=env, stderr=subprocess.PIPE)
+    assert p.returncode == 1
+    p = subprocess.run([bins["allreduce_tester"], "--emulate", "2", "ring", "4", "1", "np"], stderr=subprocess.PIPE)
+    assert p.returncode == 4

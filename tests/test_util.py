@@ -1,0 +1,81 @@
+"""Host utilities: the C++ unit-test binary (size parser tables, power-of-two
+gate, partitioner, expression compiler, error policy — the reference's
+tests/unittest.cpp cases and more) and the same functions through the Python
+package."""
+import subprocess
+
+import pytest
+
+import allreduce_proto_b200 as ar
+from allreduce_proto_b200 import utils
+
+
+def test_cpp_unittest_binary(bins):
+    p = subprocess.run([bins["unittest"]], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert p.returncode == 0, p.stdout
+
+
+def test_parse_number_tables():
+    for sign in ("", "-", "+"):
+        for suffix in ("", "b", "B", "k", "kb", "K", "m", "mb", "M", "g", "gb", "G"):
+            assert utils.parse_number(f"{sign}0{suffix}") == 0
+    assert utils.parse_number("1k") == 1024
+    assert utils.parse_number("31kb") == 31 * 1024
+    assert utils.parse_number("713m") == 713 * 1024 * 1024
+    assert utils.parse_number("128M") == 128 << 20
+    for bad in ("0.5", "a", "b", "B", "0x", "97MiB", ""):
+        with pytest.raises(ValueError):
+            utils.parse_number(bad)
+
+
+def test_get_exp_of_two():
+    assert [utils.get_exp_of_two(n) for n in (0, 1, 2, 128, 127, 129)] == [0, 0, 1, 7, 0, 0]
+
+
+def test_split_buffer_and_blocks():
+    r = utils.split_buffer(1000, 4, 4)
+    assert len(r) == 16 and r[0] == (0, 63) and r[-1][1] == 1000
+    assert all(r[i][0] == r[i - 1][1] for i in range(1, len(r)))
+    assert len(utils.split_buffer(4, 4, 2)) == 4  # empty tail ranges dropped
+    assert utils.rank_to_chunk(16, 4, 1) == [4, 5, 6, 7]
+    assert [len(utils.rank_to_chunk(10, 4, r)) for r in range(4)] == [3, 3, 2, 2]
+
+
+def test_split_buffer_error_codes():
+    def code(*a):
+        try:
+            utils.split_buffer(*a)
+        except ar.IbcommError as e:
+            return e.code
+        return 0
+    assert code(1, 4, 2) == ar.NOT_SUPPORTED            # shorter than the world size
+    assert code(256, 4, 4, 3) == ar.INVALID_ARGUMENT    # not a multiple of sizeof(T)
+    assert code(256, 4, 4, 1024) == ar.INVALID_ARGUMENT  # fewer than 2 * ws chunks
+    assert code(256, 4, 4, 128) == 0
+    assert code(1, 4, 2, 3) == ar.NOT_SUPPORTED         # the length is checked first
+
+
+def test_ring_program_shape():
+    # rank 1 of 4: first op sends its own block's highest chunk from sendbuf;
+    # every op that stores locally with a remote store too is a forward.
+    ops = utils.describe_program("ring", 1, 4, 4096)
+    assert ops[0].startswith("[1792+256] a=send")
+    assert sum("remote" in o for o in ops) == sum(1 for o in ops) - 4  # last all-gather block is not forwarded
+    # Rabenseifner on 3 ranks folds ranks 0 and 1: rank 0 ends by receiving everything.
+    ops0 = utils.describe_program("rabenseifner", 0, 3, 4096)
+    assert "remote" not in ops0[-1] and "local" in ops0[-1]
+
+
+def test_bandwidth_helpers():
+    assert utils.busbw_gbs(1 << 30, 1.0, 8) == pytest.approx((1 << 30) / 1e9 * 1.75)
+    assert utils.busbw_gbs(1 << 30, 1.0, 1) == pytest.approx((1 << 30) / 1e9)
+    assert utils.ring_bytes_per_gpu(256 << 20, 8) == pytest.approx(2 * (256 << 20) * 7 / 8)
+    assert utils.nvls_bytes_per_gpu(256 << 20, 8) == pytest.approx((256 << 20) * 1.125)
+
+
+def test_resnet50_shapes():
+    from allreduce_proto_b200.models import resnet50_num_params, resnet50_param_shapes
+    assert resnet50_num_params() == 25_557_032
+    assert len(resnet50_param_shapes()) == 161
+    plan = ar.plan_buckets([100, 200, 50, 1000], 4, 1024)
+    assert plan == [[0], [1, 2], [3]]
