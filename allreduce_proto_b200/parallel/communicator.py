@@ -239,7 +239,7 @@ class Communicator:
         w = dtype_code(wire) if wire is not None else d
         s = stream if stream is not None else torch.cuda.current_stream(sendbuf.device)
         check(lib.ibcomm_allreduce_cuda(self._h, ALGO_CODES[algo], d, _ptr(sendbuf), _ptr(recvbuf), sendbuf.numel(),
-                                        float(scale), w, C.c_void_p(s.cuda_stream), 0 if sync else 1))
+                                        float(scale), w, C.c_void_p(s.cuda_stream), 2 | (0 if sync else 1)))
         return recvbuf
 
     def check(self) -> None:

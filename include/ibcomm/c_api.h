@@ -42,11 +42,15 @@ int ibcomm_barrier(ibcomm_comm* c);
 
 /* Host buffers: algo 1 (ring) or 2 (rabenseifner). */
 int ibcomm_allreduce_host(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t len_elements);
-/* Device buffers.  stream = 0 uses the communicator's stream.  With async = 0
- * the call returns when the result is in recvbuf; with async = 1 it only
- * enqueues, and ibcomm_check() reports a failure after the caller synchronised. */
+/* Device buffers.  flags: bit 0 (IBCOMM_ASYNC) = only enqueue (ibcomm_check()
+ * reports a failure after the caller synchronised), otherwise the call returns
+ * when the result is in recvbuf; bit 1 (IBCOMM_USE_STREAM) = run on `stream`
+ * taken literally (so the null stream can be named), otherwise on the
+ * communicator's own stream. */
+#define IBCOMM_ASYNC 1
+#define IBCOMM_USE_STREAM 2
 int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t len_elements,
-                          double scale, int wire_dtype, void* stream, int async);
+                          double scale, int wire_dtype, void* stream, int flags);
 int ibcomm_check(ibcomm_comm* c);
 
 /* Peer-mapped (and, with NVSwitch multicast, switch-reducible) device memory.

@@ -66,9 +66,14 @@ struct CudaAllreduceOptions {
   // fp32 buffers may travel as bf16/fp16 on the wire (accumulation stays
   // fp32).  kFloat32 means "no compression".
   DType wire = DType::kFloat32;
-  // 0 = the communicator's own stream; the call then blocks until the result
-  // is in recvbuf (reference behaviour).  Non-zero = enqueue only.
+  // The CUDA stream to run on.  With use_stream == false the communicator's
+  // own stream is used (it synchronises with the legacy default stream).
+  // use_stream == true takes `stream` literally, so the null stream can be
+  // named too.
   void* stream = nullptr;
+  bool use_stream = false;
+  // false: the call returns when the result is in recvbuf (reference
+  // behaviour).  true: the call only enqueues.
   bool async = false;
 };
 

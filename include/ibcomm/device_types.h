@@ -79,6 +79,9 @@ enum OpFlags : uint8_t {
   kOpScale = 1,        // multiply by ExecParams::scale before storing
   kOpStoreLocal = 2,   // store to recvbuf[range]
   kOpStoreRemote = 4,  // store to peer_out's staging slot
+  // The value is final: round it through the wire type before the local store,
+  // so that the owner keeps the same bits every other rank will receive.
+  kOpRoundWire = 8,
 };
 
 struct Op {

@@ -209,7 +209,7 @@ size_t MulticastGroup::Granularity(int num_devices, size_t bytes) {
   if (!drv::HasMulticastApi()) return 0;
   CUmulticastObjectProp p = McProp(num_devices, bytes);
   size_t g = 0;
-  if (drv::Get()->MulticastGetGranularity(&g, &p, CU_MULTICAST_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS) return 0;
+  if (drv::Get()->MulticastGetGranularity(&g, &p, CU_MULTICAST_GRANULARITY_MINIMUM) != CUDA_SUCCESS) return 0;
   return g;
 }
 
@@ -224,6 +224,7 @@ int MulticastGroup::CreateRoot(size_t bytes, int num_devices) {
   }
   have_handle_ = true;
   bytes_ = bytes;
+  num_devices_ = num_devices;
   int fd = -1;
   r = api->MemExportToShareableHandle(&fd, mc_, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
   if (r != CUDA_SUCCESS) {
@@ -234,7 +235,8 @@ int MulticastGroup::CreateRoot(size_t bytes, int num_devices) {
   return fd;
 }
 
-void MulticastGroup::Import(int fd, size_t bytes) {
+void MulticastGroup::Import(int fd, size_t bytes, int num_devices) {
+  num_devices_ = num_devices;
   const drv::Api* api = drv::Get();
   CUCHECK(api->MemImportFromShareableHandle(&mc_, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
                                             CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
@@ -256,7 +258,9 @@ void MulticastGroup::BindAndMap(const SharedAllocation& mem, int device) {
   CUCHECK(api->MulticastBindMem(mc_, 0, mem.handle(), 0, bytes_, 0));
   bound_ = true;
   CUdeviceptr va = 0;
-  CUCHECK(api->MemAddressReserve(&va, bytes_, 2u << 20, 0, 0));
+  size_t gran = Granularity(num_devices_, bytes_);
+  if (gran < (2u << 20)) gran = 2u << 20;
+  CUCHECK(api->MemAddressReserve(&va, bytes_, gran, 0, 0));
   CUCHECK(api->MemMap(va, bytes_, 0, mc_, 0));
   CUmemAccessDesc desc;
   memset(&desc, 0, sizeof(desc));

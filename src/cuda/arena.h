@@ -80,7 +80,7 @@ class MulticastGroup {
   // Root: creates the object; returns the descriptor to hand to the peers.
   int CreateRoot(size_t bytes, int num_devices);
   // Others: adopt the root's object.
-  void Import(int fd, size_t bytes);
+  void Import(int fd, size_t bytes, int num_devices);
   void AddDevice(int device);
   // After EVERY rank has added its device: bind my memory, map the alias.
   void BindAndMap(const SharedAllocation& mem, int device);
@@ -93,6 +93,7 @@ class MulticastGroup {
   bool have_handle_ = false;
   bool bound_ = false;
   int device_ = -1;
+  int num_devices_ = 1;
   size_t bytes_ = 0;
   unsigned char* ptr_ = nullptr;
 };

@@ -92,6 +92,9 @@ class DeviceContext {
   int device_ = 0;
   int rank_ = 0, ws_ = 1;
   cudaStream_t stream_ = nullptr;
+  // Send and receive kernels of one rank must be able to run side by side
+  // (each waits for a kernel on ANOTHER GPU), hence one stream per direction.
+  cudaStream_t send_stream_ = nullptr, recv_stream_ = nullptr;
   cudaEvent_t last_done_ = nullptr;
   cudaStream_t last_stream_ = nullptr;
   bool have_last_ = false;
@@ -135,7 +138,11 @@ DeviceContext::DeviceContext(Communicator* comm) : comm_(comm) {
   if (ws_ > kMaxRanks) IBCOMM_FAIL(NOT_SUPPORTED, "Device collectives support up to %d ranks (got %d).\n", kMaxRanks, ws_);
   max_channels_ = std::min(env::ReadNumCudaStream(), kMaxChannels);
   layout_ = MakeArenaLayout(env::ReadPreAllocSize(), env::ReadWorkGpuMemorySize());
-  CUDACHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+  // A blocking stream: work the caller queued on the legacy default stream is
+  // ordered before the collectives issued here, and vice versa.
+  CUDACHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamDefault));
+  CUDACHECK(cudaStreamCreateWithFlags(&send_stream_, cudaStreamDefault));
+  CUDACHECK(cudaStreamCreateWithFlags(&recv_stream_, cudaStreamDefault));
   CUDACHECK(cudaEventCreateWithFlags(&last_done_, cudaEventDisableTiming));
   multicast_local_ok_ = !env::ReadDisableNvls() && ws_ > 1 && MulticastGroup::Supported(device_);
   size_t align = 0;
@@ -175,6 +182,8 @@ DeviceContext::~DeviceContext() {
   if (d_trace_) cudaFree(d_trace_);
   if (last_done_) cudaEventDestroy(last_done_);
   if (stream_) cudaStreamDestroy(stream_);
+  if (send_stream_) cudaStreamDestroy(send_stream_);
+  if (recv_stream_) cudaStreamDestroy(recv_stream_);
   (void)cudaGetLastError();
 }
 
@@ -262,7 +271,7 @@ void DeviceContext::ExchangeAllocation(SharedAllocation* mine, std::vector<std::
     if (fd >= 0) close(fd);
   } else {
     int fd = fdch_[0]->Recv(&ok, sizeof(ok), timeout);
-    if (ok) group->Import(fd, mine->bytes());
+    if (ok) group->Import(fd, mine->bytes(), ws_);
   }
   if (!ok) {
     comm_->Barrier();
@@ -309,7 +318,7 @@ void DeviceContext::ConnectPeers() {
 
 // ---------------------------------------------------------------- streams
 cudaStream_t DeviceContext::StreamFor(const CudaAllreduceOptions& opts) {
-  return opts.stream != nullptr ? static_cast<cudaStream_t>(opts.stream) : stream_;
+  return (opts.use_stream || opts.stream != nullptr) ? static_cast<cudaStream_t>(opts.stream) : stream_;
 }
 
 void DeviceContext::OrderAfterPrevious(cudaStream_t stream) {
@@ -524,7 +533,7 @@ void DeviceContext::Send(int dest, const void* buf, size_t len) {
     return;
   }
   ConnectPeers();
-  OrderAfterPrevious(stream_);
+  OrderAfterPrevious(send_stream_);
   P2pParams p;
   memset(&p, 0, sizeof(p));
   p.rank = rank_;
@@ -544,10 +553,10 @@ void DeviceContext::Send(int dest, const void* buf, size_t len) {
   p.doorbell = rr_.d_doorbell;
   s.pieces_sent += (len + p.slot_bytes - 1) / p.slot_bytes;
   IBCOMM_TRACE(*tracer_, kTraceIssueSend);
-  CUDACHECK(LaunchP2pKernel(p, stream_));
+  CUDACHECK(LaunchP2pKernel(p, send_stream_));
   ++kernel_launches_;
   IBCOMM_TRACE(*tracer_, kTraceIssueSend);
-  CUDACHECK(cudaEventRecord(s.send_done, stream_));
+  CUDACHECK(cudaEventRecord(s.send_done, send_stream_));
 }
 
 void DeviceContext::Recv(int src, void* buf, size_t len) {
@@ -570,7 +579,7 @@ void DeviceContext::Recv(int src, void* buf, size_t len) {
     return;
   }
   ConnectPeers();
-  OrderAfterPrevious(stream_);
+  OrderAfterPrevious(recv_stream_);
   P2pParams p;
   memset(&p, 0, sizeof(p));
   p.rank = rank_;
@@ -590,10 +599,10 @@ void DeviceContext::Recv(int src, void* buf, size_t len) {
   p.doorbell = rr_.d_doorbell;
   s.pieces_received += (len + p.slot_bytes - 1) / p.slot_bytes;
   IBCOMM_TRACE(*tracer_, kTraceIssueRecv);
-  CUDACHECK(LaunchP2pKernel(p, stream_));
+  CUDACHECK(LaunchP2pKernel(p, recv_stream_));
   ++kernel_launches_;
   IBCOMM_TRACE(*tracer_, kTraceIssueRecv);
-  CUDACHECK(cudaEventRecord(s.recv_done, stream_));
+  CUDACHECK(cudaEventRecord(s.recv_done, recv_stream_));
 }
 
 bool DeviceContext::SendPoll(int dest) {

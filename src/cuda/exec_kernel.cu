@@ -37,7 +37,7 @@ struct ExecTraits {
 // are predicates on registers, not divergence.
 template <typename T, typename W>
 __device__ __forceinline__ void VecLoop(const uint4* __restrict__ a_base, bool a_is_stage, const uint4* __restrict__ b_base,
-                                        uint4* l_base, uint4* r_base, uint64_t npacks, bool do_scale, double scale) {
+                                        uint4* l_base, uint4* r_base, uint64_t npacks, bool do_scale, double scale, bool round_wire) {
   using Tr = ExecTraits<T, W>;
   using A = typename Tr::A;
   constexpr int P = Tr::P;
@@ -86,13 +86,22 @@ __device__ __forceinline__ void VecLoop(const uint4* __restrict__ a_base, bool a
 #pragma unroll
           for (int e = 0; e < P; ++e) acc[e] = ScaleAcc<A>(acc[e], scale);
         }
-        if (l_base != nullptr) {
+        uint4 wq[VW];
+        if (r_base != nullptr || round_wire) {
 #pragma unroll
-          for (int v = 0; v < VT; ++v) St16(l_base + idx * VT + v, VecIO<T>::Store(acc + v * VecIO<T>::kN));
+          for (int v = 0; v < VW; ++v) wq[v] = VecIO<W>::Store(acc + v * VecIO<W>::kN);
         }
         if (r_base != nullptr) {
 #pragma unroll
-          for (int v = 0; v < VW; ++v) St16(r_base + idx * VW + v, VecIO<W>::Store(acc + v * VecIO<W>::kN));
+          for (int v = 0; v < VW; ++v) St16(r_base + idx * VW + v, wq[v]);
+        }
+        if (l_base != nullptr) {
+          if (round_wire && sizeof(W) != sizeof(T)) {
+#pragma unroll
+            for (int v = 0; v < VW; ++v) VecIO<W>::Load(wq[v], acc + v * VecIO<W>::kN);
+          }
+#pragma unroll
+          for (int v = 0; v < VT; ++v) St16(l_base + idx * VT + v, VecIO<T>::Store(acc + v * VecIO<T>::kN));
         }
       }
     }
@@ -115,6 +124,7 @@ __device__ void ScalarLoop(const Op& op, const T* sendbuf, T* recvbuf, const W* 
     if (op.src_b == kSrcSend) v += ToAcc<A, T>(sendbuf[g]);
     else if (op.src_b == kSrcRecv) v += ToAcc<A, T>(recvbuf[g]);
     if (op.flags & kOpScale) v = ScaleAcc<A>(v, scale);
+    if ((op.flags & kOpRoundWire) && sizeof(W) != sizeof(T)) v = ToAcc<A, W>(FromAcc<W, A>(v));
     if (op.flags & kOpStoreLocal) recvbuf[g] = FromAcc<T, A>(v);
     if (op.flags & kOpStoreRemote) stage_out[k] = FromAcc<W, A>(v);
   }
@@ -158,7 +168,8 @@ __device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch) {
                                                    : nullptr;
     uint4* l_base = (op.flags & kOpStoreLocal) ? reinterpret_cast<uint4*>(recvbuf + g0) : nullptr;
     uint4* r_base = (op.flags & kOpStoreRemote) ? reinterpret_cast<uint4*>(stage_out + lo) : nullptr;
-    VecLoop<T, W>(a_base, a_is_stage, b_base, l_base, r_base, npacks, (op.flags & kOpScale) != 0, p.scale);
+    VecLoop<T, W>(a_base, a_is_stage, b_base, l_base, r_base, npacks, (op.flags & kOpScale) != 0, p.scale,
+                  (op.flags & kOpRoundWire) != 0);
   }
   const uint64_t done = lo + npacks * Tr::P;
   if (done < hi) ScalarLoop<T, W>(op, sendbuf, recvbuf, stage_in, stage_out, done, hi, p.scale);

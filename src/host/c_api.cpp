@@ -175,7 +175,7 @@ int ibcomm_allreduce_host(ibcomm_comm* c, int algo, int dtype, const void* sendb
 }
 
 int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t n, double scale,
-                          int wire_dtype, void* stream, int async) {
+                          int wire_dtype, void* stream, int flags) {
   return Guard([&] {
     NeedCuda();
 #ifdef USE_CUDA
@@ -184,10 +184,11 @@ int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendb
     o.scale = scale;
     o.wire = CheckDType(wire_dtype);
     o.stream = stream;
-    o.async = async != 0;
+    o.use_stream = (flags & IBCOMM_USE_STREAM) != 0;
+    o.async = (flags & IBCOMM_ASYNC) != 0;
     c->comm.AllreduceCuda(CheckDType(dtype), sendbuf, recvbuf, n, o);
 #else
-    (void)c; (void)algo; (void)dtype; (void)sendbuf; (void)recvbuf; (void)n; (void)scale; (void)wire_dtype; (void)stream; (void)async;
+    (void)c; (void)algo; (void)dtype; (void)sendbuf; (void)recvbuf; (void)n; (void)scale; (void)wire_dtype; (void)stream; (void)flags;
 #endif
   });
 }

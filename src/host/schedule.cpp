@@ -73,6 +73,7 @@ struct Builder {
     op.src_a = kSrcStage;
     op.src_b = add;
     if (store_local) op.flags |= kOpStoreLocal;
+    if (scale) op.flags |= kOpRoundWire;
     if (scale && req.apply_scale) op.flags |= kOpScale;
     AttachIn(&op, from);
     if (forward_to >= 0) AttachOut(&op, forward_to);

@@ -1,0 +1,180 @@
+"""Worker of the multi-GPU tests: one process per GPU, started by `ibcomm_run`
+(which sets IBCOMM_RANK / IBCOMM_WORLD_SIZE / IBCOMM_BOOTSTRAP_DIR).
+
+    ibcomm_run -np N python tests/multigpu_worker.py <case>
+
+Exit status 0 = the case passed on this rank."""
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import torch  # noqa: E402
+
+import allreduce_proto_b200 as ar  # noqa: E402
+
+RANK = int(os.environ.get("IBCOMM_RANK", "0"))
+WS = int(os.environ.get("IBCOMM_WORLD_SIZE", "1"))
+
+
+def seeded(n, dtype, r, seed=0):
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1000 * seed + r)
+    if dtype in (torch.int32, torch.int64):
+        return torch.randint(-1000, 1000, (n,), device="cuda", dtype=dtype, generator=g)
+    return (torch.rand(n, device="cuda", generator=g) * 2 - 1).to(dtype)
+
+
+def expected(n, dtype, scale, seed=0):
+    acc = torch.zeros(n, dtype=torch.float64, device="cuda")
+    for r in range(WS):
+        acc += seeded(n, dtype, r, seed).double()
+    return acc * scale
+
+
+def close(out, want, dtype, wire=None):
+    if dtype in (torch.int32, torch.int64):
+        return torch.equal(out.double(), want)
+    if dtype == torch.float64:
+        tol = 1e-12
+    elif dtype == torch.float32 and wire is None:
+        tol = 1e-6 * WS
+    else:
+        tol = 2e-2 * WS
+    return torch.allclose(out.double(), want, rtol=tol, atol=tol)
+
+
+def case_allreduce(comm):
+    info = comm.device_info(connect=True)
+    algos = ["ring", "rabenseifner", "oneshot", "auto"] + (["nvls"] if info["nvls"] else [])
+    for algo in algos:
+        for dtype in (torch.float32, torch.bfloat16, torch.int32):
+            if algo == "nvls" and dtype == torch.int32:
+                continue
+            for n in (WS, 1000, 65536, (1 << 20) + 5, 8 << 20):
+                if algo == "oneshot" and n * torch.empty((), dtype=dtype).element_size() > (256 << 10):
+                    continue
+                x = seeded(n, dtype, RANK, seed=n % 97)
+                y = torch.empty_like(x)
+                comm.allreduce(x, y, algo=algo, scale=0.5, sync=True)
+                if not close(y, expected(n, dtype, 0.5, seed=n % 97), dtype):
+                    print(f"rank {RANK}: {algo} {dtype} n={n} mismatch", file=sys.stderr)
+                    return 1
+    # in place + wire compression
+    x = seeded(1 << 20, torch.float32, RANK, seed=5)
+    comm.allreduce(x, algo="ring", wire=torch.bfloat16, sync=True)
+    if not close(x, expected(1 << 20, torch.float32, 1.0, seed=5), torch.float32, wire=torch.bfloat16):
+        return 1
+    return 0
+
+
+def case_symmetric(comm):
+    """Zero-copy buffers: symmetric memory, switch reduction when available."""
+    n = (4 << 20) + 3
+    a = comm.symmetric_empty(n, torch.float32)
+    b = comm.symmetric_empty(n, torch.float32)
+    for it in range(3):
+        a.copy_(seeded(n, torch.float32, RANK, seed=it))
+        comm.allreduce(a, b, scale=1.0 / WS, sync=True)
+        if not close(b, expected(n, torch.float32, 1.0 / WS, seed=it), torch.float32):
+            print(f"rank {RANK}: symmetric out-of-place mismatch", file=sys.stderr)
+            return 1
+        comm.allreduce(a, scale=1.0 / WS, sync=True)  # in place
+        if not close(a, expected(n, torch.float32, 1.0 / WS, seed=it), torch.float32):
+            print(f"rank {RANK}: symmetric in-place mismatch", file=sys.stderr)
+            return 1
+    h = comm.symmetric_empty(1 << 20, torch.bfloat16)
+    h.copy_(seeded(1 << 20, torch.bfloat16, RANK, seed=9))
+    comm.allreduce(h, sync=True)
+    if not close(h, expected(1 << 20, torch.bfloat16, 1.0, seed=9), torch.bfloat16):
+        return 1
+    return 0
+
+
+def case_sendrecv(comm):
+    """Device buffers through the mailbox kernels; ring of neighbours plus a broadcast."""
+    comm.device_info(connect=True)
+    to, frm = (RANK + 1) % WS, (RANK - 1) % WS
+    for nbytes in (4, 1000, 256 << 10, (3 << 20) + 17):
+        out = torch.full((nbytes,), RANK + 1, dtype=torch.uint8, device="cuda")
+        out[-1] = 77
+        inn = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        comm.send(to, out, blocking=False)
+        comm.recv(frm, inn, blocking=True)
+        comm.send_wait(to)
+        if int(inn[0]) != frm + 1 or int(inn[-1]) != 77:
+            print(f"rank {RANK}: sendrecv {nbytes} mismatch", file=sys.stderr)
+            return 1
+    t = torch.full((4096,), float(RANK), device="cuda")
+    comm.bcast(t, root=WS - 1)
+    if not torch.all(t == float(WS - 1)):
+        return 1
+    # host buffers still travel over the host transport
+    hs = torch.full((1000,), float(RANK))
+    hr = torch.zeros(1000)
+    comm.send(to, hs, blocking=False)
+    comm.recv(frm, hr, blocking=True)
+    comm.send_wait(to)
+    return 0 if torch.all(hr == float(frm)) else 1
+
+
+def case_buckets(comm):
+    from allreduce_proto_b200.models import resnet50_param_shapes, synthetic_grads
+    shapes = [s for _, s in resnet50_param_shapes()]
+    for dtype, wire in ((torch.float32, None), (torch.float32, torch.bfloat16), (torch.bfloat16, None)):
+        buckets = ar.GradientBuckets(shapes, dtype=dtype, comm=comm, bucket_bytes=25 << 20)
+        grads = synthetic_grads("cuda", dtype=dtype, seed=RANK)
+        buckets.load(grads)
+        buckets.allreduce(average=True, wire=wire, sync=True)
+        want = [torch.zeros(s, dtype=torch.float64, device="cuda") for s in shapes]
+        for r in range(WS):
+            for w, g in zip(want, synthetic_grads("cuda", dtype=dtype, seed=r)):
+                w += g.double()
+        tol = 1e-7 if (dtype == torch.float32 and wire is None) else 3e-5
+        for v, w in zip(buckets.views, want):
+            if not torch.allclose(v.double(), w / WS, rtol=2e-2 if tol > 1e-6 else 1e-5, atol=tol):
+                print(f"rank {RANK}: bucket mismatch {dtype} wire={wire}", file=sys.stderr)
+                return 1
+    return 0
+
+
+def case_leave(comm):
+    """Failure detection without faulting a GPU: after one good allreduce the
+    last rank leaves between steps; the others' next collective runs into its
+    wait limit, returns error code 2 and leaves the context usable."""
+    x = torch.ones(1 << 16, device="cuda")
+    comm.allreduce(x, algo="ring", sync=True)
+    if not torch.all(x == float(WS)):
+        return 1
+    if RANK == WS - 1:
+        torch.cuda.synchronize()
+        return 0
+    comm.set_timeout_ms(1000)
+    try:
+        comm.allreduce(x, algo="ring", sync=True)
+    except ar.IbcommError as e:
+        ok = e.code == ar.TRANSPORT_ERROR
+        y = torch.ones(16, device="cuda") * 2  # the context still works
+        return 0 if ok and float(y.sum()) == 32.0 else 1
+    return 1
+
+
+def main():
+    case = sys.argv[1]
+    ngpu = torch.cuda.device_count()
+    if ngpu < WS:
+        print(f"need {WS} GPUs, have {ngpu}", file=sys.stderr)
+        return 4
+    torch.cuda.set_device(RANK % ngpu)
+    comm = ar.Communicator.from_env()
+    rc = globals()[f"case_{case}"](comm)
+    torch.cuda.synchronize()
+    if case != "leave":
+        comm.barrier()
+    comm.close()
+    return rc
+
+
+if __name__ == "__main__":
+    sys.exit(main())

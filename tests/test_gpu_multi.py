@@ -1,0 +1,79 @@
+"""Multi-GPU tests: one process per GPU over real peer mappings (and NVSwitch
+multicast where the box has it).  Skipped on machines with one GPU, where the
+same kernels are covered by the emulated ranks of test_gpu_emu.py."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+WORKER = str(Path(__file__).resolve().parent / "multigpu_worker.py")
+NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+needs2 = pytest.mark.skipif(NGPU < 2, reason="needs at least two GPUs")
+
+
+def run(bins, np, case, env=None, timeout=300):
+    cmd = ["timeout", f"{timeout}s", bins["ibcomm_run"], "-np", str(np)]
+    for k, v in (env or {}).items():
+        cmd += ["-x", f"{k}={v}"]
+    cmd += [sys.executable, WORKER, case]
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    return p.returncode, p.stderr[-4000:]
+
+
+def world_sizes():
+    return [n for n in (2, 3, 4, 5, 6, 7, 8) if n <= NGPU]
+
+
+@needs2
+@pytest.mark.parametrize("np_", world_sizes())
+def test_allreduce_every_algorithm(bins, np_):
+    code, err = run(bins, np_, "allreduce")
+    assert code == 0, err
+
+
+@needs2
+@pytest.mark.parametrize("np_", [n for n in (2, 4, 8) if n <= NGPU])
+def test_symmetric_zero_copy(bins, np_):
+    code, err = run(bins, np_, "symmetric")
+    assert code == 0, err
+
+
+@needs2
+def test_without_multicast_and_with_ipc_handles(bins):
+    code, err = run(bins, 2, "allreduce", env={"IBCOMM_DISABLE_NVLS": "1"})
+    assert code == 0, err
+    code, err = run(bins, 2, "allreduce", env={"IBCOMM_ARENA_MODE": "ipc"})
+    assert code == 0, err
+
+
+@needs2
+def test_device_send_recv_bcast(bins):
+    code, err = run(bins, min(NGPU, 4), "sendrecv")
+    assert code == 0, err
+
+
+@needs2
+def test_resnet50_gradient_buckets(bins):
+    code, err = run(bins, min(NGPU, 8), "buckets")
+    assert code == 0, err
+
+
+@needs2
+def test_rank_leaving_is_detected(bins):
+    # NVLS off: a rank that exits while bound to a multicast object can raise
+    # NVLink faults on its peers; plain peer mappings do not.
+    code, err = run(bins, 2, "leave", env={"IBCOMM_DISABLE_NVLS": "1", "NCCL_NVLS_ENABLE": "0"})
+    assert code == 0, err
+
+
+@needs2
+def test_tester_binary_on_gpus(bins):
+    for algo in ("ring", "rabenseifner"):
+        cmd = ["timeout", "120s", bins["ibcomm_run"], "-np", "2", bins["allreduce_tester"], "--device", "cuda", algo, "128M",
+               "i*np+p", "i*np*np+np*(np-1)/2"]
+        p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        assert p.returncode == 0, p.stderr[-2000:]
