@@ -66,13 +66,13 @@ int ChooseChannels(Algo algo, size_t bytes, int world_size, int max_channels) {
       break;
     case Algo::kNvls:
       // The switch does the math; enough CTAs to keep ~8 MiB in flight.
-      ch = static_cast<int>(std::min<size_t>(64, std::max<size_t>(1, bytes / (128u << 10))));
+      ch = static_cast<int>(std::min<size_t>(kMaxChannels, std::max<size_t>(1, bytes / (128u << 10))));
       break;
     default: {
       // Ring / Rabenseifner: a chunk is bytes / (4 * ws); give every channel
       // at least 16 KiB of it per step.
       size_t chunk = bytes / static_cast<size_t>(4 * std::max(1, world_size));
-      ch = static_cast<int>(std::min<size_t>(64, std::max<size_t>(1, chunk / (16u << 10))));
+      ch = static_cast<int>(std::min<size_t>(kMaxChannels, std::max<size_t>(1, chunk / (16u << 10))));
       break;
     }
   }
@@ -92,7 +92,8 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
   Algo a;
   if (bytes <= (256u << 10)) {
     a = Algo::kOneShot;
-  } else if (nvls_available) {
+  } else if (nvls_available && world_size > 2) {
+    // Two ranks: the switch path moves 1.5 S per direction, the ring 1.0 S.
     a = Algo::kNvls;
   } else if (bytes <= (8u << 20) && util::GetExpOfTwo(static_cast<uint64_t>(world_size)) != 0) {
     a = Algo::kRabenseifner;

@@ -55,10 +55,11 @@ def case_allreduce(comm):
             for n in (WS, 1000, 65536, (1 << 20) + 5, 8 << 20):
                 if algo == "oneshot" and n * torch.empty((), dtype=dtype).element_size() > (256 << 10):
                     continue
+                scale = 1.0 if dtype == torch.int32 else 0.5
                 x = seeded(n, dtype, RANK, seed=n % 97)
                 y = torch.empty_like(x)
-                comm.allreduce(x, y, algo=algo, scale=0.5, sync=True)
-                if not close(y, expected(n, dtype, 0.5, seed=n % 97), dtype):
+                comm.allreduce(x, y, algo=algo, scale=scale, sync=True)
+                if not close(y, expected(n, dtype, scale, seed=n % 97), dtype):
                     print(f"rank {RANK}: {algo} {dtype} n={n} mismatch", file=sys.stderr)
                     return 1
     # in place + wire compression

@@ -139,7 +139,7 @@ def test_unaligned_buffers_take_the_scalar_path():
 def test_repeated_calls_mixed_algorithms():
     ws = 8
     w = world(ws)
-    n = 100000
+    n = 50000
     ins = make_inputs(ws, n, torch.float32, seed=1)
     outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
     want = reference(ins, 1.0, torch.float32)
