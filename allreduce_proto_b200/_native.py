@@ -61,6 +61,7 @@ def _declare(lib) -> None:
         "ibcomm_register_process": [vp, i, u32p, u32p],
         "ibcomm_register_myself": [vp, i],
         "ibcomm_set_timeout_ms": [vp, i],
+        "ibcomm_set_max_channels": [vp, i],
         "ibcomm_send": [vp, i, vp, sz, i],
         "ibcomm_recv": [vp, i, vp, sz, i],
         "ibcomm_send_poll": [vp, i, C.POINTER(i)],

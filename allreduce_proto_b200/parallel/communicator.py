@@ -100,6 +100,10 @@ class Communicator:
     def set_timeout_ms(self, ms: int) -> None:
         check(_native.lib().ibcomm_set_timeout_ms(self._h, ms))
 
+    def set_max_channels(self, channels: int) -> None:
+        """Caps the CTAs a collective may use (0 = IBCOMM_NUM_CUDA_STREAM)."""
+        check(_native.lib().ibcomm_set_max_channels(self._h, channels))
+
     def connect_with(self, exchange) -> None:
         """Full-mesh connection.  ``exchange(rank, infos)`` receives this rank's
         ``{dest: info}`` and must return ``{src: info addressed to this rank}``."""

@@ -30,6 +30,8 @@ int ibcomm_register_queue_pair(ibcomm_comm* c, int dest_rank, const uint32_t inf
 int ibcomm_register_process(ibcomm_comm* c, int dest_rank, const uint32_t info[3], uint32_t info_out[3]);
 int ibcomm_register_myself(ibcomm_comm* c, int my_rank);
 int ibcomm_set_timeout_ms(ibcomm_comm* c, int ms);
+/* Upper bound of channels (CTAs) per collective; 0 restores IBCOMM_NUM_CUDA_STREAM. */
+int ibcomm_set_max_channels(ibcomm_comm* c, int channels);
 
 int ibcomm_send(ibcomm_comm* c, int dest_rank, const void* buf, size_t len, int blocking);
 int ibcomm_recv(ibcomm_comm* c, int src_rank, void* buf, size_t len, int blocking);

@@ -63,6 +63,8 @@ struct DeviceInfo {
   uint64_t kernel_launches;  // kernels of this library launched so far
 };
 DeviceInfo DeviceContextInfo(DeviceContext* d);
+// Caps the channels a collective may use (0 = back to IBCOMM_NUM_CUDA_STREAM).
+void DeviceContextSetMaxChannels(DeviceContext* d, int channels);
 
 // Symmetric (peer-mapped, multicast-bound when possible) user memory.  Every
 // rank must call with the same size in the same order.  Buffers inside such

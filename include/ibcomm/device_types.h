@@ -112,11 +112,16 @@ struct StageLayout {
 };
 
 // Elements [*lo, *hi) of a `count`-element chunk that channel `c` of `nch`
-// handles.  Slices start on multiples of kSliceAlign elements so that a slice
-// is 16-byte aligned in every element type whenever its chunk is.
+// handles.  The cut depends only on the slot capacity (`slot_elems`, at least
+// the largest chunk), never on the chunk's own length: a staging slot is
+// reused by chunks of different lengths, and the credit a channel receives
+// covers exactly the byte range that channel owns in every slot.  Slices start
+// on multiples of kSliceAlign elements, so a slice is 16-byte aligned in every
+// element type whenever its chunk is.
 constexpr uint32_t kSliceAlign = 64;
-IBCOMM_HD inline void ChannelSlice(uint64_t count, int nch, int c, uint64_t* lo, uint64_t* hi) {
-  uint64_t per = (count + static_cast<uint64_t>(nch) - 1) / static_cast<uint64_t>(nch);
+IBCOMM_HD inline void ChannelSlice(uint64_t count, uint64_t slot_elems, int nch, int c, uint64_t* lo, uint64_t* hi) {
+  if (slot_elems < count) slot_elems = count;
+  uint64_t per = (slot_elems + static_cast<uint64_t>(nch) - 1) / static_cast<uint64_t>(nch);
   per = (per + kSliceAlign - 1) / kSliceAlign * kSliceAlign;
   uint64_t b = per * static_cast<uint64_t>(c);
   if (b > count) b = count;

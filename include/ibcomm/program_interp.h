@@ -91,7 +91,7 @@ class ProgramSimulator {
       for (size_t oi = 0; oi < pg.ops.size(); ++oi) {
         const Op& op = pg.ops[oi];
         uint64_t lo, hi;
-        ChannelSlice(op.elem_count, nch_, ch, &lo, &hi);
+        ChannelSlice(op.elem_count, st.slot_bytes / sizeof(T), nch_, ch, &lo, &hi);
         RankMem& me = mem[static_cast<size_t>(r)];
         if (op.wait_in != 0 &&
             !wait_for(me.inflag[static_cast<size_t>(ch * kMaxRanks + op.peer_in)], op.wait_in, "data", oi))

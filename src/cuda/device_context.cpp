@@ -64,6 +64,7 @@ class DeviceContext {
   void SymmetricFree_(void* ptr);
   void CollectTrace(Tracer* tracer);
   DeviceInfo Info() const;
+  void SetMaxChannels(int c) { max_channels_ = c > 0 ? std::min(c, kMaxChannels) : std::min(env::ReadNumCudaStream(), kMaxChannels); }
 
  private:
   struct P2pState {
@@ -730,6 +731,7 @@ void DeviceContextSendWait(DeviceContext* d, int dest) { d->SendWait(dest); }
 void DeviceContextRecvWait(DeviceContext* d, int src) { d->RecvWait(src); }
 void DeviceContextCollectTrace(DeviceContext* d, Tracer* tracer) { d->CollectTrace(tracer); }
 DeviceInfo DeviceContextInfo(DeviceContext* d) { return d->Info(); }
+void DeviceContextSetMaxChannels(DeviceContext* d, int channels) { d->SetMaxChannels(channels); }
 void DeviceContextCheck(DeviceContext* d) { d->Check(); }
 uint32_t DeviceContextPeekStatus(DeviceContext* d, DeviceStatus* out) { return d->Peek(out); }
 

@@ -15,6 +15,8 @@
 // as ONE cooperative launch (CTAs that wait on each other are co-resident).
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "flags.cuh"
 #include "ibcomm/communicator.h"
 #include "kernels.h"
@@ -134,7 +136,7 @@ template <typename T, typename W>
 __device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch) {
   using Tr = ExecTraits<T, W>;
   uint64_t lo, hi;
-  ChannelSlice(op.elem_count, nch, ch, &lo, &hi);
+  ChannelSlice(op.elem_count, p.stage.slot_bytes / sizeof(W), nch, ch, &lo, &hi);
   if (lo >= hi) return;
   const T* sendbuf = static_cast<const T*>(p.sendbuf);
   T* recvbuf = static_cast<T*>(p.recvbuf);
@@ -240,16 +242,26 @@ ExecKernel(const __grid_constant__ ExecParams p0, const ExecParams* __restrict__
 
 }  // namespace dev
 
+static int ExecThreads() {
+  static int threads = [] {
+    const char* s = getenv("IBCOMM_EXEC_THREADS");
+    int v = s ? atoi(s) : 0;
+    return (v >= 64 && v <= kExecThreads && v % 32 == 0) ? v : kExecThreads;
+  }();
+  return threads;
+}
+
 template <typename T, typename W>
 static cudaError_t Launch(const ExecParams& p, const ExecParams* emu, int emu_ranks, int channels, cudaStream_t stream) {
   dim3 grid(static_cast<unsigned>(channels), static_cast<unsigned>(emu != nullptr ? emu_ranks : 1));
+  const int kThreads = ExecThreads();
   if (emu != nullptr) {
     // Ranks sharing one GPU wait on each other inside this launch: it must be
     // cooperative so the runtime refuses a grid that cannot be co-resident.
     void* args[] = {const_cast<ExecParams*>(&p), &emu};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::ExecKernel<T, W>), grid, dim3(kExecThreads), args, 0, stream);
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::ExecKernel<T, W>), grid, dim3(kThreads), args, 0, stream);
   }
-  dev::ExecKernel<T, W><<<grid, kExecThreads, 0, stream>>>(p, nullptr);
+  dev::ExecKernel<T, W><<<grid, kThreads, 0, stream>>>(p, nullptr);
   return cudaGetLastError();
 }
 

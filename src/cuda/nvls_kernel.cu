@@ -13,6 +13,8 @@
 // exactly what CTA b of the other ranks reduces, so the barriers are per CTA.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "flags.cuh"
 #include "ibcomm/communicator.h"
 #include "kernels.h"
@@ -85,7 +87,7 @@ __device__ inline bool CrossRankBarrier(const NvlsParams& p, const WaitCtx& w, i
   return *s_stop == 0;
 }
 
-template <typename T>
+template <typename T, int U>
 __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_constant__ NvlsParams p0, const NvlsParams* __restrict__ emu) {
   using A = typename Acc<T>::type;
   constexpr int kVecElems = 16 / static_cast<int>(sizeof(T));
@@ -144,7 +146,6 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
       SubRange(sb, se, cta, ncta, &b, &e);
       const unsigned char* mi = p.mc_in + win_bytes_off;
       unsigned char* mo = p.mc_out + wout_bytes_off;
-      constexpr int U = 4;
       for (uint64_t i = b + threadIdx.x; i < e; i += static_cast<uint64_t>(blockDim.x) * U) {
         uint4 v[U];
 #pragma unroll
@@ -202,15 +203,31 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
 
 }  // namespace dev
 
-template <typename T>
-static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
+static int EnvInt(const char* name, int dflt) {
+  const char* s = getenv(name);
+  return s ? atoi(s) : dflt;
+}
+
+template <typename T, int U>
+static cudaError_t LaunchNvlsU(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, int threads, cudaStream_t stream) {
   dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(emu != nullptr ? emu_ranks : 1));
   if (emu != nullptr) {
     void* args[] = {const_cast<NvlsParams*>(&p), &emu};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::NvlsKernel<T>), grid, dim3(dev::kNvlsThreads), args, 0, stream);
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::NvlsKernel<T, U>), grid, dim3(threads), args, 0, stream);
   }
-  dev::NvlsKernel<T><<<grid, dev::kNvlsThreads, 0, stream>>>(p, nullptr);
+  dev::NvlsKernel<T, U><<<grid, threads, 0, stream>>>(p, nullptr);
   return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
+  // Tuning knobs for experiments: loads in flight per thread and CTA size.
+  static const int unroll = EnvInt("IBCOMM_NVLS_UNROLL", 4);
+  static const int threads_env = EnvInt("IBCOMM_NVLS_THREADS", dev::kNvlsThreads);
+  const int threads = (threads_env >= 64 && threads_env <= dev::kNvlsThreads && threads_env % 32 == 0) ? threads_env : dev::kNvlsThreads;
+  if (unroll == 8) return LaunchNvlsU<T, 8>(p, emu, emu_ranks, blocks, threads, stream);
+  if (unroll == 2) return LaunchNvlsU<T, 2>(p, emu, emu_ranks, blocks, threads, stream);
+  return LaunchNvlsU<T, 4>(p, emu, emu_ranks, blocks, threads, stream);
 }
 
 cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {

@@ -125,6 +125,18 @@ int ibcomm_set_timeout_ms(ibcomm_comm* c, int ms) {
   return Guard([&] { c->comm.SetTimeoutMs(ms); });
 }
 
+int ibcomm_set_max_channels(ibcomm_comm* c, int channels) {
+  return Guard([&] {
+    NeedCuda();
+#ifdef USE_CUDA
+    c->comm.PrepareMemoryPool();
+    ibcomm::DeviceContextSetMaxChannels(c->comm.device(), channels);
+#else
+    (void)c; (void)channels;
+#endif
+  });
+}
+
 int ibcomm_send(ibcomm_comm* c, int dest_rank, const void* buf, size_t len, int blocking) {
   return Guard([&] { c->comm.Send(dest_rank, buf, len, blocking != 0); });
 }

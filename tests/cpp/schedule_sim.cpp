@@ -84,6 +84,20 @@ MINI_TEST(ChannelsInPlaceScale) {
     }
 }
 
+MINI_TEST(SlotReuseWithSeveralChannels) {
+  // Small staging areas (every slot is reused many times), lengths that make
+  // the last chunk shorter than the others, several channels: the byte range
+  // a channel owns inside a slot must not depend on the chunk in it.
+  for (Algo a : {Algo::kRing, Algo::kRabenseifner})
+    for (int ws : {2, 3, 4, 5, 7, 8})
+      for (int nch : {2, 4, 5}) {
+        const size_t stage = 400000;
+        const size_t maxc = stage / (static_cast<size_t>(NumRegions(a, ws)) * 4) / 128 * 128;
+        CHECK_TRUE(RunCase<int>(a, ws, 100000, 0, stage, nch, false, 1.0, maxc));
+        CHECK_TRUE(RunCase<int>(a, ws, 10007, 0, 40000, nch, true, 1.0, 40000 / (static_cast<size_t>(NumRegions(a, ws)) * 4) / 128 * 128));
+      }
+}
+
 MINI_TEST(EnvChunkSizes) {
   for (int64_t chunk : {4, 8, 16, 32, 64, 128})
     CHECK_TRUE(RunCase<int>(Algo::kRing, 4, 256, chunk, size_t(1) << 16, 1, false, 1.0));

@@ -113,14 +113,16 @@ def test_wire_compression(algo, wire):
 def test_small_staging_forces_slot_reuse(algo):
     # 1 MiB pool / work region with an 8 MiB message: chunks are cut to fit and
     # every staging slot is reused many times (credits).
-    ws = 4
-    w = world(ws, 1 << 20, 1 << 20)
-    n = 2 << 20
-    ins = make_inputs(ws, n, torch.float32, seed=5)
-    outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
-    for channels in (1, 3, 8):
-        w.allreduce(ins, outs, algo=algo, channels=channels)
-        check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+    # Lengths that leave the last chunk shorter than the others: a slot then
+    # holds chunks of different lengths over time.
+    for ws in (4, 7):
+        w = world(ws, 1 << 20, 1 << 20)
+        for n in (2 << 20, (2 << 20) + 12345, 1000003):
+            ins = make_inputs(ws, n, torch.float32, seed=5)
+            outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+            for channels in (1, 3, 8):
+                w.allreduce(ins, outs, algo=algo, channels=channels)
+                check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
 
 
 def test_unaligned_buffers_take_the_scalar_path():
