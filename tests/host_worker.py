@@ -1,0 +1,95 @@
+"""Worker of the multi-process host tests (CPU only): started by `ibcomm_run`,
+uses the Python Communicator over the shared-memory transport.
+
+    ibcomm_run -np N python tests/host_worker.py <case>
+"""
+import os
+import sys
+import time
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+import allreduce_proto_b200 as ar  # noqa: E402
+
+RANK = int(os.environ.get("IBCOMM_RANK", "0"))
+WS = int(os.environ.get("IBCOMM_WORLD_SIZE", "1"))
+
+
+def case_allreduce(comm):
+    # configs of the headline plumbing test: 4 Mi fp32 elements, uniform[-1, 1) seeded by rank
+    n = 4_194_304
+    x = torch.from_numpy(np.random.default_rng(RANK).uniform(-1, 1, n).astype(np.float32))
+    want = np.zeros(n, dtype=np.float64)
+    for r in range(WS):
+        want += np.random.default_rng(r).uniform(-1, 1, n).astype(np.float32).astype(np.float64)
+    for algo in ("ring", "rabenseifner"):
+        y = torch.empty_like(x)
+        comm.allreduce(x, y, algo=algo)
+        if not np.allclose(y.numpy().astype(np.float64), want, rtol=1e-5, atol=1e-5):
+            print(f"rank {RANK}: {algo} mismatch", file=sys.stderr)
+            return 1
+    z = torch.arange(1000, dtype=torch.int64) + RANK
+    comm.allreduce(z, algo="ring")
+    if not torch.equal(z, torch.arange(1000, dtype=torch.int64) * WS + WS * (WS - 1) // 2):
+        return 1
+    d = torch.full((777,), 0.5 * (RANK + 1), dtype=torch.float64)
+    comm.allreduce(d, algo="rabenseifner", scale=2.0)
+    return 0 if torch.allclose(d, torch.full((777,), float(WS * (WS + 1) / 2), dtype=torch.float64)) else 1
+
+
+def case_messaging(comm):
+    to, frm = (RANK + 1) % WS, (RANK - 1) % WS
+    out = np.arange(100000, dtype=np.int32) + RANK
+    inn = np.zeros_like(out)
+    comm.send(to, out, blocking=False)
+    comm.recv(frm, inn, blocking=False)
+    while not comm.recv_poll(frm):
+        pass
+    comm.send_wait(to)
+    if not np.array_equal(inn, np.arange(100000, dtype=np.int32) + frm):
+        return 1
+    b = np.full(33, RANK, dtype=np.int64)
+    comm.bcast(b, root=1 % WS)
+    comm.barrier()
+    return 0 if np.all(b == 1 % WS) else 1
+
+
+def case_peer_exit(comm):
+    """The last rank exits without taking part; the others must fail with the
+    transport error code instead of hanging."""
+    if RANK == WS - 1:
+        return 0
+    comm.set_timeout_ms(1500)
+    x = torch.ones(1 << 16)
+    t0 = time.time()
+    try:
+        comm.allreduce(x, algo="ring")
+    except ar.IbcommError as e:
+        return 0 if e.code == ar.TRANSPORT_ERROR and time.time() - t0 < 20 else 1
+    return 1
+
+
+def case_trace(comm):
+    comm.set_timer_base()
+    x = torch.ones(1 << 12)
+    comm.allreduce(x)
+    comm.dump_trace()
+    return 0
+
+
+def main():
+    case = sys.argv[1]
+    comm = ar.Communicator.from_env()
+    rc = globals()[f"case_{case}"](comm)
+    if case != "peer_exit":
+        comm.barrier()
+    comm.close()
+    return rc
+
+
+if __name__ == "__main__":
+    sys.exit(main())
