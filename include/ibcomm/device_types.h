@@ -23,7 +23,7 @@
 namespace ibcomm {
 
 constexpr int kMaxRanks = 8;       // one NVSwitch box
-constexpr int kMaxChannels = 128;  // CTAs per rank a collective may use
+constexpr int kMaxChannels = 256;  // CTAs per rank a collective may use
 constexpr int kExecThreads = 512;  // threads per channel CTA
 
 // ---- control page at the start of every rank's arena (peer-writable) ----
@@ -99,8 +99,12 @@ struct Op {
   uint32_t wait_credit;  // wait until credit[ch][peer_out] >= base + wait_credit (0 = no wait)
   uint32_t post_out;     // then peer_out.inflag[ch][me] = base + post_out     (0 = no post)
   uint32_t post_credit;  // and  peer_in.credit[ch][me] = base + post_credit   (0 = no post)
-  uint64_t elem_begin;   // chunk range in elements of the message
+  uint64_t elem_begin;   // range in elements of the message
   uint64_t elem_count;
+  // First element of the slot-sized cell the range lies in (<= elem_begin).
+  // Staging offsets and the split among channels are relative to the cell, so
+  // an element keeps its channel and its place in a slot in every op.
+  uint64_t cell_begin;
 };
 
 // Geometry of the staging area a program runs in.
@@ -111,22 +115,25 @@ struct StageLayout {
   uint32_t regions;      // number of regions (= distinct in-peers)
 };
 
-// Elements [*lo, *hi) of a `count`-element chunk that channel `c` of `nch`
-// handles.  The cut depends only on the slot capacity (`slot_elems`, at least
-// the largest chunk), never on the chunk's own length: a staging slot is
-// reused by chunks of different lengths, and the credit a channel receives
-// covers exactly the byte range that channel owns in every slot.  Slices start
-// on multiples of kSliceAlign elements, so a slice is 16-byte aligned in every
-// element type whenever its chunk is.
+// Cell-relative elements [*lo, *hi) that channel `c` of `nch` handles of an op
+// that covers [first, first + count) of its cell.  The cut depends only on the
+// slot capacity (`slot_elems`), never on the op: a staging slot is reused by
+// ranges of different lengths, and the credit a channel receives covers
+// exactly the byte range that channel owns in every slot; likewise an element
+// is always handled by the same channel, whatever range an op names.  Slices
+// start on multiples of kSliceAlign elements, so a slice is 16-byte aligned in
+// every element type whenever its cell is.
 constexpr uint32_t kSliceAlign = 64;
-IBCOMM_HD inline void ChannelSlice(uint64_t count, uint64_t slot_elems, int nch, int c, uint64_t* lo, uint64_t* hi) {
-  if (slot_elems < count) slot_elems = count;
+IBCOMM_HD inline void ChannelSlice(uint64_t first, uint64_t count, uint64_t slot_elems, int nch, int c, uint64_t* lo,
+                                   uint64_t* hi) {
+  if (slot_elems < first + count) slot_elems = first + count;
   uint64_t per = (slot_elems + static_cast<uint64_t>(nch) - 1) / static_cast<uint64_t>(nch);
   per = (per + kSliceAlign - 1) / kSliceAlign * kSliceAlign;
   uint64_t b = per * static_cast<uint64_t>(c);
-  if (b > count) b = count;
   uint64_t e = b + per;
-  if (e > count) e = count;
+  if (b < first) b = first;
+  if (e > first + count) e = first + count;
+  if (b > e) b = e;
   *lo = b;
   *hi = e;
 }

@@ -25,8 +25,8 @@ struct SimResult {
 template <typename T>
 class ProgramSimulator {
  public:
-  ProgramSimulator(Algo algo, int world_size, size_t stage_bytes, int channels)
-      : algo_(algo), ws_(world_size), stage_bytes_(stage_bytes), nch_(channels) {}
+  ProgramSimulator(Algo algo, int world_size, size_t stage_bytes, int channels, size_t piece_elems = 0)
+      : algo_(algo), ws_(world_size), stage_bytes_(stage_bytes), nch_(channels), piece_elems_(piece_elems) {}
 
   // inputs[r] is rank r's send buffer; outputs[r] receives its result.
   // `in_place` makes every rank use one buffer for both.
@@ -40,6 +40,7 @@ class ProgramSimulator {
       q.rank = r;
       q.world_size = ws_;
       q.ranges = ranges;
+      q.piece_elems = piece_elems_;
       q.wire_elem_bytes = sizeof(T);
       q.stage_bytes = stage_bytes_;
       q.apply_scale = (scale != 1.0);
@@ -91,7 +92,7 @@ class ProgramSimulator {
       for (size_t oi = 0; oi < pg.ops.size(); ++oi) {
         const Op& op = pg.ops[oi];
         uint64_t lo, hi;
-        ChannelSlice(op.elem_count, st.slot_bytes / sizeof(T), nch_, ch, &lo, &hi);
+        ChannelSlice(op.elem_begin - op.cell_begin, op.elem_count, st.slot_bytes / sizeof(T), nch_, ch, &lo, &hi);
         RankMem& me = mem[static_cast<size_t>(r)];
         if (op.wait_in != 0 &&
             !wait_for(me.inflag[static_cast<size_t>(ch * kMaxRanks + op.peer_in)], op.wait_in, "data", oi))
@@ -107,7 +108,7 @@ class ProgramSimulator {
           stage_out = reinterpret_cast<T*>(mem[static_cast<size_t>(op.peer_out)].stage.data() +
                                            (static_cast<size_t>(op.region_out) * st.slots + op.slot_out) * st.slot_bytes);
         for (uint64_t k = lo; k < hi; ++k) {
-          const uint64_t g = op.elem_begin + k;
+          const uint64_t g = op.cell_begin + k;
           T v = op.src_a == kSrcStage ? stage_in[k] : (op.src_a == kSrcSend ? sendbuf[g] : recvbuf[g]);
           if (op.src_b == kSrcSend) v = static_cast<T>(v + sendbuf[g]);
           else if (op.src_b == kSrcRecv) v = static_cast<T>(v + recvbuf[g]);
@@ -141,6 +142,7 @@ class ProgramSimulator {
   int ws_;
   size_t stage_bytes_;
   int nch_;
+  size_t piece_elems_;
   std::vector<Program> programs_;
 };
 

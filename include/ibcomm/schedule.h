@@ -29,6 +29,11 @@ struct ProgramRequest {
   int rank = 0;
   int world_size = 1;
   std::vector<Range> ranges;      // pipeline chunks of the message, in elements
+  // Rabenseifner only: length of a transfer piece in elements.  0 = one piece
+  // per chunk.  A step moves a contiguous run of chunks, so with a piece
+  // length the run is cut into pieces of that length regardless of chunk
+  // boundaries (fewer, larger ops).  Must be the same on every rank.
+  size_t piece_elems = 0;
   size_t wire_elem_bytes = 4;     // element size in staging
   uint64_t stage_offset = 0;      // where the staging area starts in the arena
   uint64_t stage_bytes = 0;       // how large it is

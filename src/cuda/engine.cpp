@@ -1,5 +1,6 @@
 #include "engine.h"
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 
@@ -91,33 +92,48 @@ const CachedProgram& ProgramCache::Get(Algo algo, int rank, int world_size, size
   // Read at the point of use, like the reference: a bad value fails the call.
   const long long env_chunk = env::ReadChunkSize();
   const bool ring = algo == Algo::kRing;
-  const uint64_t stage_off = ring ? layout.pool_offset : layout.work_offset;
-  const uint64_t stage_bytes = ring ? layout.pool_bytes : layout.work_bytes;
+  // The ring stages in the pool.  Rabenseifner lands its pieces in the work
+  // region and, since one collective runs at a time, in the pool in front of
+  // it as well (the two are adjacent in the arena).
+  const uint64_t stage_off = layout.pool_offset;
+  const uint64_t stage_bytes = ring ? layout.pool_bytes : layout.pool_bytes + layout.work_bytes;
   Key key{static_cast<int>(algo), rank, world_size, len_elements, static_cast<int>(dtype), static_cast<int>(wire),
           env_chunk, apply_scale, stage_off, stage_bytes};
   auto it = cache_.find(key);
   if (it != cache_.end()) return *it->second;
 
   const int regions = NumRegions(algo, world_size);
-  // At least four slots per region keep the pipeline moving; two is the
-  // minimum the schedule needs.
-  uint64_t max_chunk_wire = stage_bytes / (static_cast<uint64_t>(regions) * 4) / 128 * 128;
-  if (max_chunk_wire < 128) max_chunk_wire = 128;
-  const size_t max_chunk_user = static_cast<size_t>(max_chunk_wire / wsize * esize);
   ProgramRequest req;
   req.algo = algo;
   req.rank = rank;
   req.world_size = world_size;
-  req.ranges = SplitForDevice(len_elements, esize, static_cast<size_t>(world_size), env_chunk, max_chunk_user);
-  if (!ring && rank == 0) {
-    const size_t nominal = len_elements / (4 * static_cast<size_t>(world_size)) * wsize;
-    static bool warned = false;
-    if (nominal > stage_bytes / static_cast<uint64_t>(regions) && !warned) {
-      warned = true;
-      IBCOMM_WARN("IBCOMM_WORK_GPU_MEMORY_SIZE (%llu bytes) is smaller than one chunk per partner (%zu bytes x %d); "
-                  "chunks are cut into smaller pieces. Increase it for large messages.\n",
-                  static_cast<unsigned long long>(stage_bytes), nominal, regions);
+  if (ring) {
+    // At least four slots keep the pipeline moving; two is the minimum the
+    // schedule needs.
+    uint64_t max_chunk_wire = stage_bytes / (static_cast<uint64_t>(regions) * 4) / 128 * 128;
+    if (max_chunk_wire < 128) max_chunk_wire = 128;
+    const size_t max_chunk_user = static_cast<size_t>(max_chunk_wire / wsize * esize);
+    req.ranges = SplitForDevice(len_elements, esize, static_cast<size_t>(world_size), env_chunk, max_chunk_user);
+  } else {
+    // Chunks only fix the block boundaries here; what travels are pieces:
+    // IBCOMM_CHUNKSIZE when set, otherwise an eighth of the message (four
+    // pieces in the largest step), as far as two slots per partner fit.
+    req.ranges = SplitForDevice(len_elements, esize, static_cast<size_t>(world_size), env_chunk, 0);
+    size_t cap = static_cast<size_t>(stage_bytes / (static_cast<uint64_t>(regions) * 2) / wsize) / 32 * 32;
+    if (cap < 32) cap = 32;
+    size_t piece = env_chunk > 0 ? static_cast<size_t>(env_chunk) / esize : std::max<size_t>(util::ceilDiv(len_elements, size_t(8)), 16384);
+    if (piece > cap) {
+      static bool warned = false;
+      if (!warned && rank == 0) {
+        warned = true;
+        IBCOMM_WARN("IBCOMM_MEMORY_POOL_PRE_ALLOC + IBCOMM_WORK_GPU_MEMORY_SIZE (%llu bytes) limit Rabenseifner's transfer "
+                    "pieces to %zu bytes instead of %zu; increase them for large messages.\n",
+                    static_cast<unsigned long long>(stage_bytes), cap * wsize, piece * wsize);
+      }
+      piece = cap;
     }
+    if (env_chunk <= 0 && piece >= 32) piece = util::ceilDiv(piece, size_t(32)) * 32;
+    req.piece_elems = piece;
   }
   req.wire_elem_bytes = wsize;
   req.stage_offset = stage_off;

@@ -118,7 +118,7 @@ __device__ void ScalarLoop(const Op& op, const T* sendbuf, T* recvbuf, const W* 
                            uint64_t hi, double scale) {
   using A = typename Acc<T>::type;
   for (uint64_t k = lo + threadIdx.x; k < hi; k += blockDim.x) {
-    const uint64_t g = op.elem_begin + k;
+    const uint64_t g = op.cell_begin + k;
     A v;
     if (op.src_a == kSrcStage) v = ToAcc<A, W>(LdScalarStrong<W>(stage_in + k));
     else if (op.src_a == kSrcSend) v = ToAcc<A, T>(sendbuf[g]);
@@ -136,7 +136,7 @@ template <typename T, typename W>
 __device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch) {
   using Tr = ExecTraits<T, W>;
   uint64_t lo, hi;
-  ChannelSlice(op.elem_count, p.stage.slot_bytes / sizeof(W), nch, ch, &lo, &hi);
+  ChannelSlice(op.elem_begin - op.cell_begin, op.elem_count, p.stage.slot_bytes / sizeof(W), nch, ch, &lo, &hi);
   if (lo >= hi) return;
   const T* sendbuf = static_cast<const T*>(p.sendbuf);
   T* recvbuf = static_cast<T*>(p.recvbuf);
@@ -149,7 +149,7 @@ __device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch) {
   if (op.flags & kOpStoreRemote)
     stage_out = reinterpret_cast<W*>(p.peers.arena[op.peer_out] + st.offset +
                                      (static_cast<uint64_t>(op.region_out) * st.slots + op.slot_out) * st.slot_bytes);
-  const uint64_t g0 = op.elem_begin + lo;
+  const uint64_t g0 = op.cell_begin + lo;
   const bool uses_send = op.src_a == kSrcSend || op.src_b == kSrcSend;
   const bool uses_recv = op.src_a == kSrcRecv || op.src_b == kSrcRecv || (op.flags & kOpStoreLocal);
   bool aligned = true;

@@ -61,6 +61,25 @@ template <> struct Multimem<__nv_bfloat16> {
   }
 };
 
+// dst[b..e) = src[b..e) in 16-byte vectors, eight loads in flight per thread.
+template <bool kStrongSrc>
+__device__ __forceinline__ void CopyVectors(uint4* dst, const uint4* src, uint64_t b, uint64_t e) {
+  constexpr int kU = 8;
+  for (uint64_t i = b + threadIdx.x; i < e; i += static_cast<uint64_t>(blockDim.x) * kU) {
+    uint4 v[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+      if (idx < e) v[u] = kStrongSrc ? Ld16Strong(src + idx) : Ld16(src + idx);
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+      if (idx < e) St16(dst + idx, v[u]);
+    }
+  }
+}
+
 // [*b, *e) = part `part` of `parts` of the range [lo, hi).
 __device__ __forceinline__ void SubRange(uint64_t lo, uint64_t hi, int part, int parts, uint64_t* b, uint64_t* e) {
   const uint64_t len = hi - lo;
@@ -130,7 +149,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
         uint64_t sb, se, b, e;
         SubRange(0, nvec, s, p.world_size, &sb, &se);
         SubRange(sb, se, cta, ncta, &b, &e);
-        for (uint64_t i = b + threadIdx.x; i < e; i += blockDim.x) St16(dst + i, Ld16(src + i));
+        CopyVectors<false>(dst, src, b, e);
       }
       if (cta == 0) {
         T* dt = reinterpret_cast<T*>(p.local_in);
@@ -195,7 +214,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
         uint64_t sb, se, b, e;
         SubRange(0, nvec, s, p.world_size, &sb, &se);
         SubRange(sb, se, cta, ncta, &b, &e);
-        for (uint64_t i = b + threadIdx.x; i < e; i += blockDim.x) St16(dst + i, Ld16Strong(src + i));
+        CopyVectors<true>(dst, src, b, e);
       }
     }
   }

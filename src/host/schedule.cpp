@@ -31,13 +31,39 @@ struct Builder {
     IBCOMM_FAIL(INVALID_ARGUMENT, "schedule: rank %d is not an in-peer of rank %d.\n", sender, receiver);
   }
 
-  Op Base(int chunk) const {
+  Op Base(const Range& g) const {
     Op op{};
     op.peer_in = -1;
     op.peer_out = -1;
-    op.elem_begin = req.ranges[static_cast<size_t>(chunk)].first;
-    op.elem_count = req.ranges[static_cast<size_t>(chunk)].second - req.ranges[static_cast<size_t>(chunk)].first;
+    op.elem_begin = g.first;
+    op.elem_count = g.second - g.first;
+    op.cell_begin = g.first;
+    if (req.algo == Algo::kRabenseifner && req.piece_elems != 0) op.cell_begin = g.first / req.piece_elems * req.piece_elems;
     return op;
+  }
+  Range ChunkRange(int chunk) const { return req.ranges[static_cast<size_t>(chunk)]; }
+
+  // Cuts the contiguous chunk list `chunks` into transfer pieces: one piece per
+  // chunk, or, when the request names a piece length, pieces of that length
+  // over the whole contiguous element range (fewer, larger ops).
+  std::vector<Range> Pieces(const std::vector<int>& chunks) const {
+    std::vector<Range> out;
+    if (chunks.empty()) return out;
+    if (req.piece_elems == 0 || req.algo != Algo::kRabenseifner) {
+      for (int c : chunks) out.push_back(ChunkRange(c));
+      return out;
+    }
+    // Pieces are the cells of a fixed grid over the message (multiples of the
+    // piece length), clipped to the run: an element lies in the same cell in
+    // every step.
+    const size_t b = ChunkRange(chunks.front()).first, e = ChunkRange(chunks.back()).second;
+    size_t x = b;
+    while (x < e) {
+      const size_t cell_end = (x / req.piece_elems + 1) * req.piece_elems;
+      out.emplace_back(x, std::min(e, cell_end));
+      x = std::min(e, cell_end);
+    }
+    return out;
   }
 
   void AttachOut(Op* op, int to) {
@@ -60,16 +86,16 @@ struct Builder {
   }
 
   // Plain send of a chunk taken from `src` (sendbuf or recvbuf).
-  void Send(int chunk, OpSrc src, int to) {
-    Op op = Base(chunk);
+  void Send(const Range& g, OpSrc src, int to) {
+    Op op = Base(g);
     op.src_a = src;
     AttachOut(&op, to);
     prog.ops.push_back(op);
   }
 
   // Receive a chunk; optionally add `add` to it, store locally and/or forward.
-  void Recv(int chunk, int from, OpSrc add, bool store_local, bool scale, int forward_to) {
-    Op op = Base(chunk);
+  void Recv(const Range& g, int from, OpSrc add, bool store_local, bool scale, int forward_to) {
+    Op op = Base(g);
     op.src_a = kSrcStage;
     op.src_b = add;
     if (store_local) op.flags |= kOpStoreLocal;
@@ -83,17 +109,14 @@ struct Builder {
   // One exchange step with a single partner: `sends` leave, `recvs` arrive.
   // Sends run at most `slots` ahead of the receives so that neither side can
   // block on credits the other side has not had a chance to return.
-  struct RecvSpec {
-    int chunk;
-    OpSrc add;
-    bool scale;
-  };
-  void Exchange(int peer, const std::vector<int>& sends, OpSrc send_src, const std::vector<RecvSpec>& recvs) {
+  void Exchange(int peer, const std::vector<int>& send_chunks, OpSrc send_src, const std::vector<int>& recv_chunks,
+                OpSrc recv_add, bool recv_scale) {
+    const std::vector<Range> sends = Pieces(send_chunks), recvs = Pieces(recv_chunks);
     size_t si = 0, ri = 0;
     const size_t ahead = slots;
     while (si < sends.size() && si < ahead) Send(sends[si++], send_src, peer);
     while (ri < recvs.size()) {
-      Recv(recvs[ri].chunk, peer, recvs[ri].add, true, recvs[ri].scale, -1);
+      Recv(recvs[ri], peer, recv_add, true, recv_scale, -1);
       ++ri;
       if (si < sends.size()) Send(sends[si++], send_src, peer);
     }
@@ -121,17 +144,17 @@ void BuildRing(Builder* bld) {
   };
   for (size_t i = 0; i < positions; ++i) {
     int c = at(r, i);
-    if (c >= 0) bld->Send(c, kSrcSend, to);
+    if (c >= 0) bld->Send(bld->ChunkRange(c), kSrcSend, to);
     for (int k = 0; k <= ws - 2; ++k) {  // reduce-scatter
       c = at(Mod(r - 1 - k, ws), i);
       if (c < 0) continue;
       const bool final_step = (k == ws - 2);
-      bld->Recv(c, from, kSrcSend, /*store_local=*/final_step, /*scale=*/final_step, to);
+      bld->Recv(bld->ChunkRange(c), from, kSrcSend, /*store_local=*/final_step, /*scale=*/final_step, to);
     }
     for (int k = 0; k <= ws - 2; ++k) {  // all-gather
       c = at(Mod(r - k, ws), i);
       if (c < 0) continue;
-      bld->Recv(c, from, kSrcNone, true, false, k != ws - 2 ? to : -1);
+      bld->Recv(bld->ChunkRange(c), from, kSrcNone, true, false, k != ws - 2 ? to : -1);
     }
   }
 }
@@ -144,11 +167,10 @@ void BuildRabenseifner(Builder* bld) {
   const int exp = util::GetExpOfTwo(static_cast<uint64_t>(p));
   const int C = static_cast<int>(q.ranges.size());
   auto real_rank = [extra](int v) { return v < extra ? 2 * v + 1 : v + extra; };
-  using RecvSpec = Builder::RecvSpec;
-
   std::vector<int> all(static_cast<size_t>(C));
   for (int i = 0; i < C; ++i) all[static_cast<size_t>(i)] = i;
   const std::vector<int> front(all.begin(), all.begin() + C / 2), back(all.begin() + C / 2, all.end());
+  const std::vector<int> none;
 
   int vrank;
   OpSrc partial = kSrcSend;  // where my running partial sum lives
@@ -157,16 +179,12 @@ void BuildRabenseifner(Builder* bld) {
     const int partner = even ? r + 1 : r - 1;
     const std::vector<int>& keep = even ? front : back;
     const std::vector<int>& give = even ? back : front;
-    std::vector<RecvSpec> recvs;
-    for (int c : keep) recvs.push_back({c, kSrcSend, false});
-    bld->Exchange(partner, give, kSrcSend, recvs);
+    bld->Exchange(partner, give, kSrcSend, keep, kSrcSend, false);
     if (even) {
-      bld->Exchange(partner, keep, kSrcRecv, {});
+      bld->Exchange(partner, keep, kSrcRecv, none, kSrcNone, false);
       vrank = -1;
     } else {
-      std::vector<RecvSpec> rest;
-      for (int c : give) rest.push_back({c, kSrcNone, false});
-      bld->Exchange(partner, {}, kSrcRecv, rest);
+      bld->Exchange(partner, none, kSrcRecv, give, kSrcNone, false);
       vrank = r / 2;
       partial = kSrcRecv;
     }
@@ -186,9 +204,8 @@ void BuildRabenseifner(Builder* bld) {
       } else {
         kb = b; ke = mid; sb = mid; se = e;
       }
-      std::vector<RecvSpec> recvs;
-      for (int c : ChunksOfBlocks(blocks, kb, ke)) recvs.push_back({c, partial, s == exp - 1});
-      bld->Exchange(real_rank(vpeer), ChunksOfBlocks(blocks, sb, se), partial, recvs);
+      bld->Exchange(real_rank(vpeer), ChunksOfBlocks(blocks, sb, se), partial, ChunksOfBlocks(blocks, kb, ke), partial,
+                    s == exp - 1);
       partial = kSrcRecv;
       b = kb;
       e = ke;
@@ -202,22 +219,15 @@ void BuildRabenseifner(Builder* bld) {
       } else {
         rb = b - w; re = b;
       }
-      std::vector<RecvSpec> recvs;
-      for (int c : ChunksOfBlocks(blocks, rb, re)) recvs.push_back({c, kSrcNone, false});
-      bld->Exchange(real_rank(vpeer), ChunksOfBlocks(blocks, b, e), kSrcRecv, recvs);
+      bld->Exchange(real_rank(vpeer), ChunksOfBlocks(blocks, b, e), kSrcRecv, ChunksOfBlocks(blocks, rb, re), kSrcNone, false);
       b = std::min(b, rb);
       e = std::max(e, re);
     }
   }
 
   if (r < 2 * extra) {
-    if ((r & 1) == 0) {
-      std::vector<RecvSpec> recvs;
-      for (int c : all) recvs.push_back({c, kSrcNone, false});
-      bld->Exchange(r + 1, {}, kSrcRecv, recvs);
-    } else {
-      bld->Exchange(r - 1, all, kSrcRecv, {});
-    }
+    if ((r & 1) == 0) bld->Exchange(r + 1, none, kSrcRecv, all, kSrcNone, false);
+    else bld->Exchange(r - 1, all, kSrcRecv, none, kSrcNone, false);
   }
 }
 
@@ -264,7 +274,8 @@ StageLayout PlanStage(const ProgramRequest& req) {
   st.offset = req.stage_offset;
   st.regions = static_cast<uint32_t>(NumRegions(req.algo, req.world_size));
   // +16 so that a slice may start at the same 16-byte phase as the user data.
-  uint64_t bytes = MaxChunkElems(req.ranges) * req.wire_elem_bytes;
+  const bool pieces = req.algo == Algo::kRabenseifner && req.piece_elems != 0;
+  uint64_t bytes = (pieces ? req.piece_elems : MaxChunkElems(req.ranges)) * req.wire_elem_bytes;
   st.slot_bytes = (bytes + 127) & ~uint64_t(127);
   if (st.slot_bytes == 0) st.slot_bytes = 128;
   uint64_t per_region = req.stage_bytes / st.regions;

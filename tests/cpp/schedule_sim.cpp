@@ -13,13 +13,13 @@ using namespace ibcomm;
 
 template <typename T>
 static bool RunCase(Algo algo, int ws, size_t n, int64_t env_chunk, size_t stage_bytes, int nch, bool in_place,
-                    double scale, size_t max_chunk_bytes = 0) {
+                    double scale, size_t max_chunk_bytes = 0, size_t piece_elems = 0) {
   std::vector<Range> ranges = SplitForDevice(n, sizeof(T), static_cast<size_t>(ws), env_chunk, max_chunk_bytes);
   std::vector<std::vector<T>> in(static_cast<size_t>(ws), std::vector<T>(n)), out;
   std::mt19937 gen(static_cast<unsigned>(n * 31 + static_cast<size_t>(ws)));
   for (int r = 0; r < ws; ++r)
     for (size_t i = 0; i < n; ++i) in[static_cast<size_t>(r)][i] = static_cast<T>(static_cast<int>(gen() % 2001) - 1000);
-  ProgramSimulator<T> sim(algo, ws, stage_bytes, nch);
+  ProgramSimulator<T> sim(algo, ws, stage_bytes, nch, piece_elems);
   SimResult res = sim.Run(ranges, in, &out, scale, in_place);
   if (!res.ok) {
     fprintf(stderr, "%s ws=%d n=%zu: %s", AlgoName(algo), ws, n, res.error.c_str());
@@ -95,6 +95,18 @@ MINI_TEST(SlotReuseWithSeveralChannels) {
         const size_t maxc = stage / (static_cast<size_t>(NumRegions(a, ws)) * 4) / 128 * 128;
         CHECK_TRUE(RunCase<int>(a, ws, 100000, 0, stage, nch, false, 1.0, maxc));
         CHECK_TRUE(RunCase<int>(a, ws, 10007, 0, 40000, nch, true, 1.0, 40000 / (static_cast<size_t>(NumRegions(a, ws)) * 4) / 128 * 128));
+      }
+}
+
+MINI_TEST(RabenseifnerMergedPieces) {
+  // Transfer pieces that ignore chunk boundaries: larger than a chunk, smaller
+  // than a chunk, and not a divisor of anything; tight staging and several channels.
+  for (int ws = 2; ws <= 8; ++ws)
+    for (size_t piece : {size_t(32), size_t(1000), size_t(4096), size_t(100000)})
+      for (int nch : {1, 3}) {
+        CHECK_TRUE(RunCase<int>(Algo::kRabenseifner, ws, 100003, 0, size_t(1) << 22, nch, false, 1.0, 0, piece));
+        const size_t regions = static_cast<size_t>(NumRegions(Algo::kRabenseifner, ws));
+        CHECK_TRUE(RunCase<int>(Algo::kRabenseifner, ws, 50000, 0, 2 * regions * ((piece * 4 + 127) / 128 * 128), nch, true, 1.0, 0, piece));
       }
 }
 
