@@ -57,6 +57,9 @@ def parse_args():
     ap.add_argument("--sweep-max-bytes", type=int, default=1 << 30)
     ap.add_argument("--out", default=None)
     ap.add_argument("--no-extras", action="store_true", help="skip per-algorithm and NCCL measurements")
+    ap.add_argument("--kernel-case", default=None,
+                    choices=["copy", "exec_ring_emu8", "exec_rabenseifner_emu8", "oneshot_emu8"],
+                    help="run one small single-GPU case of one kernel (for ncu captures) and print its time")
     return ap.parse_args()
 
 
@@ -174,6 +177,8 @@ def main() -> int:
 
     if args.sweep:
         return sweep(args, comm, world, rank, dev, time_steps, barrier)
+    if args.kernel_case:
+        return kernel_case(args, comm, dev, time_steps)
 
     n = args.elements
     nbytes = n * 4
@@ -289,6 +294,32 @@ def main() -> int:
         comm.close()
         dist.destroy_process_group()
     return 0 if ok else 1
+
+
+def kernel_case(args, comm, dev, time_steps) -> int:
+    """One kernel, one GPU, small inputs (still larger than L2): the workload of the ncu captures in profiles/."""
+    import torch
+
+    import allreduce_proto_b200 as ar
+
+    case = args.kernel_case
+    if case == "copy":
+        n = 64 << 20  # 256 MiB in, 256 MiB out
+        x = torch.rand(n, device=dev)
+        y = torch.empty_like(x)
+        ms = time_steps(lambda: comm.allreduce(x, y, scale=0.5), args.steps, args.warmup)
+        moved = 2 * n * 4
+    else:
+        emu = ar.EmuWorld(8)
+        algo = {"exec_ring_emu8": "ring", "exec_rabenseifner_emu8": "rabenseifner", "oneshot_emu8": "oneshot"}[case]
+        m = (16 << 10) if algo == "oneshot" else (8 << 20)  # elements per rank: 64 KiB or 32 MiB
+        ins = [torch.rand(m, device=dev) for _ in range(8)]
+        outs = [torch.empty(m, device=dev) for _ in range(8)]
+        ms = time_steps(lambda: emu.allreduce(ins, outs, algo=algo, scale=0.125, sync=False), args.steps, args.warmup)
+        moved = None
+    print(json.dumps({"kernel_case": case, "ms": ms, "steps": args.steps,
+                      "gbs_read_plus_write": (moved / (ms / 1e3) / 1e9) if moved else None}))
+    return 0
 
 
 def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
