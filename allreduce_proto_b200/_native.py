@@ -21,7 +21,7 @@ CUDA_ERROR = 3
 NOT_SUPPORTED = 4
 
 DTYPE_CODES = {"float32": 0, "float64": 1, "int32": 2, "int64": 3, "float16": 4, "bfloat16": 5}
-ALGO_CODES = {"auto": 0, "ring": 1, "rabenseifner": 2, "nvls": 3, "oneshot": 4}
+ALGO_CODES = {"auto": 0, "ring": 1, "rabenseifner": 2, "nvls": 3, "oneshot": 4, "direct": 5}
 ALGO_NAMES = {v: k for k, v in ALGO_CODES.items()}
 
 
@@ -84,6 +84,7 @@ def _declare(lib) -> None:
         "ibcomm_emu_set_timeout_ms": [vp, i],
         "ibcomm_emu_last_channels": [vp],
         "ibcomm_emu_set_silent_rank": [vp, i],
+        "ibcomm_emu_set_direct_staging": [vp, i],
         "ibcomm_emu_last_status": [vp, C.POINTER(StatusReport)],
         "ibcomm_copy_scale": [vp, vp, sz, i, i, dbl, vp],
         "ibcomm_parse_number": [C.c_char_p, C.POINTER(C.c_int64)],

@@ -111,6 +111,8 @@ class Communicator:
         theirs = exchange(self.rank, mine)
         for src, info in theirs.items():
             self.register_queue_pair(src, info)
+        # Nobody may leave (and take its endpoints away) before everybody attached.
+        self.barrier()
 
     @classmethod
     def from_torch_distributed(cls, group=None, tag: str = "c0") -> "Communicator":

@@ -18,7 +18,7 @@ typedef struct ibcomm_comm ibcomm_comm;
 typedef struct ibcomm_emu ibcomm_emu;
 
 /* dtype: 0 float32, 1 float64, 2 int32, 3 int64, 4 float16, 5 bfloat16
- * algo : 0 auto, 1 ring, 2 rabenseifner, 3 nvls, 4 oneshot */
+ * algo : 0 auto, 1 ring, 2 rabenseifner, 3 nvls, 4 oneshot, 5 direct */
 
 const char* ibcomm_last_error(void);
 int ibcomm_has_cuda(void);
@@ -89,6 +89,8 @@ int ibcomm_emu_last_channels(ibcomm_emu* w);
 /* Test hook: rank `rank` does not take part in the following collectives
  * (-1 = everybody takes part), so its peers' bounded waits run out. */
 int ibcomm_emu_set_silent_rank(ibcomm_emu* w, int rank);
+/* Direct algorithm through the pool windows (1) or in place (0, default). */
+int ibcomm_emu_set_direct_staging(ibcomm_emu* w, int on);
 typedef struct {
   uint32_t code;
   uint32_t kind;

@@ -40,6 +40,9 @@ class EmuWorld {
   // return at once), so its peers' bounded waits run out and they report a
   // timeout; nothing faults or hangs.  -1 restores normal operation.
   void SetSilentRank(int r);
+  // Makes the direct algorithm stage through the pool windows (as it does for
+  // buffers the peers cannot map) instead of using the buffers in place.
+  void SetDirectStaging(bool on);
   int last_channels() const;
 
   struct Impl;

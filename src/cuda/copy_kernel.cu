@@ -2,12 +2,14 @@
 //
 // Used for world_size == 1 (the reference's whole-buffer cudaMemcpy,
 // ibcomm/allreduce_cuda_impl.h:40-46, 332-340, with the scale and the type
-// conversion fused in) and for local staging copies.  Tiles travel
-// global -> shared -> global with the bulk asynchronous copy engine (TMA,
-// non-tensor form `cp.async.bulk`, no cluster multicast): one elected thread
-// issues the copies and an mbarrier reports their arrival, the CTA's threads
-// only touch shared memory.  A multi-stage ring of tiles keeps loads, math and
-// stores of different tiles in flight at once.  Every wait is bounded.
+// conversion fused in) and for local staging copies.  Input tiles travel
+// global -> shared with the bulk asynchronous copy engine (TMA, non-tensor
+// form `cp.async.bulk`, no cluster multicast).  Every warp runs its own
+// pipeline: a ring of four 4 KiB tiles with one mbarrier each, refilled by the
+// warp's first lane, so 128 KiB of loads are in flight per SM without
+// occupying registers and no CTA-wide barrier sits on the critical path.  The
+// lanes read a tile from shared memory, scale and convert it, and write the
+// result with 16-byte global stores.  Every wait is bounded.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -19,8 +21,9 @@ namespace ibcomm {
 namespace dev {
 
 constexpr int kCopyThreads = 256;
-constexpr int kCopyStages = 4;
-constexpr int kCopyTileBytesIn = 16384;  // bytes of input per tile
+constexpr int kCopyWarps = kCopyThreads / 32;
+constexpr int kCopyStages = 4;            // tiles in flight per warp
+constexpr int kCopyTileBytesIn = 4096;    // bytes of input per tile
 constexpr uint32_t kMbarSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -63,32 +66,32 @@ __device__ __forceinline__ void BulkWaitRead() {
 __device__ __forceinline__ void BulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void FenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// Tiles of `kTileElems` elements.  Requires 16-byte aligned `in` and `out`;
-// the ragged end (less than one 16-byte vector of either type) is finished
-// with plain loads and stores.
+// Tiles of `kTileElems` elements, dealt round-robin to the warps of the grid.
+// Requires 16-byte aligned `in` and `out`; the ragged end (less than one
+// 16-byte vector of either type) is finished with plain loads and stores.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(kCopyThreads) CopyScaleTmaKernel(const TI* __restrict__ in, TO* __restrict__ out, uint64_t n,
                                                                    double scale, uint32_t* doorbell) {
   using A = typename Acc<TI>::type;
   constexpr int kTileElems = kCopyTileBytesIn / static_cast<int>(sizeof(TI));
-  constexpr int kOutTileBytes = kTileElems * static_cast<int>(sizeof(TO));
   extern __shared__ __align__(128) unsigned char smem[];
-  TI* in_tiles = reinterpret_cast<TI*>(smem);
-  TO* out_tiles = reinterpret_cast<TO*>(smem + kCopyStages * kCopyTileBytesIn);
-  __shared__ uint64_t full_bar[kCopyStages];
-  __shared__ int s_fail;
+  __shared__ uint64_t full_bar[kCopyWarps][kCopyStages];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  TI* my_tiles_smem = reinterpret_cast<TI*>(smem + static_cast<size_t>(warp) * kCopyStages * kCopyTileBytesIn);
 
-  // Elements that can move as whole 16-byte vectors in both types.
-  constexpr uint64_t kQuantum = 16 / (sizeof(TI) < sizeof(TO) ? sizeof(TI) : sizeof(TO));
-  const uint64_t n_bulk = n / kQuantum * kQuantum;
+  // Elements that move as whole 16-byte vectors in both types.
+  constexpr int kQ = 16 / static_cast<int>(sizeof(TI) < sizeof(TO) ? sizeof(TI) : sizeof(TO));
+  constexpr int kNI = kQ / VecIO<TI>::kN;  // input vectors per quantum
+  constexpr int kNO = kQ / VecIO<TO>::kN;  // output vectors per quantum
+  const uint64_t n_bulk = n / kQ * kQ;
   const uint64_t num_tiles = (n_bulk + kTileElems - 1) / kTileElems;
+  const bool do_scale = scale != 1.0;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kCopyStages; ++s) MbarInit(&full_bar[s], 1);
-    s_fail = 0;
+  if (lane == 0) {
+    for (int s = 0; s < kCopyStages; ++s) MbarInit(&full_bar[warp][s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
+  __syncwarp();
 
   auto tile_elems = [&](uint64_t t) -> uint32_t {
     const uint64_t b = t * kTileElems;
@@ -96,54 +99,61 @@ __global__ void __launch_bounds__(kCopyThreads) CopyScaleTmaKernel(const TI* __r
     return static_cast<uint32_t>(e - b);
   };
 
-  // This CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
-  const uint64_t first = blockIdx.x, step = gridDim.x;
+  // This warp's tiles: first, first + step, ...
+  const uint64_t first = static_cast<uint64_t>(blockIdx.x) * kCopyWarps + warp;
+  const uint64_t step = static_cast<uint64_t>(gridDim.x) * kCopyWarps;
   const uint64_t my_tiles = first < num_tiles ? (num_tiles - first + step - 1) / step : 0;
 
-  if (threadIdx.x == 0) {
+  if (lane == 0) {
     for (uint64_t k = 0; k < my_tiles && k < kCopyStages; ++k) {
       const uint64_t t = first + k * step;
       const uint32_t bytes = tile_elems(t) * static_cast<uint32_t>(sizeof(TI));
-      MbarExpectTx(&full_bar[k], bytes);
-      BulkLoad(in_tiles + k * kTileElems, in + t * kTileElems, bytes, &full_bar[k]);
+      MbarExpectTx(&full_bar[warp][k], bytes);
+      BulkLoad(my_tiles_smem + k * kTileElems, in + t * kTileElems, bytes, &full_bar[warp][k]);
     }
   }
+  __syncwarp();
 
+  bool failed = false;
   for (uint64_t k = 0; k < my_tiles; ++k) {
     const int s = static_cast<int>(k % kCopyStages);
     const uint32_t parity = static_cast<uint32_t>((k / kCopyStages) & 1);
     const uint64_t t = first + k * step;
-    const uint32_t cnt = tile_elems(t);
-    if (!MbarWait(&full_bar[s], parity)) s_fail = 1;
-    // The store that last read out_tiles[s] (tile k - kCopyStages) must be done
-    // reading shared memory before the slot is overwritten.
-    if (threadIdx.x == 0) BulkWaitRead<kCopyStages - 1>();
-    __syncthreads();
-    if (s_fail) break;
-    const TI* src = in_tiles + s * kTileElems;
-    TO* dst = out_tiles + s * kTileElems;
-    for (uint32_t i = threadIdx.x; i < cnt; i += kCopyThreads) {
-      A v = ToAcc<A, TI>(src[i]);
-      dst[i] = FromAcc<TO, A>(ScaleAcc<A>(v, scale));
+    const uint32_t quanta = tile_elems(t) / kQ;
+    if (!MbarWait(&full_bar[warp][s], parity)) failed = true;
+    if (__any_sync(0xffffffffu, failed)) {
+      failed = true;
+      break;
     }
-    FenceProxyAsync();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      BulkStore(out + t * kTileElems, dst, cnt * static_cast<uint32_t>(sizeof(TO)));
-      BulkCommit();
+    const uint4* src = reinterpret_cast<const uint4*>(my_tiles_smem + s * kTileElems);
+    uint4* dst = reinterpret_cast<uint4*>(out + t * kTileElems);
+    for (uint32_t q = lane; q < quanta; q += 32) {
+      A acc[kQ];
+#pragma unroll
+      for (int v = 0; v < kNI; ++v) VecIO<TI>::Load(src[q * kNI + v], acc + v * VecIO<TI>::kN);
+      if (do_scale) {
+#pragma unroll
+        for (int e = 0; e < kQ; ++e) acc[e] = ScaleAcc<A>(acc[e], scale);
+      }
+      typename Acc<TO>::type out_acc[kQ];
+#pragma unroll
+      for (int e = 0; e < kQ; ++e) out_acc[e] = static_cast<typename Acc<TO>::type>(acc[e]);
+#pragma unroll
+      for (int v = 0; v < kNO; ++v) St16(dst + q * kNO + v, VecIO<TO>::Store(out_acc + v * VecIO<TO>::kN));
+    }
+    // Every lane is done reading the stage before it is refilled.
+    __syncwarp();
+    if (lane == 0) {
       const uint64_t kn = k + kCopyStages;
       if (kn < my_tiles) {
         const uint64_t tn = first + kn * step;
         const uint32_t bytes = tile_elems(tn) * static_cast<uint32_t>(sizeof(TI));
-        MbarExpectTx(&full_bar[s], bytes);
-        BulkLoad(in_tiles + s * kTileElems, in + tn * kTileElems, bytes, &full_bar[s]);
+        MbarExpectTx(&full_bar[warp][s], bytes);
+        BulkLoad(my_tiles_smem + s * kTileElems, in + tn * kTileElems, bytes, &full_bar[warp][s]);
       }
     }
   }
-  if (threadIdx.x == 0) {
-    BulkWaitAll();
-    if (s_fail && doorbell != nullptr) *reinterpret_cast<volatile uint32_t*>(doorbell) = kStatusWaitTimeout;
-  }
+  if (failed && lane == 0 && doorbell != nullptr) *reinterpret_cast<volatile uint32_t*>(doorbell) = kStatusWaitTimeout;
   // Ragged end.
   if (blockIdx.x == 0) {
     for (uint64_t i = n_bulk + threadIdx.x; i < n; i += kCopyThreads) {
@@ -151,7 +161,6 @@ __global__ void __launch_bounds__(kCopyThreads) CopyScaleTmaKernel(const TI* __r
       out[i] = FromAcc<TO, A>(ScaleAcc<A>(v, scale));
     }
   }
-  (void)kOutTileBytes;
 }
 
 // Plain grid-stride variant for unaligned buffers.
@@ -177,7 +186,7 @@ static cudaError_t LaunchCopyTyped(const CopyParams& p, int blocks, cudaStream_t
     return cudaGetLastError();
   }
   constexpr int kTileElems = dev::kCopyTileBytesIn / static_cast<int>(sizeof(TI));
-  const size_t smem = static_cast<size_t>(dev::kCopyStages) * (dev::kCopyTileBytesIn + kTileElems * sizeof(TO));
+  const size_t smem = static_cast<size_t>(dev::kCopyWarps) * dev::kCopyStages * dev::kCopyTileBytesIn;
   static thread_local bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(dev::CopyScaleTmaKernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -185,7 +194,8 @@ static cudaError_t LaunchCopyTyped(const CopyParams& p, int blocks, cudaStream_t
     configured = true;
   }
   const uint64_t tiles = (p.len_elements + kTileElems - 1) / kTileElems;
-  if (static_cast<uint64_t>(blocks) > tiles) blocks = static_cast<int>(tiles);
+  const uint64_t blocks_needed = (tiles + dev::kCopyWarps - 1) / dev::kCopyWarps;
+  if (static_cast<uint64_t>(blocks) > blocks_needed) blocks = static_cast<int>(blocks_needed);
   if (blocks < 1) blocks = 1;
   dev::CopyScaleTmaKernel<TI, TO><<<blocks, dev::kCopyThreads, smem, stream>>>(in, out, p.len_elements, p.scale, doorbell);
   return cudaGetLastError();

@@ -85,7 +85,8 @@ class DeviceContext {
   void RunProgram(Algo algo, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
                   cudaStream_t stream);
   void RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels, cudaStream_t stream);
-  void RunNvls(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels, cudaStream_t stream);
+  void RunTwoShot(bool multimem, DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
+                  cudaStream_t stream);
   void ExchangeAllocation(SharedAllocation* mine, std::vector<std::unique_ptr<SharedAllocation>>* imported,
                           unsigned char** peer_ptr, bool try_multicast, std::unique_ptr<MulticastGroup>* mc);
 
@@ -361,7 +362,7 @@ const SymmetricAlloc* DeviceContext::FindSymmetric(const void* p, size_t bytes) 
 void DeviceContext::RunCopy(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, cudaStream_t stream) {
   if (sendbuf == recvbuf && scale == 1.0) return;
   CopyParams cp{sendbuf, recvbuf, n, static_cast<int32_t>(dtype), static_cast<int32_t>(dtype), scale};
-  CUDACHECK(LaunchCopyKernel(cp, 148 * 2, stream));
+  CUDACHECK(LaunchCopyKernel(cp, 148, stream));
   ++kernel_launches_;
 }
 
@@ -401,8 +402,8 @@ void DeviceContext::RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, 
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
 }
 
-void DeviceContext::RunNvls(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
-                            cudaStream_t stream) {
+void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale,
+                               int channels, cudaStream_t stream) {
   const size_t esize = DTypeSize(dtype);
   const size_t bytes = n * esize;
   NvlsParams p;
@@ -410,6 +411,7 @@ void DeviceContext::RunNvls(DType dtype, const void* sendbuf, void* recvbuf, siz
   p.rank = rank_;
   p.world_size = ws_;
   p.dtype = static_cast<int32_t>(dtype);
+  p.use_multimem = multimem ? 1 : 0;
   p.peers = rr_.peers;
   p.sendbuf = sendbuf;
   p.recvbuf = recvbuf;
@@ -422,8 +424,11 @@ void DeviceContext::RunNvls(DType dtype, const void* sendbuf, void* recvbuf, siz
 
   const SymmetricAlloc* sin = FindSymmetric(sendbuf, bytes);
   const SymmetricAlloc* sout = FindSymmetric(recvbuf, bytes);
-  const bool zin = sin != nullptr && sin->mc && (reinterpret_cast<uintptr_t>(sendbuf) & 15u) == 0;
-  const bool zout = sout != nullptr && sout->mc && (reinterpret_cast<uintptr_t>(recvbuf) & 15u) == 0;
+  // Zero-copy needs the buffer mapped by the peers and, for the switch path,
+  // bound to a multicast object.
+  const bool zin = sin != nullptr && (sin->mc || !multimem) && (reinterpret_cast<uintptr_t>(sendbuf) & 15u) == 0;
+  const bool zout = sout != nullptr && (sout->mc || !multimem) && (reinterpret_cast<uintptr_t>(recvbuf) & 15u) == 0;
+  unsigned char* const mc_arena = mc_ ? mc_->ptr() : nullptr;
   // Staging windows: first half of the pool for inputs, second half for outputs.
   const uint64_t half = layout_.pool_bytes / 2 / 4096 * 4096;
   uint64_t window_elems = half / esize;
@@ -431,21 +436,23 @@ void DeviceContext::RunNvls(DType dtype, const void* sendbuf, void* recvbuf, siz
   p.stage_out = zout ? 0 : 1;
   if (zin) {
     const size_t off = static_cast<const unsigned char*>(sendbuf) - sin->mine->ptr();
-    p.mc_in = sin->mc->ptr() + off;
+    p.mc_in = sin->mc ? sin->mc->ptr() + off : nullptr;
     p.local_in = sin->mine->ptr() + off;
     for (int q = 0; q < ws_; ++q) p.peer_in[q] = sin->peer_ptr[q] + off;
   } else {
-    p.mc_in = mc_->ptr() + layout_.pool_offset;
+    p.mc_in = mc_arena ? mc_arena + layout_.pool_offset : nullptr;
     p.local_in = arena_.ptr() + layout_.pool_offset;
     for (int q = 0; q < ws_; ++q) p.peer_in[q] = rr_.peers.arena[q] + layout_.pool_offset;
   }
   if (zout) {
     const size_t off = static_cast<unsigned char*>(recvbuf) - sout->mine->ptr();
-    p.mc_out = sout->mc->ptr() + off;
+    p.mc_out = sout->mc ? sout->mc->ptr() + off : nullptr;
     p.local_out = sout->mine->ptr() + off;
+    for (int q = 0; q < ws_; ++q) p.peer_out[q] = sout->peer_ptr[q] + off;
   } else {
-    p.mc_out = mc_->ptr() + layout_.pool_offset + half;
+    p.mc_out = mc_arena ? mc_arena + layout_.pool_offset + half : nullptr;
     p.local_out = arena_.ptr() + layout_.pool_offset + half;
+    for (int q = 0; q < ws_; ++q) p.peer_out[q] = rr_.peers.arena[q] + layout_.pool_offset + half;
   }
   p.window_elems = (zin && zout) ? n : window_elems;
   if (p.window_elems == 0) p.window_elems = 1;
@@ -483,7 +490,8 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
     TunerChoice c = ChooseAlgorithm(bytes, ws_, nvls_ok, zero_copy, max_channels_);
     algo = c.algo;
     channels = c.channels;
-    if (algo == Algo::kOneShot && (bytes > layout_.oneshot_slot_bytes || wire != dtype)) {
+    if ((algo == Algo::kOneShot && (bytes > layout_.oneshot_slot_bytes || wire != dtype)) ||
+        ((algo == Algo::kDirect || algo == Algo::kNvls) && wire != dtype)) {
       algo = Algo::kRing;
       channels = ChooseChannels(algo, bytes, ws_, max_channels_);
     }
@@ -494,7 +502,7 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
       IBCOMM_FAIL(INVALID_ARGUMENT, "One-shot allreduce handles at most %llu bytes (got %zu).\n",
                   static_cast<unsigned long long>(layout_.oneshot_slot_bytes), bytes);
     if (algo == Algo::kOneShot && wire != dtype) IBCOMM_FAIL(NOT_SUPPORTED, "One-shot allreduce has no wire compression.\n");
-    if (algo == Algo::kDirect) IBCOMM_FAIL(NOT_SUPPORTED, "Algorithm 'direct' is not available.\n");
+    if (algo == Algo::kDirect && wire != dtype) IBCOMM_FAIL(NOT_SUPPORTED, "The direct algorithm has no wire compression.\n");
     channels = ChooseChannels(algo, bytes, ws_, max_channels_);
   }
   OrderAfterPrevious(stream);
@@ -507,7 +515,10 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
       RunOneShot(dtype, sendbuf, recvbuf, n, opts.scale, channels, stream);
       break;
     case Algo::kNvls:
-      RunNvls(dtype, sendbuf, recvbuf, n, opts.scale, channels, stream);
+      RunTwoShot(true, dtype, sendbuf, recvbuf, n, opts.scale, channels, stream);
+      break;
+    case Algo::kDirect:
+      RunTwoShot(false, dtype, sendbuf, recvbuf, n, opts.scale, channels, stream);
       break;
     default:
       IBCOMM_FAIL(INVALID_ARGUMENT, "Unknown algorithm.\n");

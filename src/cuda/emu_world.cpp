@@ -25,6 +25,7 @@ struct EmuWorld::Impl {
   int max_blocks = 0;
   int last_channels = 0;
   int silent_rank = -1;
+  bool direct_staging = false;
   uint32_t last_status = 0;
   DeviceStatus last_report{};
 
@@ -78,6 +79,7 @@ EmuWorld::~EmuWorld() {
 }
 
 void EmuWorld::SetSilentRank(int r) { impl_->silent_rank = r; }
+void EmuWorld::SetDirectStaging(bool on) { impl_->direct_staging = on; }
 void EmuWorld::SetTimeoutMs(int ms) { impl_->timeout_ms = ms > 0 ? ms : env::ReadTimeoutMs(); }
 int EmuWorld::last_channels() const { return impl_->last_channels; }
 
@@ -109,13 +111,61 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
   }
 
   if (algo == Algo::kAuto) algo = ChooseAlgorithm(bytes, m.ws, false, false, kMaxChannels).algo;
-  if (algo == Algo::kNvls || algo == Algo::kDirect)
-    IBCOMM_FAIL(NOT_SUPPORTED, "Algorithm '%s' needs one GPU per rank; it cannot be emulated on one GPU.\n", AlgoName(algo));
+  if (algo == Algo::kNvls)
+    IBCOMM_FAIL(NOT_SUPPORTED, "Algorithm 'nvls' needs NVSwitch multicast between GPUs; it cannot be emulated on one GPU.\n");
   const uint64_t timeout_ns = static_cast<uint64_t>(m.timeout_ms) * 1000000ull;
   const uint64_t seq = ++m.seq;
   const int cap = std::max(1, m.max_blocks / m.ws);
 
-  if (algo == Algo::kOneShot) {
+  if (algo == Algo::kDirect) {
+    // The two-shot kernel with peer loads and stores.  All ranks' buffers live
+    // on this GPU, so they can be used in place; with `direct_staging` they
+    // go through the pool windows like buffers the peers cannot map.
+    const uint64_t half = m.layout.pool_bytes / 2 / 4096 * 4096;
+    std::vector<NvlsParams> ps(static_cast<size_t>(m.ws));
+    for (int r = 0; r < m.ws; ++r) {
+      NvlsParams& p = ps[static_cast<size_t>(r)];
+      memset(&p, 0, sizeof(p));
+      const RankResources& rr = m.ranks[static_cast<size_t>(r)];
+      p.rank = r;
+      p.world_size = m.ws;
+      p.dtype = static_cast<int32_t>(dtype);
+      p.use_multimem = 0;
+      p.peers = rr.peers;
+      p.sendbuf = sendbufs[static_cast<size_t>(r)];
+      p.recvbuf = recvbufs[static_cast<size_t>(r)];
+      p.len_elements = n;
+      p.scale = scale;
+      p.seq = seq;
+      p.timeout_ns = timeout_ns;
+      p.status = rr.d_status;
+      p.doorbell = rr.d_doorbell;
+      bool aligned = true;
+      for (int q = 0; q < m.ws; ++q)
+        aligned = aligned && ((reinterpret_cast<uintptr_t>(sendbufs[static_cast<size_t>(q)]) | reinterpret_cast<uintptr_t>(recvbufs[static_cast<size_t>(q)])) & 15u) == 0;
+      const bool staged = m.direct_staging || !aligned;
+      p.stage_in = staged ? 1 : 0;
+      p.stage_out = staged ? 1 : 0;
+      for (int q = 0; q < m.ws; ++q) {
+        if (staged) {
+          p.peer_in[q] = rr.peers.arena[q] + m.layout.pool_offset;
+          p.peer_out[q] = rr.peers.arena[q] + m.layout.pool_offset + half;
+        } else {
+          p.peer_in[q] = static_cast<unsigned char*>(const_cast<void*>(sendbufs[static_cast<size_t>(q)]));
+          p.peer_out[q] = static_cast<unsigned char*>(recvbufs[static_cast<size_t>(q)]);
+        }
+      }
+      p.local_in = p.peer_in[r];
+      p.local_out = p.peer_out[r];
+      p.window_elems = staged ? std::max<uint64_t>(1, half / esize) : n;
+    }
+    int ch = channels > 0 ? channels : ChooseChannels(Algo::kDirect, bytes, m.ws, kMaxChannels);
+    ch = std::min(ch, cap);
+    void* d = m.Params(ps.size() * sizeof(NvlsParams));
+    CUDACHECK(cudaMemcpyAsync(d, ps.data(), ps.size() * sizeof(NvlsParams), cudaMemcpyHostToDevice, stream));
+    CUDACHECK(LaunchNvlsKernel(ps[0], static_cast<const NvlsParams*>(d), m.ws, ch, stream));
+    m.last_channels = ch;
+  } else if (algo == Algo::kOneShot) {
     if (bytes > m.layout.oneshot_slot_bytes)
       IBCOMM_FAIL(INVALID_ARGUMENT, "One-shot allreduce handles at most %llu bytes (got %zu).\n",
                   static_cast<unsigned long long>(m.layout.oneshot_slot_bytes), bytes);

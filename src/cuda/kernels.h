@@ -26,11 +26,12 @@ struct CopyParams {
 };
 cudaError_t LaunchCopyKernel(const CopyParams& p, int blocks, cudaStream_t stream);
 
-// ---- NVSwitch multicast allreduce (two-shot) ----
+// ---- two-shot allreduce: in the NVSwitch (multimem) or by direct peer loads/stores ----
 struct NvlsParams {
   int32_t rank;
   int32_t world_size;
   int32_t dtype;
+  int32_t use_multimem;  // 1: multimem.ld_reduce / multimem.st; 0: peer loads + peer stores
   int32_t stage_in;    // copy sendbuf into the multicast-bound staging first
   int32_t stage_out;   // results land in staging and are copied to recvbuf
   PeerTable peers;     // control pages live in the arenas
@@ -45,8 +46,10 @@ struct NvlsParams {
   unsigned char* mc_out;
   unsigned char* local_in;
   unsigned char* local_out;
-  // Unicast views of every rank's input window (for the unaligned tail).
+  // Unicast views of every rank's input window (direct variant; unaligned tail)
+  // and output window (direct variant).
   unsigned char* peer_in[kMaxRanks];
+  unsigned char* peer_out[kMaxRanks];
   uint64_t window_elems;
   uint64_t seq;
   uint64_t timeout_ns;

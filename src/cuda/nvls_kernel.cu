@@ -11,6 +11,14 @@
 // window by window inside this same kernel (copy in -> barrier -> reduce ->
 // barrier -> copy out), with the copies of CTA b on every rank covering
 // exactly what CTA b of the other ranks reduces, so the barriers are per CTA.
+//
+// The same kernel without multimem is the "direct" two-shot algorithm: a rank
+// loads its shard from every peer's buffer over NVLink (plain 16-byte peer
+// loads, summed in rank order), scales it and stores it into every peer's
+// output buffer.  It needs no multicast (and can therefore be emulated with
+// several ranks on one GPU), moves 2*S*(ws-1)/ws per direction like the ring
+// but in two synchronisation steps instead of 2*(ws-1), and supports every
+// element type.
 #include <cooperative_groups.h>
 
 #include <cstdlib>
@@ -25,7 +33,11 @@ namespace dev {
 
 constexpr int kNvlsThreads = 512;
 
-template <typename T> struct Multimem;
+template <typename T> struct Multimem {
+  // Types without a multimem form (integers, fp64) only run the direct variant.
+  __device__ __forceinline__ static uint4 LdReduce(const void*) { return make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ static void St(void*, uint4) {}
+};
 
 template <> struct Multimem<float> {
   __device__ __forceinline__ static uint4 LdReduce(const void* mc) {
@@ -106,7 +118,7 @@ __device__ inline bool CrossRankBarrier(const NvlsParams& p, const WaitCtx& w, i
   return *s_stop == 0;
 }
 
-template <typename T, int U>
+template <typename T, int U, bool kMultimem>
 __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_constant__ NvlsParams p0, const NvlsParams* __restrict__ emu) {
   using A = typename Acc<T>::type;
   constexpr int kVecElems = 16 / static_cast<int>(sizeof(T));
@@ -145,11 +157,18 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
     if (p.stage_in) {
       const uint4* src = reinterpret_cast<const uint4*>(sendbuf + w0);
       uint4* dst = reinterpret_cast<uint4*>(p.local_in);
+      const bool src_aligned = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
       for (int s = 0; s < p.world_size; ++s) {
         uint64_t sb, se, b, e;
         SubRange(0, nvec, s, p.world_size, &sb, &se);
         SubRange(sb, se, cta, ncta, &b, &e);
-        CopyVectors<false>(dst, src, b, e);
+        if (src_aligned) {
+          CopyVectors<false>(dst, src, b, e);
+        } else {
+          // A user buffer that is only element-aligned: element by element.
+          T* dt = reinterpret_cast<T*>(p.local_in);
+          for (uint64_t i = b * kVecElems + threadIdx.x; i < e * kVecElems; i += blockDim.x) dt[i] = sendbuf[w0 + i];
+        }
       }
       if (cta == 0) {
         T* dt = reinterpret_cast<T*>(p.local_in);
@@ -165,26 +184,52 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
       SubRange(sb, se, cta, ncta, &b, &e);
       const unsigned char* mi = p.mc_in + win_bytes_off;
       unsigned char* mo = p.mc_out + wout_bytes_off;
-      for (uint64_t i = b + threadIdx.x; i < e; i += static_cast<uint64_t>(blockDim.x) * U) {
-        uint4 v[U];
+      if (kMultimem) {
+        for (uint64_t i = b + threadIdx.x; i < e; i += static_cast<uint64_t>(blockDim.x) * U) {
+          uint4 v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
-          if (idx < e) v[u] = Multimem<T>::LdReduce(mi + idx * 16);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
-          if (idx < e) {
-            if (do_scale) {
-              A acc[kVecElems];
-              VecIO<T>::Load(v[u], acc);
-#pragma unroll
-              for (int k = 0; k < kVecElems; ++k) acc[k] = ScaleAcc<A>(acc[k], p.scale);
-              v[u] = VecIO<T>::Store(acc);
-            }
-            Multimem<T>::St(mo + idx * 16, v[u]);
+          for (int u = 0; u < U; ++u) {
+            const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+            if (idx < e) v[u] = Multimem<T>::LdReduce(mi + idx * 16);
           }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+            if (idx < e) {
+              if (do_scale) {
+                A acc[kVecElems];
+                VecIO<T>::Load(v[u], acc);
+#pragma unroll
+                for (int k = 0; k < kVecElems; ++k) acc[k] = ScaleAcc<A>(acc[k], p.scale);
+                v[u] = VecIO<T>::Store(acc);
+              }
+              Multimem<T>::St(mo + idx * 16, v[u]);
+            }
+          }
+        }
+      } else {
+        // Direct variant: one 16-byte load per peer, all issued before the
+        // adds; the sum runs in rank order, so whoever reduces a shard, the
+        // bits are the same.
+        const int ws = p.world_size;
+        for (uint64_t i = b + threadIdx.x; i < e; i += blockDim.x) {
+          uint4 v[kMaxRanks];
+#pragma unroll
+          for (int q = 0; q < kMaxRanks; ++q)
+            if (q < ws) v[q] = Ld16Strong(p.peer_in[q] + win_bytes_off + i * 16);
+          A acc[kVecElems];
+          VecIO<T>::Load(v[0], acc);
+#pragma unroll
+          for (int q = 1; q < kMaxRanks; ++q)
+            if (q < ws) VecIO<T>::Add(v[q], acc);
+          if (do_scale) {
+#pragma unroll
+            for (int k = 0; k < kVecElems; ++k) acc[k] = ScaleAcc<A>(acc[k], p.scale);
+          }
+          const uint4 r = VecIO<T>::Store(acc);
+#pragma unroll
+          for (int q = 0; q < kMaxRanks; ++q)
+            if (q < ws) St16(p.peer_out[q] + wout_bytes_off + i * 16, r);
         }
       }
     }
@@ -210,11 +255,17 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
     if (p.stage_out) {
       const uint4* src = reinterpret_cast<const uint4*>(p.local_out);
       uint4* dst = reinterpret_cast<uint4*>(recvbuf + w0);
+      const bool dst_aligned = (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
       for (int s = 0; s < p.world_size; ++s) {
         uint64_t sb, se, b, e;
         SubRange(0, nvec, s, p.world_size, &sb, &se);
         SubRange(sb, se, cta, ncta, &b, &e);
-        CopyVectors<true>(dst, src, b, e);
+        if (dst_aligned) {
+          CopyVectors<true>(dst, src, b, e);
+        } else {
+          const T* st = reinterpret_cast<const T*>(p.local_out);
+          for (uint64_t i = b * kVecElems + threadIdx.x; i < e * kVecElems; i += blockDim.x) recvbuf[w0 + i] = LdScalarStrong<T>(st + i);
+        }
       }
     }
   }
@@ -227,16 +278,21 @@ static int EnvInt(const char* name, int dflt) {
   return s ? atoi(s) : dflt;
 }
 
-template <typename T, int U>
+template <typename T, int U, bool kMultimem>
 static cudaError_t LaunchNvlsU(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, int threads, cudaStream_t stream) {
   dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(emu != nullptr ? emu_ranks : 1));
   if (emu != nullptr) {
     void* args[] = {const_cast<NvlsParams*>(&p), &emu};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::NvlsKernel<T, U>), grid, dim3(threads), args, 0, stream);
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::NvlsKernel<T, U, kMultimem>), grid, dim3(threads), args, 0, stream);
   }
-  dev::NvlsKernel<T, U><<<grid, threads, 0, stream>>>(p, nullptr);
+  dev::NvlsKernel<T, U, kMultimem><<<grid, threads, 0, stream>>>(p, nullptr);
   return cudaGetLastError();
 }
+
+template <typename T> struct HasMultimem { static constexpr bool value = false; };
+template <> struct HasMultimem<float> { static constexpr bool value = true; };
+template <> struct HasMultimem<__half> { static constexpr bool value = true; };
+template <> struct HasMultimem<__nv_bfloat16> { static constexpr bool value = true; };
 
 template <typename T>
 static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
@@ -244,18 +300,28 @@ static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, i
   static const int unroll = EnvInt("IBCOMM_NVLS_UNROLL", 4);
   static const int threads_env = EnvInt("IBCOMM_NVLS_THREADS", dev::kNvlsThreads);
   const int threads = (threads_env >= 64 && threads_env <= dev::kNvlsThreads && threads_env % 32 == 0) ? threads_env : dev::kNvlsThreads;
-  if (unroll == 8) return LaunchNvlsU<T, 8>(p, emu, emu_ranks, blocks, threads, stream);
-  if (unroll == 2) return LaunchNvlsU<T, 2>(p, emu, emu_ranks, blocks, threads, stream);
-  return LaunchNvlsU<T, 4>(p, emu, emu_ranks, blocks, threads, stream);
+  if (!p.use_multimem) return LaunchNvlsU<T, 4, false>(p, emu, emu_ranks, blocks, threads, stream);
+  if constexpr (HasMultimem<T>::value) {
+    if (unroll == 8) return LaunchNvlsU<T, 8, true>(p, emu, emu_ranks, blocks, threads, stream);
+    if (unroll == 2) return LaunchNvlsU<T, 2, true>(p, emu, emu_ranks, blocks, threads, stream);
+    return LaunchNvlsU<T, 4, true>(p, emu, emu_ranks, blocks, threads, stream);
+  } else {
+    return cudaErrorInvalidValue;
+  }
 }
 
 cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
-  switch (static_cast<DType>(p.dtype)) {
+  const DType t = static_cast<DType>(p.dtype);
+  if (p.use_multimem && !(t == DType::kFloat32 || t == DType::kFloat16 || t == DType::kBFloat16)) return cudaErrorInvalidValue;
+  switch (t) {
     case DType::kFloat32: return LaunchNvlsTyped<float>(p, emu, emu_ranks, blocks, stream);
     case DType::kFloat16: return LaunchNvlsTyped<__half>(p, emu, emu_ranks, blocks, stream);
     case DType::kBFloat16: return LaunchNvlsTyped<__nv_bfloat16>(p, emu, emu_ranks, blocks, stream);
-    default: return cudaErrorInvalidValue;
+    case DType::kFloat64: return LaunchNvlsTyped<double>(p, emu, emu_ranks, blocks, stream);
+    case DType::kInt32: return LaunchNvlsTyped<int>(p, emu, emu_ranks, blocks, stream);
+    case DType::kInt64: return LaunchNvlsTyped<long long>(p, emu, emu_ranks, blocks, stream);
   }
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace ibcomm

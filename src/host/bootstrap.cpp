@@ -78,6 +78,8 @@ void ConnectAll(Communicator* comm, const BootstrapEnv& env, const std::string& 
       std::this_thread::sleep_for(std::chrono::milliseconds(1));
     }
   }
+  // Nobody may leave (and take its endpoints away) before everybody attached.
+  comm->Barrier();
 }
 
 long long SumOverRanks(Communicator* comm, long long value) {

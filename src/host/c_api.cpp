@@ -332,6 +332,16 @@ int ibcomm_emu_set_silent_rank(ibcomm_emu* w, int rank) {
   });
 }
 
+int ibcomm_emu_set_direct_staging(ibcomm_emu* w, int on) {
+  return Guard([&] {
+#ifdef USE_CUDA
+    w->world.SetDirectStaging(on != 0);
+#else
+    (void)w; (void)on;
+#endif
+  });
+}
+
 int ibcomm_emu_last_status(ibcomm_emu* w, ibcomm_status_report* out) {
   return Guard([&] {
 #ifdef USE_CUDA

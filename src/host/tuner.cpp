@@ -48,6 +48,7 @@ void LoadRules() {
     else if (n == "rabenseifner") a = Algo::kRabenseifner;
     else if (n == "nvls") a = Algo::kNvls;
     else if (n == "oneshot") a = Algo::kOneShot;
+    else if (n == "direct") a = Algo::kDirect;
     else continue;
     g_rules.push_back(Rule{ws, static_cast<size_t>(mb), a, ch});
   }
@@ -65,7 +66,9 @@ int ChooseChannels(Algo algo, size_t bytes, int world_size, int max_channels) {
       ch = static_cast<int>(std::min<size_t>(16, (bytes + (32u << 10) - 1) / (32u << 10)));
       break;
     case Algo::kNvls:
-      // The switch does the math; enough CTAs to keep ~8 MiB in flight.
+    case Algo::kDirect:
+      // The switch (or the peers' memory) does most of the work; enough CTAs
+      // to keep several MiB in flight.
       ch = static_cast<int>(std::min<size_t>(kMaxChannels, std::max<size_t>(1, bytes / (128u << 10))));
       break;
     default: {
@@ -88,12 +91,14 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
     int ch = r.channels > 0 ? std::min(r.channels, max_channels) : ChooseChannels(r.algo, bytes, world_size, max_channels);
     return TunerChoice{r.algo, ch};
   }
-  (void)zero_copy;
   Algo a;
   if (bytes <= (256u << 10)) {
     a = Algo::kOneShot;
+  } else if (world_size == 2 && zero_copy) {
+    // Two ranks: peer loads + peer stores move S per direction in two steps;
+    // the switch path would move 1.5 S.
+    a = Algo::kDirect;
   } else if (nvls_available && world_size > 2) {
-    // Two ranks: the switch path moves 1.5 S per direction, the ring 1.0 S.
     a = Algo::kNvls;
   } else if (bytes <= (8u << 20) && util::GetExpOfTwo(static_cast<uint64_t>(world_size)) != 0) {
     a = Algo::kRabenseifner;

@@ -47,7 +47,7 @@ def close(out, want, dtype, wire=None):
 
 def case_allreduce(comm):
     info = comm.device_info(connect=True)
-    algos = ["ring", "rabenseifner", "oneshot", "auto"] + (["nvls"] if info["nvls"] else [])
+    algos = ["ring", "rabenseifner", "oneshot", "direct", "auto"] + (["nvls"] if info["nvls"] else [])
     for algo in algos:
         for dtype in (torch.float32, torch.bfloat16, torch.int32):
             if algo == "nvls" and dtype == torch.int32:

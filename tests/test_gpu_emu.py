@@ -125,6 +125,30 @@ def test_small_staging_forces_slot_reuse(algo):
                 check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
 
 
+@pytest.mark.parametrize("ws", [2, 3, 4, 5, 8])
+def test_direct_two_shot(ws):
+    # The two-shot kernel with peer loads/stores (the code path of the NVLS
+    # kernel minus multimem): in place on the ranks' buffers, and staged
+    # through pool windows (1 MiB pool = 512 KiB windows, so 4 MiB messages
+    # take several rounds).
+    w = world(ws, 1 << 20, 1 << 20)
+    for staged in (False, True):
+        w.set_direct_staging(staged)
+        for n in (ws, 1000, 65536 + 3, 1 << 20):
+            for dtype in (torch.float32, torch.bfloat16, torch.int32):
+                ins = make_inputs(ws, n, dtype, seed=n + ws)
+                want = reference(ins, 0.5 if dtype != torch.int32 else 1.0, dtype)
+                outs = [torch.zeros(n, device="cuda", dtype=dtype) for _ in range(ws)]
+                w.allreduce(ins, outs, algo="direct", scale=0.5 if dtype != torch.int32 else 1.0)
+                check(outs, want, dtype, ws)
+        # in place
+        bufs = make_inputs(ws, 50001, torch.float32, seed=3)
+        want = reference(bufs, 1.0, torch.float32)
+        w.allreduce(bufs, None, algo="direct")
+        check(bufs, want, torch.float32, ws)
+    w.set_direct_staging(False)
+
+
 def test_unaligned_buffers_take_the_scalar_path():
     ws = 3
     w = world(ws)
@@ -133,7 +157,7 @@ def test_unaligned_buffers_take_the_scalar_path():
     ins = [t[1:] for t in base]  # 4-byte aligned only
     outs_base = [torch.zeros(n + 3, device="cuda") for _ in range(ws)]
     outs = [t[3:] for t in outs_base]
-    for algo in ("ring", "rabenseifner", "oneshot"):
+    for algo in ("ring", "rabenseifner", "oneshot", "direct"):
         w.allreduce(ins, outs, algo=algo)
         check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
 
@@ -146,7 +170,7 @@ def test_repeated_calls_mixed_algorithms():
     outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
     want = reference(ins, 1.0, torch.float32)
     for it in range(30):
-        algo = ("ring", "oneshot", "rabenseifner")[it % 3]
+        algo = ("ring", "oneshot", "rabenseifner", "direct")[it % 4]
         w.allreduce(ins, outs, algo=algo, sync=False)
     torch.cuda.synchronize()
     check(outs, want, torch.float32, ws)
