@@ -212,15 +212,17 @@ def main() -> int:
     max_err = float((recvbuf[:check_n].double() - want).abs().max().item())
     ok = max_err <= 1e-5 * world
 
-    launches_before = comm.device_info()["kernel_launches"]
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = time_steps(step, args.steps, args.warmup)
-    clocks = sampler.stop() if rank == 0 else {}
+    for _ in range(args.warmup):
+        step()
+    # kernels of this library launched by the timed steps (the library counts them)
+    launches_before = comm.device_info()["kernel_launches"]
+    ms = time_steps(step, args.steps, 0)
     info = comm.device_info()
-    # kernel launches inside the timed region only (warm-up excluded)
-    launches = (info["kernel_launches"] - launches_before) * args.steps // (args.steps + args.warmup)
+    launches = info["kernel_launches"] - launches_before
+    clocks = sampler.stop() if rank == 0 else {}
     comm.check()
     value = busbw_gbs(nbytes, ms / 1e3, world)
 
@@ -246,7 +248,8 @@ def main() -> int:
         plain_out = torch.empty_like(plain_in)
         k, w = max(3, args.steps // 2), 3
         if world > 1:
-            candidates = [("ring", plain_in, plain_out), ("rabenseifner", plain_in, plain_out)]
+            candidates = [("ring", plain_in, plain_out), ("rabenseifner", plain_in, plain_out),
+                          ("direct", plain_in, plain_out), ("direct_zero_copy", sendbuf, recvbuf)]
             if info["nvls"]:
                 candidates += [("nvls", plain_in, plain_out)]          # staged through the pool
                 candidates += [("nvls_zero_copy", sendbuf, recvbuf)]   # symmetric buffers
@@ -356,9 +359,11 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
         if world > 1:
             if size <= (256 << 10):
                 algos.append(("oneshot", plain_in, plain_out))
-            algos += [("ring", plain_in, plain_out), ("rabenseifner", plain_in, plain_out)]
+            algos += [("ring", plain_in, plain_out), ("rabenseifner", plain_in, plain_out),
+                      ("direct", plain_in, plain_out), ("direct_zero_copy", sym_in, sym_out)]
             if info["nvls"]:
                 algos += [("nvls", plain_in, plain_out), ("nvls_zero_copy", sym_in, sym_out)]
+            algos.append(("auto_plain", plain_in, plain_out))
             algos.append(("auto", sym_in, sym_out))
         else:
             algos.append(("auto", plain_in, plain_out))

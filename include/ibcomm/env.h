@@ -17,14 +17,15 @@
 namespace ibcomm {
 namespace env {
 
-constexpr int kDefaultNumCudaStream = 64;
+constexpr int kDefaultNumCudaStream = 128;
 constexpr size_t kDefaultPoolPreAlloc = 64ull << 20;
 constexpr size_t kDefaultWorkGpuMemory = 32ull << 20;
 constexpr int kDefaultTimeoutMs = 10000;
 
 // > 0 when set, 0 when unset.  <= 0 while set is INVALID_ARGUMENT (exit 1).
 int64_t ReadChunkSize();
-// 1..1024, default 64.  Outside the range is INVALID_ARGUMENT.
+// 1..1024, default 128 (the value in the reference's code, memory_pool.h:82;
+// its README says 64).  Outside the range is INVALID_ARGUMENT.
 int ReadNumCudaStream();
 // 4..1 GiB, default 64 MiB.  Outside the range is INVALID_ARGUMENT.
 size_t ReadPreAllocSize();

@@ -254,7 +254,9 @@ static int ExecThreads() {
 template <typename T, typename W>
 static cudaError_t Launch(const ExecParams& p, const ExecParams* emu, int emu_ranks, int channels, cudaStream_t stream) {
   dim3 grid(static_cast<unsigned>(channels), static_cast<unsigned>(emu != nullptr ? emu_ranks : 1));
-  const int kThreads = ExecThreads();
+  // Beyond one CTA per SM, two smaller CTAs share an SM: while one waits for a
+  // flag, the other streams.
+  const int kThreads = (channels > 148 && ExecThreads() > 256) ? 256 : ExecThreads();
   if (emu != nullptr) {
     // Ranks sharing one GPU wait on each other inside this launch: it must be
     // cooperative so the runtime refuses a grid that cannot be co-resident.

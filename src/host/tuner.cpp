@@ -66,14 +66,18 @@ int ChooseChannels(Algo algo, size_t bytes, int world_size, int max_channels) {
       ch = static_cast<int>(std::min<size_t>(16, (bytes + (32u << 10) - 1) / (32u << 10)));
       break;
     case Algo::kNvls:
+      // The switch does the math; 32-64 CTAs saturate it (more only add
+      // barrier traffic).
+      ch = static_cast<int>(std::min<size_t>(64, std::max<size_t>(1, bytes / (128u << 10))));
+      break;
     case Algo::kDirect:
-      // The switch (or the peers' memory) does most of the work; enough CTAs
-      // to keep several MiB in flight.
-      ch = static_cast<int>(std::min<size_t>(kMaxChannels, std::max<size_t>(1, bytes / (128u << 10))));
+      // Peer loads are latency-bound: as many CTAs as there are SMs to spare.
+      ch = static_cast<int>(std::min<size_t>(128, std::max<size_t>(1, bytes / (128u << 10))));
       break;
     default: {
       // Ring / Rabenseifner: a chunk is bytes / (4 * ws); give every channel
-      // at least 16 KiB of it per step.
+      // at least 16 KiB of it per step.  More channels than needed to fill the
+      // links hide the flag round trips of the others.
       size_t chunk = bytes / static_cast<size_t>(4 * std::max(1, world_size));
       ch = static_cast<int>(std::min<size_t>(kMaxChannels, std::max<size_t>(1, chunk / (16u << 10))));
       break;
@@ -91,17 +95,26 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
     int ch = r.channels > 0 ? std::min(r.channels, max_channels) : ChooseChannels(r.algo, bytes, world_size, max_channels);
     return TunerChoice{r.algo, ch};
   }
+  // Built-in table, from bus-bandwidth sweeps on 2 and 8 B200 (profiles/).
   Algo a;
-  if (bytes <= (256u << 10)) {
+  if (zero_copy) {
+    // Buffers every peer maps (symmetric memory): nothing is staged.
+    if (bytes <= (16u << 10)) {
+      a = Algo::kOneShot;
+    } else if (nvls_available && (world_size > 2 || bytes <= (4u << 20))) {
+      // In-switch reduction: 1 + 1/ws of the message per direction.  With two
+      // ranks that is 1.5 S against the direct algorithm's 1.0 S, so large
+      // messages go direct there.
+      a = Algo::kNvls;
+    } else {
+      a = bytes <= (256u << 10) ? Algo::kOneShot : Algo::kDirect;
+    }
+  } else if (bytes <= (256u << 10)) {
     a = Algo::kOneShot;
-  } else if (world_size == 2 && zero_copy) {
-    // Two ranks: peer loads + peer stores move S per direction in two steps;
-    // the switch path would move 1.5 S.
-    a = Algo::kDirect;
-  } else if (nvls_available && world_size > 2) {
-    a = Algo::kNvls;
-  } else if (bytes <= (8u << 20) && util::GetExpOfTwo(static_cast<uint64_t>(world_size)) != 0) {
-    a = Algo::kRabenseifner;
+  } else if (nvls_available && world_size > 2 && bytes <= (128u << 20)) {
+    a = Algo::kNvls;  // staged through the pool inside the kernel
+  } else if (bytes <= (32u << 20)) {
+    a = Algo::kDirect;  // staged; two synchronisation steps
   } else {
     a = Algo::kRing;
   }
