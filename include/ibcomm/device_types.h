@@ -41,7 +41,17 @@ struct ControlPage {
   uint64_t p2p_credit[kMaxRanks];
   // Set (to the call sequence) by any rank that gave up; polled by waiters.
   uint64_t abort_seq;
-  uint64_t pad_[7];
+  // Written only by this rank's own kernels: the number of collectives it has
+  // completed, and how many CTAs of the running one have finished.  Every
+  // collective kernel takes its sequence number from here (call_seq + 1) and
+  // the last CTA to finish publishes it, so a kernel's parameters carry
+  // nothing that changes from call to call and a captured CUDA graph of
+  // collectives can be replayed.  All ranks issue the same collectives in the
+  // same order, so their counters agree.
+  uint64_t call_seq;
+  uint32_t done_ctas;
+  uint32_t pad32_;
+  uint64_t pad_[5];
   // One-shot allreduce flags: [parity][cta][source].
   uint64_t oneshot_flag[2][kMaxChannels][kMaxRanks];
 };
@@ -157,7 +167,6 @@ struct ExecParams {
   int32_t num_ops;
   int32_t trace_capacity;  // records per channel, 0 = tracing off
   StageLayout stage;
-  uint64_t seq;          // call sequence number (same on every rank)
   uint64_t timeout_ns;   // limit of every wait
   DeviceStatus* status;  // device memory, fetched by the host after a failure
   uint32_t* doorbell;    // host-mapped word a failing kernel sets non-zero

@@ -110,8 +110,6 @@ class DeviceContext {
   RankResources rr_;
   StatusBlock status_;
   ProgramCache cache_;
-  uint64_t seq_ = 0;
-  uint64_t oneshot_calls_ = 0;
   uint64_t calls_ = 0;
   uint64_t kernel_launches_ = 0;
   int last_algo_ = 0, last_channels_ = 0;
@@ -323,18 +321,30 @@ cudaStream_t DeviceContext::StreamFor(const CudaAllreduceOptions& opts) {
   return (opts.use_stream || opts.stream != nullptr) ? static_cast<cudaStream_t>(opts.stream) : stream_;
 }
 
+static bool IsCapturing(cudaStream_t stream) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return st != cudaStreamCaptureStatusNone;
+}
+
 void DeviceContext::OrderAfterPrevious(cudaStream_t stream) {
   // Collectives of one communicator reuse the same staging memory and flags:
   // the next one may only start when the previous one has finished, also when
-  // the caller switches streams.
+  // the caller switches streams.  Inside a stream capture the graph's own
+  // edges order the collectives; the caller keeps them on one stream.
+  if (IsCapturing(stream)) return;
   if (have_last_ && last_stream_ != stream) CUDACHECK(cudaStreamWaitEvent(stream, last_done_, 0));
 }
 
 void DeviceContext::MarkIssued(cudaStream_t stream) {
+  ++calls_;
+  if (IsCapturing(stream)) return;
   CUDACHECK(cudaEventRecord(last_done_, stream));
   last_stream_ = stream;
   have_last_ = true;
-  ++calls_;
 }
 
 void DeviceContext::Finish(cudaStream_t stream, bool async) {
@@ -369,7 +379,6 @@ void DeviceContext::RunCopy(DType dtype, const void* sendbuf, void* recvbuf, siz
 void DeviceContext::RunProgram(Algo algo, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale,
                                int channels, cudaStream_t stream) {
   const CachedProgram& cp = cache_.Get(algo, rank_, ws_, n, dtype, wire, layout_, scale != 1.0);
-  const uint64_t seq = ++seq_;
   DeviceTraceRec* trace = nullptr;
   int cap = 0;
   if (d_trace_ != nullptr && channels <= trace_channels_) {
@@ -382,7 +391,7 @@ void DeviceContext::RunProgram(Algo algo, DType dtype, DType wire, const void* s
     clock_gettime(CLOCK_MONOTONIC_RAW, &pt.host_launch);
     pending_trace_.push_back(pt);
   }
-  ExecParams p = MakeExecParams(rr_, cp, dtype, wire, sendbuf, recvbuf, n, scale, seq,
+  ExecParams p = MakeExecParams(rr_, cp, dtype, wire, sendbuf, recvbuf, n, scale,
                                 static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull, trace, cap);
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
   CUDACHECK(LaunchExecKernel(p, nullptr, 1, channels, stream));
@@ -392,9 +401,7 @@ void DeviceContext::RunProgram(Algo algo, DType dtype, DType wire, const void* s
 
 void DeviceContext::RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
                                cudaStream_t stream) {
-  const uint64_t seq = ++seq_;
-  const int parity = static_cast<int>(oneshot_calls_++ & 1);
-  OneShotParams p = MakeOneShotParams(rr_, dtype, sendbuf, recvbuf, n, scale, seq, parity,
+  OneShotParams p = MakeOneShotParams(rr_, dtype, sendbuf, recvbuf, n, scale,
                                       static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull);
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
   CUDACHECK(LaunchOneShotKernel(p, nullptr, 1, channels, stream));
@@ -417,7 +424,6 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   p.recvbuf = recvbuf;
   p.len_elements = n;
   p.scale = scale;
-  p.seq = ++seq_;
   p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
   p.status = rr_.d_status;
   p.doorbell = rr_.d_doorbell;

@@ -19,8 +19,6 @@ struct EmuWorld::Impl {
   ProgramCache cache;
   void* d_params = nullptr;  // parameter blocks of one launch
   size_t d_params_bytes = 0;
-  uint64_t seq = 0;
-  uint64_t oneshot_calls = 0;
   int timeout_ms = env::kDefaultTimeoutMs;
   int max_blocks = 0;
   int last_channels = 0;
@@ -114,7 +112,6 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
   if (algo == Algo::kNvls)
     IBCOMM_FAIL(NOT_SUPPORTED, "Algorithm 'nvls' needs NVSwitch multicast between GPUs; it cannot be emulated on one GPU.\n");
   const uint64_t timeout_ns = static_cast<uint64_t>(m.timeout_ms) * 1000000ull;
-  const uint64_t seq = ++m.seq;
   const int cap = std::max(1, m.max_blocks / m.ws);
 
   if (algo == Algo::kDirect) {
@@ -136,7 +133,6 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
       p.recvbuf = recvbufs[static_cast<size_t>(r)];
       p.len_elements = n;
       p.scale = scale;
-      p.seq = seq;
       p.timeout_ns = timeout_ns;
       p.status = rr.d_status;
       p.doorbell = rr.d_doorbell;
@@ -169,11 +165,10 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
     if (bytes > m.layout.oneshot_slot_bytes)
       IBCOMM_FAIL(INVALID_ARGUMENT, "One-shot allreduce handles at most %llu bytes (got %zu).\n",
                   static_cast<unsigned long long>(m.layout.oneshot_slot_bytes), bytes);
-    const int parity = static_cast<int>(m.oneshot_calls++ & 1);
     std::vector<OneShotParams> ps;
     for (int r = 0; r < m.ws; ++r)
       ps.push_back(MakeOneShotParams(m.ranks[static_cast<size_t>(r)], dtype, sendbufs[static_cast<size_t>(r)],
-                                     recvbufs[static_cast<size_t>(r)], n, scale, seq, parity, timeout_ns));
+                                     recvbufs[static_cast<size_t>(r)], n, scale, timeout_ns));
     int ch = channels > 0 ? channels : ChooseChannels(Algo::kOneShot, bytes, m.ws, kMaxChannels);
     ch = std::min(ch, cap);
     void* d = m.Params(ps.size() * sizeof(OneShotParams));
@@ -186,7 +181,7 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
     for (int r = 0; r < m.ws; ++r) {
       const CachedProgram& cp = m.cache.Get(algo, r, m.ws, n, dtype, wire, m.layout, scale != 1.0);
       ps.push_back(MakeExecParams(m.ranks[static_cast<size_t>(r)], cp, dtype, wire, sendbufs[static_cast<size_t>(r)],
-                                  recvbufs[static_cast<size_t>(r)], n, scale, seq, timeout_ns, nullptr, 0));
+                                  recvbufs[static_cast<size_t>(r)], n, scale, timeout_ns, nullptr, 0));
       if (r == m.silent_rank) ps.back().num_ops = 0;
     }
     int ch = channels > 0 ? channels : ChooseChannels(algo, bytes, m.ws, kMaxChannels);

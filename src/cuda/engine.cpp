@@ -153,7 +153,7 @@ const CachedProgram& ProgramCache::Get(Algo algo, int rank, int world_size, size
 }
 
 ExecParams MakeExecParams(const RankResources& rr, const CachedProgram& cp, DType dtype, DType wire, const void* sendbuf,
-                          void* recvbuf, size_t len_elements, double scale, uint64_t seq, uint64_t timeout_ns,
+                          void* recvbuf, size_t len_elements, double scale, uint64_t timeout_ns,
                           DeviceTraceRec* trace, int trace_capacity) {
   ExecParams p;
   memset(&p, 0, sizeof(p));
@@ -170,7 +170,6 @@ ExecParams MakeExecParams(const RankResources& rr, const CachedProgram& cp, DTyp
   p.num_ops = static_cast<int32_t>(cp.prog.ops.size());
   p.trace_capacity = trace_capacity;
   p.stage = cp.prog.stage;
-  p.seq = seq;
   p.timeout_ns = timeout_ns;
   p.status = rr.d_status;
   p.doorbell = rr.d_doorbell;
@@ -179,13 +178,12 @@ ExecParams MakeExecParams(const RankResources& rr, const CachedProgram& cp, DTyp
 }
 
 OneShotParams MakeOneShotParams(const RankResources& rr, DType dtype, const void* sendbuf, void* recvbuf,
-                                size_t len_elements, double scale, uint64_t seq, int parity, uint64_t timeout_ns) {
+                                size_t len_elements, double scale, uint64_t timeout_ns) {
   OneShotParams p;
   memset(&p, 0, sizeof(p));
   p.rank = rr.rank;
   p.world_size = rr.world_size;
   p.dtype = static_cast<int32_t>(dtype);
-  p.parity = parity;
   p.peers = rr.peers;
   p.sendbuf = sendbuf;
   p.recvbuf = recvbuf;
@@ -193,7 +191,6 @@ OneShotParams MakeOneShotParams(const RankResources& rr, DType dtype, const void
   p.scale = scale;
   p.slot_offset = rr.layout.oneshot_offset;
   p.slot_bytes = rr.layout.oneshot_slot_bytes;
-  p.seq = seq;
   p.timeout_ns = timeout_ns;
   p.status = rr.d_status;
   p.doorbell = rr.d_doorbell;

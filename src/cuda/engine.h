@@ -57,11 +57,11 @@ class ProgramCache {
 };
 
 ExecParams MakeExecParams(const RankResources& rr, const CachedProgram& cp, DType dtype, DType wire, const void* sendbuf,
-                          void* recvbuf, size_t len_elements, double scale, uint64_t seq, uint64_t timeout_ns,
+                          void* recvbuf, size_t len_elements, double scale, uint64_t timeout_ns,
                           DeviceTraceRec* trace, int trace_capacity);
 
 OneShotParams MakeOneShotParams(const RankResources& rr, DType dtype, const void* sendbuf, void* recvbuf,
-                                size_t len_elements, double scale, uint64_t seq, int parity, uint64_t timeout_ns);
+                                size_t len_elements, double scale, uint64_t timeout_ns);
 
 // Formats a failure report.
 std::string DescribeStatus(const DeviceStatus& st);

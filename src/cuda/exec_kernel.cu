@@ -177,41 +177,30 @@ __device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch) {
   if (done < hi) ScalarLoop<T, W>(op, sendbuf, recvbuf, stage_in, stage_out, done, hi, p.scale);
 }
 
+// Body of the executor for one CTA; returns when the program is done or a wait gave up.
 template <typename T, typename W>
-__global__ void __launch_bounds__(kExecThreads, 1)
-ExecKernel(const __grid_constant__ ExecParams p0, const ExecParams* __restrict__ emu) {
-  __shared__ ExecParams p;
-  __shared__ int s_stop;
+__device__ void ExecBody(const ExecParams& p, uint64_t seq, int* s_stop) {
   const int ch = blockIdx.x, nch = gridDim.x;
-  {
-    const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y)
-                                           : reinterpret_cast<const uint32_t*>(&p0);
-    for (unsigned i = threadIdx.x; i < sizeof(ExecParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
-    if (threadIdx.x == 0) s_stop = 0;
-  }
-  __syncthreads();
-  if (p.world_size <= 1 || p.num_ops <= 0) return;
-
   WaitCtx w;
   w.peers = &p.peers;
   w.status = p.status;
   w.doorbell = p.doorbell;
-  w.seq = p.seq;
+  w.seq = seq;
   w.timeout_ns = p.timeout_ns;
   w.rank = p.rank;
   w.world_size = p.world_size;
   w.channel = ch;
-  const uint64_t base = p.seq << 32;
+  const uint64_t base = seq << 32;
   ControlPage* const me = Ctl(p.peers, p.rank);
 
   // Entry barrier per channel: every peer's channel `ch` has started this
   // call, hence finished the previous one, so staging slots are free.
   if (threadIdx.x < p.world_size && threadIdx.x != p.rank) {
     StReleaseSys(&Ctl(p.peers, threadIdx.x)->bar[ch][p.rank], base | 1u);
-    if (!WaitGE(&me->bar[ch][threadIdx.x], base | 1u, w, kWaitBarrier, threadIdx.x, -1)) s_stop = 1;
+    if (!WaitGE(&me->bar[ch][threadIdx.x], base | 1u, w, kWaitBarrier, threadIdx.x, -1)) *s_stop = 1;
   }
   __syncthreads();
-  if (s_stop) return;
+  if (*s_stop) return;
 
   DeviceTraceRec* trace = (p.trace != nullptr && p.trace_capacity > 0) ? p.trace + static_cast<size_t>(ch) * p.trace_capacity : nullptr;
 
@@ -222,11 +211,11 @@ ExecKernel(const __grid_constant__ ExecParams p0, const ExecParams* __restrict__
       if (op.wait_in != 0) ok = WaitGE(&me->inflag[ch][op.peer_in], base | op.wait_in, w, kWaitData, op.peer_in, oi);
       if (ok && op.wait_credit != 0)
         ok = WaitGE(&me->credit[ch][op.peer_out], base | op.wait_credit, w, kWaitCredit, op.peer_out, oi);
-      if (!ok) s_stop = 1;
+      if (!ok) *s_stop = 1;
       if (trace != nullptr && oi < p.trace_capacity) trace[oi].t_wait_done = GlobalTimerNs();
     }
     __syncthreads();
-    if (s_stop) return;
+    if (*s_stop) return;
     RunOpData<T, W>(op, p, ch, nch);
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -238,6 +227,26 @@ ExecKernel(const __grid_constant__ ExecParams p0, const ExecParams* __restrict__
       if (trace != nullptr && oi < p.trace_capacity) trace[oi].t_done = GlobalTimerNs();
     }
   }
+}
+
+template <typename T, typename W>
+__global__ void __launch_bounds__(kExecThreads, 1)
+ExecKernel(const __grid_constant__ ExecParams p0, const ExecParams* __restrict__ emu) {
+  __shared__ ExecParams p;
+  __shared__ int s_stop;
+  __shared__ uint64_t s_seq;
+  {
+    const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y)
+                                           : reinterpret_cast<const uint32_t*>(&p0);
+    for (unsigned i = threadIdx.x; i < sizeof(ExecParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
+    if (threadIdx.x == 0) s_stop = 0;
+  }
+  __syncthreads();
+  if (p.world_size <= 1) return;
+  const uint64_t seq = BeginCollective(p.peers, p.rank, &s_seq);
+  // num_ops <= 0: this rank sits the call out (test hook), but still counts it.
+  if (p.num_ops > 0) ExecBody<T, W>(p, seq, &s_stop);
+  EndCollective(p.peers, p.rank, seq, gridDim.x);
 }
 
 }  // namespace dev

@@ -67,6 +67,31 @@ __device__ inline void ReportFailure(const WaitCtx& w, uint32_t code, uint32_t k
   if (w.doorbell != nullptr) *reinterpret_cast<volatile uint32_t*>(w.doorbell) = code;
 }
 
+// Sequence number of the running collective: one more than the number this
+// rank has completed.  Call with all threads of the CTA; `scratch` is a
+// __shared__ word.
+__device__ inline uint64_t BeginCollective(const PeerTable& peers, int rank, uint64_t* scratch) {
+  if (threadIdx.x == 0) *scratch = LdRelaxedSys(&Ctl(peers, rank)->call_seq) + 1;
+  __syncthreads();
+  return *scratch;
+}
+
+// Every CTA of the rank calls this exactly once, on every path out of the
+// kernel; the last one publishes the new count.  `ctas` = CTAs of this rank.
+__device__ inline void EndCollective(const PeerTable& peers, int rank, uint64_t seq, unsigned ctas) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ControlPage* me = Ctl(peers, rank);
+    __threadfence();
+    const unsigned prev = atomicAdd(&me->done_ctas, 1u);
+    if (prev + 1 == ctas) {
+      me->done_ctas = 0;
+      __threadfence();
+      StRelaxedSys(&me->call_seq, seq);
+    }
+  }
+}
+
 // Makes every CTA of every rank of this call stop waiting.
 __device__ inline void BroadcastAbort(const WaitCtx& w) {
   for (int r = 0; r < w.world_size; ++r) StRelaxedSys(&Ctl(*w.peers, r)->abort_seq, w.seq);

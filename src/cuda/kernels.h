@@ -51,7 +51,6 @@ struct NvlsParams {
   unsigned char* peer_in[kMaxRanks];
   unsigned char* peer_out[kMaxRanks];
   uint64_t window_elems;
-  uint64_t seq;
   uint64_t timeout_ns;
   DeviceStatus* status;
   uint32_t* doorbell;
@@ -63,7 +62,7 @@ struct OneShotParams {
   int32_t rank;
   int32_t world_size;
   int32_t dtype;
-  int32_t parity;         // which half of the double-buffered slots (one-shot call count & 1)
+  int32_t pad_;
   PeerTable peers;
   const void* sendbuf;
   void* recvbuf;
@@ -71,7 +70,6 @@ struct OneShotParams {
   double scale;
   uint64_t slot_offset;   // byte offset of the one-shot area in the arena
   uint64_t slot_bytes;    // bytes reserved per (parity, source rank)
-  uint64_t seq;           // call sequence number (same on every rank)
   uint64_t timeout_ns;
   DeviceStatus* status;
   uint32_t* doorbell;

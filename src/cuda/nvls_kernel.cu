@@ -107,7 +107,7 @@ __device__ __forceinline__ void SubRange(uint64_t lo, uint64_t hi, int part, int
 // Barrier between CTA `cta` of every rank.  Returns false when it gave up.
 __device__ inline bool CrossRankBarrier(const NvlsParams& p, const WaitCtx& w, int cta, uint32_t phase, int* s_stop) {
   __syncthreads();
-  const uint64_t val = (p.seq << 32) | phase;
+  const uint64_t val = (w.seq << 32) | phase;
   if (threadIdx.x < p.world_size && static_cast<int>(threadIdx.x) != p.rank) {
     FenceSys();
     StReleaseSys(&Ctl(p.peers, threadIdx.x)->bar[cta][p.rank], val);
@@ -118,24 +118,17 @@ __device__ inline bool CrossRankBarrier(const NvlsParams& p, const WaitCtx& w, i
   return *s_stop == 0;
 }
 
+// Body of the two-shot kernel for one CTA; returns early when a barrier gave up.
 template <typename T, int U, bool kMultimem>
-__global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_constant__ NvlsParams p0, const NvlsParams* __restrict__ emu) {
+__device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
   using A = typename Acc<T>::type;
   constexpr int kVecElems = 16 / static_cast<int>(sizeof(T));
-  __shared__ NvlsParams p;
-  __shared__ int s_stop;
-  {
-    const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y) : reinterpret_cast<const uint32_t*>(&p0);
-    for (unsigned i = threadIdx.x; i < sizeof(NvlsParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
-    if (threadIdx.x == 0) s_stop = 0;
-  }
-  __syncthreads();
   const int cta = blockIdx.x, ncta = gridDim.x;
   WaitCtx w;
   w.peers = &p.peers;
   w.status = p.status;
   w.doorbell = p.doorbell;
-  w.seq = p.seq;
+  w.seq = seq;
   w.timeout_ns = p.timeout_ns;
   w.rank = p.rank;
   w.world_size = p.world_size;
@@ -269,6 +262,22 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
       }
     }
   }
+}
+
+template <typename T, int U, bool kMultimem>
+__global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_constant__ NvlsParams p0, const NvlsParams* __restrict__ emu) {
+  __shared__ NvlsParams p;
+  __shared__ int s_stop;
+  __shared__ uint64_t s_seq;
+  {
+    const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y) : reinterpret_cast<const uint32_t*>(&p0);
+    for (unsigned i = threadIdx.x; i < sizeof(NvlsParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
+    if (threadIdx.x == 0) s_stop = 0;
+  }
+  __syncthreads();
+  const uint64_t seq = BeginCollective(p.peers, p.rank, &s_seq);
+  TwoShotBody<T, U, kMultimem>(p, seq, s_stop);
+  EndCollective(p.peers, p.rank, seq, gridDim.x);
 }
 
 }  // namespace dev

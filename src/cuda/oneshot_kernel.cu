@@ -5,7 +5,7 @@
 // 2*(ws-1) hops of the ring: this is the latency end of the size sweep, for
 // which the reference has no dedicated path.
 //
-// The slots are double-buffered by the parity of the one-shot call counter, so
+// The slots are double-buffered by the parity of the call number, so
 // consecutive calls need no exit barrier: a peer can only reach call k+2 after
 // it consumed this rank's data of call k+1, which this rank sent after it had
 // finished reading call k.
@@ -21,22 +21,17 @@ namespace dev {
 
 constexpr int kOneShotThreads = 512;
 
+// Body of the one-shot kernel for one CTA; returns early when a wait gave up.
 template <typename T>
-__global__ void __launch_bounds__(kOneShotThreads, 1)
-OneShotKernel(const __grid_constant__ OneShotParams p0, const OneShotParams* __restrict__ emu) {
+__device__ void OneShotBody(const OneShotParams& p, uint64_t seq, int& s_stop) {
   using A = typename Acc<T>::type;
   constexpr int kVecElems = 16 / static_cast<int>(sizeof(T));
-  __shared__ OneShotParams p;
-  __shared__ int s_stop;
-  {
-    const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y) : reinterpret_cast<const uint32_t*>(&p0);
-    for (unsigned i = threadIdx.x; i < sizeof(OneShotParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
-    if (threadIdx.x == 0) s_stop = 0;
-  }
-  __syncthreads();
   const int cta = blockIdx.x, ncta = gridDim.x;
   const int ws = p.world_size, me = p.rank;
-  const unsigned parity = static_cast<unsigned>(p.parity & 1);
+  // Slots are double-buffered by the parity of the call number; two one-shot
+  // calls with the same parity always have another collective (with its entry
+  // barrier) or a one-shot call of the other parity between them.
+  const unsigned parity = static_cast<unsigned>(seq & 1u);
   const T* sendbuf = static_cast<const T*>(p.sendbuf);
   T* recvbuf = static_cast<T*>(p.recvbuf);
 
@@ -44,7 +39,7 @@ OneShotKernel(const __grid_constant__ OneShotParams p0, const OneShotParams* __r
   w.peers = &p.peers;
   w.status = p.status;
   w.doorbell = p.doorbell;
-  w.seq = p.seq;
+  w.seq = seq;
   w.timeout_ns = p.timeout_ns;
   w.rank = me;
   w.world_size = ws;
@@ -80,8 +75,8 @@ OneShotKernel(const __grid_constant__ OneShotParams p0, const OneShotParams* __r
   if (threadIdx.x < ws && static_cast<int>(threadIdx.x) != me) {
     const int q = threadIdx.x;
     FenceSys();
-    StReleaseSys(&Ctl(p.peers, q)->oneshot_flag[parity][cta][me], p.seq);
-    if (!WaitGE(&Ctl(p.peers, me)->oneshot_flag[parity][cta][q], p.seq, w, kWaitOneShot, q, -1)) s_stop = 1;
+    StReleaseSys(&Ctl(p.peers, q)->oneshot_flag[parity][cta][me], seq);
+    if (!WaitGE(&Ctl(p.peers, me)->oneshot_flag[parity][cta][q], seq, w, kWaitOneShot, q, -1)) s_stop = 1;
   }
   __syncthreads();
   if (s_stop) return;
@@ -108,6 +103,23 @@ OneShotKernel(const __grid_constant__ OneShotParams p0, const OneShotParams* __r
     if (do_scale) acc = ScaleAcc<A>(acc, p.scale);
     recvbuf[i] = FromAcc<T, A>(acc);
   }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kOneShotThreads, 1)
+OneShotKernel(const __grid_constant__ OneShotParams p0, const OneShotParams* __restrict__ emu) {
+  __shared__ OneShotParams p;
+  __shared__ int s_stop;
+  __shared__ uint64_t s_seq;
+  {
+    const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y) : reinterpret_cast<const uint32_t*>(&p0);
+    for (unsigned i = threadIdx.x; i < sizeof(OneShotParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
+    if (threadIdx.x == 0) s_stop = 0;
+  }
+  __syncthreads();
+  const uint64_t seq = BeginCollective(p.peers, p.rank, &s_seq);
+  OneShotBody<T>(p, seq, s_stop);
+  EndCollective(p.peers, p.rank, seq, gridDim.x);
 }
 
 }  // namespace dev

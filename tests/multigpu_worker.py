@@ -140,6 +140,58 @@ def case_buckets(comm):
     return 0
 
 
+def case_graph(comm):
+    """Collectives captured in a CUDA graph and replayed: the kernels take their
+    call number from device memory, so a replay is a new, correctly sequenced call."""
+    info = comm.device_info(connect=True)
+    n = 1 << 16
+    cases = [("oneshot", n), ("ring", 1 << 20), ("rabenseifner", 1 << 20), ("direct", 1 << 20)]
+    if info["nvls"]:
+        cases.append(("nvls", 1 << 20))
+    stream = torch.cuda.Stream()
+    for algo, m in cases:
+        x = comm.symmetric_empty(m, torch.float32)
+        y = comm.symmetric_empty(m, torch.float32)
+        x.copy_(seeded(m, torch.float32, RANK, seed=1))
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            # warm-up: every distinct call is issued once outside the capture,
+            # which builds and uploads its program (an allocation)
+            comm.allreduce(x, y, algo=algo, scale=0.5)
+            comm.allreduce(y, x, algo=algo, scale=1.0)
+        stream.synchronize()
+        x.copy_(seeded(m, torch.float32, RANK, seed=1))
+        comm.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            comm.allreduce(x, y, algo=algo, scale=0.5)
+            comm.allreduce(y, x, algo=algo, scale=1.0)  # two dependent collectives per replay
+        for it in range(4):
+            x.copy_(seeded(m, torch.float32, RANK, seed=10 + it))
+            torch.cuda.synchronize()
+            comm.barrier()
+            g.replay()
+            torch.cuda.synchronize()
+            comm.check()
+            want = expected(m, torch.float32, 0.5, seed=10 + it) * WS
+            if not torch.allclose(x.double(), want, rtol=1e-5 * WS, atol=1e-5 * WS):
+                print(f"rank {RANK}: graph replay {it} of {algo} mismatch", file=sys.stderr)
+                return 1
+        # an ordinary call after the replays still lines up with the peers
+        comm.allreduce(x, y, algo=algo, sync=True)
+    return 0
+
+
+def case_trace(comm):
+    """Device-side trace: per-op %globaltimer stamps end up in the trace file."""
+    comm.set_timer_base()
+    x = seeded(1 << 20, torch.float32, RANK)
+    for algo in ("ring", "rabenseifner"):
+        comm.allreduce(x.clone(), algo=algo, sync=True)
+    comm.dump_trace()
+    return 0
+
+
 def case_leave(comm):
     """Failure detection without faulting a GPU: after one good allreduce the
     last rank leaves between steps; the others' next collective runs into its

@@ -71,6 +71,26 @@ def test_rank_leaving_is_detected(bins):
 
 
 @needs2
+def test_cuda_graph_capture_and_replay(bins):
+    code, err = run(bins, 2, "graph")
+    assert code == 0, err
+
+
+@needs2
+def test_device_trace(bins, tmp_path):
+    prefix = str(tmp_path / "devtrace")
+    code, err = run(bins, 2, "trace", env={"IBCOMM_TRACE": "1", "IBCOMM_TRACE_FILE": prefix})
+    assert code == 0, err
+    for r in range(2):
+        lines = {ln.split(",")[0]: ln.split(",")[1:] for ln in Path(f"{prefix}_{r}.dat").read_text().splitlines()}
+        # begin/duration pairs of the kernel's waits ("received") and data phases ("reduced"), and of the host's launches
+        assert len([v for v in lines["received"] if v]) >= 4
+        assert len([v for v in lines["reduced"] if v]) >= 4
+        assert len([v for v in lines["issue_redu_kernel"] if v]) >= 2
+        assert all(float(v) >= 0 for v in lines["reduced"] if v)
+
+
+@needs2
 def test_tester_binary_on_gpus(bins):
     for algo in ("ring", "rabenseifner"):
         cmd = ["timeout", "120s", bins["ibcomm_run"], "-np", "2", bins["allreduce_tester"], "--device", "cuda", algo, "128M",
