@@ -13,6 +13,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "ibcomm/communicator.h"
 #include "kernels.h"
 #include "vec_ops.cuh"
@@ -20,10 +22,19 @@
 namespace ibcomm {
 namespace dev {
 
-constexpr int kCopyThreads = 256;
+#ifndef IBCOMM_COPY_THREADS
+#define IBCOMM_COPY_THREADS 256
+#endif
+constexpr int kCopyThreads = IBCOMM_COPY_THREADS;
 constexpr int kCopyWarps = kCopyThreads / 32;
-constexpr int kCopyStages = 4;            // tiles in flight per warp
-constexpr int kCopyTileBytesIn = 4096;    // bytes of input per tile
+#ifndef IBCOMM_COPY_STAGES
+#define IBCOMM_COPY_STAGES 4
+#endif
+#ifndef IBCOMM_COPY_TILE
+#define IBCOMM_COPY_TILE 4096
+#endif
+constexpr int kCopyStages = IBCOMM_COPY_STAGES;      // tiles in flight per warp
+constexpr int kCopyTileBytesIn = IBCOMM_COPY_TILE;   // bytes of input per tile
 constexpr uint32_t kMbarSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -192,6 +203,10 @@ static cudaError_t LaunchCopyTyped(const CopyParams& p, int blocks, cudaStream_t
     cudaError_t e = cudaFuncSetAttribute(dev::CopyScaleTmaKernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     configured = true;
+  }
+  if (const char* e = getenv("IBCOMM_COPY_BLOCKS")) {  // experiment knob: CTAs of the copy kernel
+    int v = atoi(e);
+    if (v > 0) blocks = v;
   }
   const uint64_t tiles = (p.len_elements + kTileElems - 1) / kTileElems;
   const uint64_t blocks_needed = (tiles + dev::kCopyWarps - 1) / dev::kCopyWarps;

@@ -335,14 +335,15 @@ void DeviceContext::OrderAfterPrevious(cudaStream_t stream) {
   // the next one may only start when the previous one has finished, also when
   // the caller switches streams.  Inside a stream capture the graph's own
   // edges order the collectives; the caller keeps them on one stream.
+  // No event is recorded per call (it would put a bubble between
+  // back-to-back kernels); the rare switch of streams waits on the host.
   if (IsCapturing(stream)) return;
-  if (have_last_ && last_stream_ != stream) CUDACHECK(cudaStreamWaitEvent(stream, last_done_, 0));
+  if (have_last_ && last_stream_ != stream) CUDACHECK(cudaStreamSynchronize(last_stream_));
 }
 
 void DeviceContext::MarkIssued(cudaStream_t stream) {
   ++calls_;
   if (IsCapturing(stream)) return;
-  CUDACHECK(cudaEventRecord(last_done_, stream));
   last_stream_ = stream;
   have_last_ = true;
 }
@@ -372,7 +373,7 @@ const SymmetricAlloc* DeviceContext::FindSymmetric(const void* p, size_t bytes) 
 void DeviceContext::RunCopy(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, cudaStream_t stream) {
   if (sendbuf == recvbuf && scale == 1.0) return;
   CopyParams cp{sendbuf, recvbuf, n, static_cast<int32_t>(dtype), static_cast<int32_t>(dtype), scale};
-  CUDACHECK(LaunchCopyKernel(cp, 148, stream));
+  CUDACHECK(LaunchCopyKernel(cp, kCopyDefaultBlocks, stream));
   ++kernel_launches_;
 }
 

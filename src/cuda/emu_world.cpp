@@ -102,7 +102,7 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
 
   if (m.ws == 1) {
     CopyParams cp{sendbufs[0], recvbufs[0], n, static_cast<int32_t>(dtype), static_cast<int32_t>(dtype), scale};
-    if (!(sendbufs[0] == recvbufs[0] && scale == 1.0)) CUDACHECK(LaunchCopyKernel(cp, 148, stream));
+    if (!(sendbufs[0] == recvbufs[0] && scale == 1.0)) CUDACHECK(LaunchCopyKernel(cp, kCopyDefaultBlocks, stream));
     m.last_channels = 0;
     if (!async) CUDACHECK(cudaStreamSynchronize(stream));
     return;

@@ -362,7 +362,7 @@ int ibcomm_copy_scale(const void* in, void* out, size_t n, int dtype_in, int dty
     NeedCuda();
 #ifdef USE_CUDA
     ibcomm::CopyParams p{in, out, n, static_cast<int32_t>(CheckDType(dtype_in)), static_cast<int32_t>(CheckDType(dtype_out)), scale};
-    cudaError_t e = ibcomm::LaunchCopyKernel(p, 148, static_cast<cudaStream_t>(stream));
+    cudaError_t e = ibcomm::LaunchCopyKernel(p, ibcomm::kCopyDefaultBlocks, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) IBCOMM_FAIL(CUDA_ERROR, "copy kernel launch failed: %s\n", cudaGetErrorString(e));
 #else
     (void)in; (void)out; (void)n; (void)dtype_in; (void)dtype_out; (void)scale; (void)stream;
