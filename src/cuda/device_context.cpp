@@ -511,6 +511,8 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
     if (algo == Algo::kOneShot && wire != dtype) IBCOMM_FAIL(NOT_SUPPORTED, "One-shot allreduce has no wire compression.\n");
     if (algo == Algo::kDirect && wire != dtype) IBCOMM_FAIL(NOT_SUPPORTED, "The direct algorithm has no wire compression.\n");
     channels = ChooseChannels(algo, bytes, ws_, max_channels_);
+    if (algo == Algo::kNvls && !(FindSymmetric(sendbuf, bytes) != nullptr && FindSymmetric(recvbuf, bytes) != nullptr))
+      channels = std::max(channels, ChooseChannels(Algo::kDirect, bytes, ws_, max_channels_));
   }
   OrderAfterPrevious(stream);
   switch (algo) {

@@ -109,7 +109,8 @@ __device__ inline bool CrossRankBarrier(const NvlsParams& p, const WaitCtx& w, i
   __syncthreads();
   const uint64_t val = (w.seq << 32) | phase;
   if (threadIdx.x < p.world_size && static_cast<int>(threadIdx.x) != p.rank) {
-    FenceSys();
+    // The release store orders everything this CTA wrote before the barrier
+    // (observed by this thread through __syncthreads) ahead of the flag.
     StReleaseSys(&Ctl(p.peers, threadIdx.x)->bar[cta][p.rank], val);
     if (!WaitGE(&Ctl(p.peers, p.rank)->bar[cta][threadIdx.x], val, w, kWaitBarrier, threadIdx.x, static_cast<int>(phase)))
       *s_stop = 1;

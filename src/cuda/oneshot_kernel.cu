@@ -74,8 +74,7 @@ __device__ void OneShotBody(const OneShotParams& p, uint64_t seq, int& s_stop) {
   // (2) tell them, (3) wait for theirs.
   if (threadIdx.x < ws && static_cast<int>(threadIdx.x) != me) {
     const int q = threadIdx.x;
-    FenceSys();
-    StReleaseSys(&Ctl(p.peers, q)->oneshot_flag[parity][cta][me], seq);
+    StReleaseSys(&Ctl(p.peers, q)->oneshot_flag[parity][cta][me], seq);  // release: the pushes above come first
     if (!WaitGE(&Ctl(p.peers, me)->oneshot_flag[parity][cta][q], seq, w, kWaitOneShot, q, -1)) s_stop = 1;
   }
   __syncthreads();

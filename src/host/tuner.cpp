@@ -118,7 +118,11 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
   } else {
     a = Algo::kRing;
   }
-  return TunerChoice{a, ChooseChannels(a, bytes, world_size, max_channels)};
+  int ch = ChooseChannels(a, bytes, world_size, max_channels);
+  // Staged switch path: the copies in and out of the pool run on the same
+  // CTAs, and 64 of them cannot pull full HBM bandwidth.
+  if (a == Algo::kNvls && !zero_copy) ch = std::max(ch, ChooseChannels(Algo::kDirect, bytes, world_size, max_channels));
+  return TunerChoice{a, ch};
 }
 
 }  // namespace ibcomm
