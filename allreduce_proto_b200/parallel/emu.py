@@ -53,9 +53,10 @@ class EmuWorld:
         """Test hook: ``rank`` skips the following collectives (-1: nobody does)."""
         check(_native.lib().ibcomm_emu_set_silent_rank(self._h, rank))
 
-    def set_direct_staging(self, on: bool) -> None:
-        """Direct algorithm through the pool windows (True) or in place (False)."""
-        check(_native.lib().ibcomm_emu_set_direct_staging(self._h, int(on)))
+    def set_direct_staging(self, mode) -> None:
+        """Direct algorithm: 0/False in place, 1/True staged through the pool windows,
+        2 staged with the pipelined mover/reducer kernel."""
+        check(_native.lib().ibcomm_emu_set_direct_staging(self._h, int(mode)))
 
     @property
     def last_channels(self) -> int:

@@ -40,9 +40,10 @@ class EmuWorld {
   // return at once), so its peers' bounded waits run out and they report a
   // timeout; nothing faults or hangs.  -1 restores normal operation.
   void SetSilentRank(int r);
-  // Makes the direct algorithm stage through the pool windows (as it does for
-  // buffers the peers cannot map) instead of using the buffers in place.
-  void SetDirectStaging(bool on);
+  // How the direct algorithm treats the buffers: 0 in place, 1 staged through
+  // the pool window by window (as for buffers the peers cannot map), 2 staged
+  // with the pipelined kernel (mover and reducer CTAs).
+  void SetDirectStaging(int mode);
   int last_channels() const;
 
   struct Impl;

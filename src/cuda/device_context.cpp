@@ -5,6 +5,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <deque>
 #include <map>
@@ -113,6 +114,7 @@ class DeviceContext {
   uint64_t calls_ = 0;
   uint64_t kernel_launches_ = 0;
   int last_algo_ = 0, last_channels_ = 0;
+  int last_channels_override_ = 0;  // CTAs of the pipelined staged kernel, when it ran
   int max_channels_ = env::kDefaultNumCudaStream;
   std::vector<P2pState> p2p_;
   std::vector<std::unique_ptr<SymmetricAlloc>> symm_;
@@ -463,6 +465,35 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   }
   p.window_elems = (zin && zout) ? n : window_elems;
   if (p.window_elems == 0) p.window_elems = 1;
+  // Both buffers staged and the message large enough to be worth a pipeline:
+  // mover CTAs copy the neighbouring windows while reducer CTAs work.
+  const uint64_t quarter = layout_.pool_bytes / 4 / 4096 * 4096;
+  const bool pipelined = !zin && !zout && bytes >= (4u << 20) && quarter / esize >= 1024 && getenv("IBCOMM_NO_STAGE_PIPELINE") == nullptr;
+  if (pipelined) {
+    static int max_pairs = StagedTwoShotMaxPairs(device_);
+    int pairs = static_cast<int>(std::min<size_t>(64, std::max<size_t>(1, bytes / (256u << 10))));
+    pairs = std::min(pairs, std::min(max_pairs, std::max(1, max_channels_ / 2)));
+    if (pairs >= 1) {
+      p.window_elems = quarter / esize;
+      p.window_stride = quarter;
+      const uint64_t in_off = layout_.pool_offset, out_off = layout_.pool_offset + 2 * quarter;
+      p.mc_in = mc_arena ? mc_arena + in_off : nullptr;
+      p.mc_out = mc_arena ? mc_arena + out_off : nullptr;
+      p.local_in = arena_.ptr() + in_off;
+      p.local_out = arena_.ptr() + out_off;
+      for (int q = 0; q < ws_; ++q) {
+        p.peer_in[q] = rr_.peers.arena[q] + in_off;
+        p.peer_out[q] = rr_.peers.arena[q] + out_off;
+      }
+      IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+      CUDACHECK(LaunchStagedTwoShotKernel(p, nullptr, 1, pairs, stream));
+      ++kernel_launches_;
+      IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+      last_channels_override_ = 2 * pairs;
+      return;
+    }
+  }
+  last_channels_override_ = 0;
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
   CUDACHECK(LaunchNvlsKernel(p, nullptr, 1, channels, stream));
   ++kernel_launches_;
@@ -534,7 +565,8 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
   }
   MarkIssued(stream);
   last_algo_ = static_cast<int>(algo);
-  last_channels_ = channels;
+  last_channels_ = last_channels_override_ > 0 ? last_channels_override_ : channels;
+  last_channels_override_ = 0;
   Finish(stream, opts.async);
 }
 

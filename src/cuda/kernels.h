@@ -56,11 +56,18 @@ struct NvlsParams {
   unsigned char* peer_in[kMaxRanks];
   unsigned char* peer_out[kMaxRanks];
   uint64_t window_elems;
+  // Pipelined staged kernel only: the input and output areas each hold two
+  // windows, this many bytes apart.
+  uint64_t window_stride;
   uint64_t timeout_ns;
   DeviceStatus* status;
   uint32_t* doorbell;
 };
 cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
+// Staged buffers, pipelined: `pairs` reducer CTAs and `pairs` mover CTAs per
+// rank in one cooperative launch (they hand windows to each other).
+cudaError_t LaunchStagedTwoShotKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int pairs, cudaStream_t stream);
+int StagedTwoShotMaxPairs(int device);
 
 // ---- one-shot allreduce for small messages (push to every peer, sum locally) ----
 struct OneShotParams {

@@ -26,98 +26,11 @@
 #include "flags.cuh"
 #include "ibcomm/communicator.h"
 #include "kernels.h"
+#include "twoshot_common.cuh"
 #include "vec_ops.cuh"
 
 namespace ibcomm {
 namespace dev {
-
-constexpr int kNvlsThreads = 512;
-
-template <typename T> struct Multimem {
-  // Types without a multimem form (integers, fp64) only run the direct variant.
-  __device__ __forceinline__ static uint4 LdReduce(const void*) { return make_uint4(0, 0, 0, 0); }
-  __device__ __forceinline__ static void St(void*, uint4) {}
-};
-
-template <> struct Multimem<float> {
-  __device__ __forceinline__ static uint4 LdReduce(const void* mc) {
-    uint4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
-    return v;
-  }
-  __device__ __forceinline__ static void St(void* mc, uint4 v) {
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-  }
-};
-template <> struct Multimem<__half> {
-  __device__ __forceinline__ static uint4 LdReduce(const void* mc) {
-    uint4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
-    return v;
-  }
-  __device__ __forceinline__ static void St(void* mc, uint4 v) {
-    asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-  }
-};
-template <> struct Multimem<__nv_bfloat16> {
-  __device__ __forceinline__ static uint4 LdReduce(const void* mc) {
-    uint4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
-    return v;
-  }
-  __device__ __forceinline__ static void St(void* mc, uint4 v) {
-    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-  }
-};
-
-// dst[b..e) = src[b..e) in 16-byte vectors, eight loads in flight per thread.
-template <bool kStrongSrc>
-__device__ __forceinline__ void CopyVectors(uint4* dst, const uint4* src, uint64_t b, uint64_t e) {
-  constexpr int kU = 8;
-  for (uint64_t i = b + threadIdx.x; i < e; i += static_cast<uint64_t>(blockDim.x) * kU) {
-    uint4 v[kU];
-#pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
-      if (idx < e) v[u] = kStrongSrc ? Ld16Strong(src + idx) : Ld16(src + idx);
-    }
-#pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
-      if (idx < e) St16(dst + idx, v[u]);
-    }
-  }
-}
-
-// [*b, *e) = part `part` of `parts` of the range [lo, hi).
-__device__ __forceinline__ void SubRange(uint64_t lo, uint64_t hi, int part, int parts, uint64_t* b, uint64_t* e) {
-  const uint64_t len = hi - lo;
-  const uint64_t per = (len + static_cast<uint64_t>(parts) - 1) / static_cast<uint64_t>(parts);
-  uint64_t x = lo + per * static_cast<uint64_t>(part);
-  if (x > hi) x = hi;
-  uint64_t y = x + per;
-  if (y > hi) y = hi;
-  *b = x;
-  *e = y;
-}
-
-// Barrier between CTA `cta` of every rank.  Returns false when it gave up.
-__device__ inline bool CrossRankBarrier(const NvlsParams& p, const WaitCtx& w, int cta, uint32_t phase, int* s_stop) {
-  __syncthreads();
-  const uint64_t val = (w.seq << 32) | phase;
-  if (threadIdx.x < p.world_size && static_cast<int>(threadIdx.x) != p.rank) {
-    // The release store orders everything this CTA wrote before the barrier
-    // (observed by this thread through __syncthreads) ahead of the flag.
-    StReleaseSys(&Ctl(p.peers, threadIdx.x)->bar[cta][p.rank], val);
-    if (!WaitGE(&Ctl(p.peers, p.rank)->bar[cta][threadIdx.x], val, w, kWaitBarrier, threadIdx.x, static_cast<int>(phase)))
-      *s_stop = 1;
-  }
-  __syncthreads();
-  return *s_stop == 0;
-}
 
 // Body of the two-shot kernel for one CTA; returns early when a barrier gave up.
 template <typename T, int U, bool kMultimem>
@@ -299,11 +212,6 @@ static cudaError_t LaunchNvlsU(const NvlsParams& p, const NvlsParams* emu, int e
   return cudaGetLastError();
 }
 
-template <typename T> struct HasMultimem { static constexpr bool value = false; };
-template <> struct HasMultimem<float> { static constexpr bool value = true; };
-template <> struct HasMultimem<__half> { static constexpr bool value = true; };
-template <> struct HasMultimem<__nv_bfloat16> { static constexpr bool value = true; };
-
 template <typename T>
 static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
   // Tuning knobs for experiments: loads in flight per thread and CTA size.
@@ -311,7 +219,7 @@ static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, i
   static const int threads_env = EnvInt("IBCOMM_NVLS_THREADS", dev::kNvlsThreads);
   const int threads = (threads_env >= 64 && threads_env <= dev::kNvlsThreads && threads_env % 32 == 0) ? threads_env : dev::kNvlsThreads;
   if (!p.use_multimem) return LaunchNvlsU<T, 4, false>(p, emu, emu_ranks, blocks, threads, stream);
-  if constexpr (HasMultimem<T>::value) {
+  if constexpr (dev::HasMultimem<T>::value) {
     if (unroll == 8) return LaunchNvlsU<T, 8, true>(p, emu, emu_ranks, blocks, threads, stream);
     if (unroll == 2) return LaunchNvlsU<T, 2, true>(p, emu, emu_ranks, blocks, threads, stream);
     return LaunchNvlsU<T, 4, true>(p, emu, emu_ranks, blocks, threads, stream);

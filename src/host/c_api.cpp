@@ -335,7 +335,7 @@ int ibcomm_emu_set_silent_rank(ibcomm_emu* w, int rank) {
 int ibcomm_emu_set_direct_staging(ibcomm_emu* w, int on) {
   return Guard([&] {
 #ifdef USE_CUDA
-    w->world.SetDirectStaging(on != 0);
+    w->world.SetDirectStaging(on);
 #else
     (void)w; (void)on;
 #endif

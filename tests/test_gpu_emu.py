@@ -132,7 +132,7 @@ def test_direct_two_shot(ws):
     # through pool windows (1 MiB pool = 512 KiB windows, so 4 MiB messages
     # take several rounds).
     w = world(ws, 1 << 20, 1 << 20)
-    for staged in (False, True):
+    for staged in (0, 1, 2):  # in place, staged, staged + pipelined (mover and reducer CTAs)
         w.set_direct_staging(staged)
         for n in (ws, 1000, 65536 + 3, 1 << 20):
             for dtype in (torch.float32, torch.bfloat16, torch.int32):
@@ -146,7 +146,7 @@ def test_direct_two_shot(ws):
         want = reference(bufs, 1.0, torch.float32)
         w.allreduce(bufs, None, algo="direct")
         check(bufs, want, torch.float32, ws)
-    w.set_direct_staging(False)
+    w.set_direct_staging(0)
 
 
 def test_unaligned_buffers_take_the_scalar_path():
