@@ -17,15 +17,17 @@
 namespace ibcomm {
 namespace env {
 
-constexpr int kDefaultNumCudaStream = 128;
+constexpr int kDefaultNumCudaStream = 256;
 constexpr size_t kDefaultPoolPreAlloc = 64ull << 20;
 constexpr size_t kDefaultWorkGpuMemory = 32ull << 20;
 constexpr int kDefaultTimeoutMs = 10000;
 
 // > 0 when set, 0 when unset.  <= 0 while set is INVALID_ARGUMENT (exit 1).
 int64_t ReadChunkSize();
-// 1..1024, default 128 (the value in the reference's code, memory_pool.h:82;
-// its README says 64).  Outside the range is INVALID_ARGUMENT.
+// 1..1024, default 256 (the reference's code says 128, memory_pool.h:82, its
+// README 64; here the value caps the CTAs of a collective, and the ring and
+// Rabenseifner kernels measure best with two 256-thread CTAs per SM).
+// Outside the range is INVALID_ARGUMENT.
 int ReadNumCudaStream();
 // 4..1 GiB, default 64 MiB.  Outside the range is INVALID_ARGUMENT.
 size_t ReadPreAllocSize();

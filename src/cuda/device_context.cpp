@@ -465,10 +465,14 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   }
   p.window_elems = (zin && zout) ? n : window_elems;
   if (p.window_elems == 0) p.window_elems = 1;
-  // Both buffers staged and the message large enough to be worth a pipeline:
-  // mover CTAs copy the neighbouring windows while reducer CTAs work.
+  // Optional (IBCOMM_STAGE_PIPELINE=1): both buffers staged and a large
+  // message: mover CTAs copy the neighbouring windows while reducer CTAs work.
+  // Off by default: on 2 B200 it measured no faster than the sequential
+  // windows (which put every CTA on every phase) for the switch path and
+  // slower for the direct path, whose peer loads want all the CTAs.
   const uint64_t quarter = layout_.pool_bytes / 4 / 4096 * 4096;
-  const bool pipelined = !zin && !zout && bytes >= (4u << 20) && quarter / esize >= 1024 && getenv("IBCOMM_NO_STAGE_PIPELINE") == nullptr;
+  const char* pipe_env = getenv("IBCOMM_STAGE_PIPELINE");
+  const bool pipelined = pipe_env != nullptr && pipe_env[0] == '1' && !zin && !zout && bytes >= (4u << 20) && quarter / esize >= 1024;
   if (pipelined) {
     static int max_pairs = StagedTwoShotMaxPairs(device_);
     int pairs = static_cast<int>(std::min<size_t>(64, std::max<size_t>(1, bytes / (256u << 10))));

@@ -111,12 +111,14 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
     }
   } else if (bytes <= (256u << 10)) {
     a = Algo::kOneShot;
-  } else if (nvls_available && world_size > 2 && bytes <= (128u << 20)) {
+  } else if (nvls_available && world_size > 2 && bytes <= (64u << 20)) {
     a = Algo::kNvls;  // staged through the pool inside the kernel
   } else if (bytes <= (32u << 20)) {
     a = Algo::kDirect;  // staged; two synchronisation steps
   } else {
-    a = Algo::kRing;
+    // Large messages in ordinary memory: the chunk-pipelined programs keep
+    // their staging inside the transfer.  Halving/doubling needs fewer steps.
+    a = util::GetExpOfTwo(static_cast<uint64_t>(world_size)) != 0 ? Algo::kRabenseifner : Algo::kRing;
   }
   int ch = ChooseChannels(a, bytes, world_size, max_channels);
   // Staged switch path: the copies in and out of the pool run on the same

@@ -70,6 +70,24 @@ def case_allreduce(comm):
     return 0
 
 
+def case_pipeline(comm):
+    """Staged buffers with the pipelined mover/reducer kernel (IBCOMM_STAGE_PIPELINE=1 is set by the test)."""
+    info = comm.device_info(connect=True)
+    for algo in ["direct"] + (["nvls"] if info["nvls"] else []):
+        for n in ((8 << 20) + 3, 40_000_001):
+            x = seeded(n, torch.float32, RANK, seed=3)
+            y = torch.empty_like(x)
+            comm.allreduce(x, y, algo=algo, scale=0.5, sync=True)
+            if not close(y, expected(n, torch.float32, 0.5, seed=3), torch.float32):
+                print(f"rank {RANK}: pipelined {algo} n={n} mismatch", file=sys.stderr)
+                return 1
+            comm.allreduce(x, algo=algo, sync=True)  # in place
+            if not close(x, expected(n, torch.float32, 1.0, seed=3), torch.float32):
+                print(f"rank {RANK}: pipelined in-place {algo} n={n} mismatch", file=sys.stderr)
+                return 1
+    return 0
+
+
 def case_symmetric(comm):
     """Zero-copy buffers: symmetric memory, switch reduction when available."""
     n = (4 << 20) + 3

@@ -43,6 +43,12 @@ def test_symmetric_zero_copy(bins, np_):
 
 
 @needs2
+def test_pipelined_staging_kernel(bins):
+    code, err = run(bins, min(NGPU, 4), "pipeline", env={"IBCOMM_STAGE_PIPELINE": "1"})
+    assert code == 0, err
+
+
+@needs2
 def test_without_multicast_and_with_ipc_handles(bins):
     code, err = run(bins, 2, "allreduce", env={"IBCOMM_DISABLE_NVLS": "1"})
     assert code == 0, err
