@@ -357,7 +357,7 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
         warm = 20 if size <= (1 << 20) else 5
         algos = []
         if world > 1:
-            if size <= (256 << 10):
+            if size <= (512 << 10):
                 algos.append(("oneshot", plain_in, plain_out))
             algos += [("ring", plain_in, plain_out), ("rabenseifner", plain_in, plain_out),
                       ("direct", plain_in, plain_out), ("direct_zero_copy", sym_in, sym_out)]

@@ -14,7 +14,7 @@ ArenaLayout MakeArenaLayout(size_t pool_bytes, size_t work_bytes) {
   l.control_offset = off;
   off += AlignUp(sizeof(ControlPage), 65536);
   l.oneshot_offset = off;
-  l.oneshot_slot_bytes = 256u << 10;
+  l.oneshot_slot_bytes = 512u << 10;
   off += 2ull * kMaxRanks * l.oneshot_slot_bytes;
   l.mailbox_offset = off;
   l.mailbox_slot_bytes = 256u << 10;

@@ -109,8 +109,8 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
     } else {
       a = bytes <= (256u << 10) ? Algo::kOneShot : Algo::kDirect;
     }
-  } else if (bytes <= (256u << 10)) {
-    a = Algo::kOneShot;
+  } else if (bytes <= (512u << 10)) {
+    a = Algo::kOneShot;  // ordinary buffers: one push per peer beats three staged phases
   } else if (nvls_available && world_size > 2 && bytes <= (64u << 20)) {
     a = Algo::kNvls;  // staged through the pool inside the kernel
   } else if (bytes <= (32u << 20)) {

@@ -53,7 +53,7 @@ def case_allreduce(comm):
             if algo == "nvls" and dtype == torch.int32:
                 continue
             for n in (WS, 1000, 65536, (1 << 20) + 5, 8 << 20):
-                if algo == "oneshot" and n * torch.empty((), dtype=dtype).element_size() > (256 << 10):
+                if algo == "oneshot" and n * torch.empty((), dtype=dtype).element_size() > (512 << 10):
                     continue
                 scale = 1.0 if dtype == torch.int32 else 0.5
                 x = seeded(n, dtype, RANK, seed=n % 97)
