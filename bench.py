@@ -56,6 +56,8 @@ def parse_args():
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--sweep-max-bytes", type=int, default=1 << 30)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--write-tuning", default=None, metavar="PATH",
+                    help="with --sweep: write the fastest algorithm per size as an IBCOMM_TUNING_FILE table")
     ap.add_argument("--no-extras", action="store_true", help="skip per-algorithm and NCCL measurements")
     ap.add_argument("--kernel-case", default=None,
                     choices=["copy", "exec_ring_emu8", "exec_rabenseifner_emu8", "oneshot_emu8"],
@@ -389,11 +391,34 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
             for r in rows:
                 f.write(json.dumps(r) + "\n")
         print(json.dumps({"sweep": out_path, "rows": len(rows), "n_gpus": world, "nvls": info["nvls"]}))
+        if args.write_tuning and world > 1:
+            write_tuning(args.write_tuning, rows, world)
     if world > 1:
         dist.barrier()
         comm.close()
         dist.destroy_process_group()
     return 0
+
+
+def write_tuning(path: str, rows: list, world: int) -> None:
+    """IBCOMM_TUNING_FILE table ("world_size max_bytes algorithm channels", first match wins) from a sweep:
+    per size the fastest algorithm measured on symmetric buffers (plain-buffer columns where there is no
+    symmetric variant); consecutive sizes with the same choice are merged."""
+    best = []
+    for size in sorted({r["bytes"] for r in rows}):
+        cands = [r for r in rows if r["bytes"] == size and "us" in r and r["algo"] in
+                 ("oneshot", "ring", "rabenseifner", "direct_zero_copy", "nvls_zero_copy")]
+        if cands:
+            w = min(cands, key=lambda r: r["us"])
+            best.append((size, w["algo"].split("_")[0], int(w.get("channels") or 0)))
+    lines = ["# world_size max_bytes algorithm channels   (written by bench.py --sweep --write-tuning)"]
+    for i, (size, algo, ch) in enumerate(best):
+        last = i + 1 == len(best)
+        if not last and best[i + 1][1] == algo:
+            continue
+        lines.append(f"{world} {0 if last else size} {algo} 0")
+    with open(path, "w") as f:
+        f.write("\n".join(lines) + "\n")
 
 
 if __name__ == "__main__":

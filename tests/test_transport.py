@@ -13,3 +13,29 @@ def test_sendrecv_binary(bins):
 def test_schedule_simulator(bins):
     p = subprocess.run([bins["schedule_sim"]], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
     assert p.returncode == 0, p.stdout
+
+
+def test_schedule_simulator_under_thread_sanitizer(tmp_path):
+    """The flag protocol of the op programs (release store of a flag after the
+    data, acquire load before reading it, credits before a slot is reused) is
+    replayed on CPU threads under ThreadSanitizer: any data race between the
+    emulated ranks or channels is reported."""
+    import shutil
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    if shutil.which("g++") is None:
+        import pytest
+        pytest.skip("no g++")
+    exe = tmp_path / "schedule_sim_tsan"
+    srcs = ["tests/cpp/schedule_sim.cpp"] + [f"src/host/{n}.cpp" for n in
+            ("error", "env", "partition", "schedule", "shm_transport", "trace", "communicator")]
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", "-w", f"-I{root / 'include'}", f"-I{root / 'tests' / 'cpp'}",
+           *[str(root / s) for s in srcs], "-o", str(exe), "-pthread", "-lrt"]
+    b = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if b.returncode != 0 and "tsan" in b.stdout.lower():
+        import pytest
+        pytest.skip("ThreadSanitizer runtime not available")
+    assert b.returncode == 0, b.stdout[-2000:]
+    p = subprocess.run([str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
+    assert p.returncode == 0, p.stdout[-3000:]
+    assert "ThreadSanitizer" not in p.stdout, p.stdout[-3000:]
