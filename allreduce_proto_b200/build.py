@@ -50,7 +50,6 @@ CUDA_SOURCES = [
     "src/cuda/emu_world.cpp",
     "src/cuda/exec_kernel.cu",
     "src/cuda/nvls_kernel.cu",
-    "src/cuda/staged_kernel.cu",
     "src/cuda/oneshot_kernel.cu",
     "src/cuda/copy_kernel.cu",
     "src/cuda/p2p_sendrecv.cu",

@@ -54,8 +54,7 @@ class EmuWorld:
         check(_native.lib().ibcomm_emu_set_silent_rank(self._h, rank))
 
     def set_direct_staging(self, mode) -> None:
-        """Direct algorithm: 0/False in place, 1/True staged through the pool windows,
-        2 staged with the pipelined mover/reducer kernel."""
+        """Direct algorithm: 0/False in place, 1/True staged through the pool windows."""
         check(_native.lib().ibcomm_emu_set_direct_staging(self._h, int(mode)))
 
     @property

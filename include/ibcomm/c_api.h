@@ -89,8 +89,7 @@ int ibcomm_emu_last_channels(ibcomm_emu* w);
 /* Test hook: rank `rank` does not take part in the following collectives
  * (-1 = everybody takes part), so its peers' bounded waits run out. */
 int ibcomm_emu_set_silent_rank(ibcomm_emu* w, int rank);
-/* Direct algorithm: in place (0, default), staged through the pool windows (1),
- * staged with the pipelined mover/reducer kernel (2). */
+/* Direct algorithm: in place (0, default) or staged through the pool windows (1). */
 int ibcomm_emu_set_direct_staging(ibcomm_emu* w, int on);
 typedef struct {
   uint32_t code;

@@ -54,12 +54,6 @@ struct ControlPage {
   uint64_t pad_[5];
   // One-shot allreduce flags: [parity][cta][source].
   uint64_t oneshot_flag[2][kMaxChannels][kMaxRanks];
-  // Pipelined staged allreduce, local hand-shakes between the mover CTA and
-  // the reducer CTA of one index (written and read on this GPU only):
-  // windows copied in, windows reduced everywhere, windows copied out.
-  uint64_t stage_in_ready[kMaxChannels];
-  uint64_t stage_out_ready[kMaxChannels];
-  uint64_t stage_out_consumed[kMaxChannels];
 };
 
 // ---- error report written by a kernel whose bounded wait ran out ----

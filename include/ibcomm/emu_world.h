@@ -41,8 +41,7 @@ class EmuWorld {
   // timeout; nothing faults or hangs.  -1 restores normal operation.
   void SetSilentRank(int r);
   // How the direct algorithm treats the buffers: 0 in place, 1 staged through
-  // the pool window by window (as for buffers the peers cannot map), 2 staged
-  // with the pipelined kernel (mover and reducer CTAs).
+  // the pool window by window (as for buffers the peers cannot map).
   void SetDirectStaging(int mode);
   int last_channels() const;
 

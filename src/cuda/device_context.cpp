@@ -114,7 +114,6 @@ class DeviceContext {
   uint64_t calls_ = 0;
   uint64_t kernel_launches_ = 0;
   int last_algo_ = 0, last_channels_ = 0;
-  int last_channels_override_ = 0;  // CTAs of the pipelined staged kernel, when it ran
   int max_channels_ = env::kDefaultNumCudaStream;
   std::vector<P2pState> p2p_;
   std::vector<std::unique_ptr<SymmetricAlloc>> symm_;
@@ -440,7 +439,11 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   unsigned char* const mc_arena = mc_ ? mc_->ptr() : nullptr;
   // Staging windows: first half of the pool for inputs, second half for outputs.
   const uint64_t half = layout_.pool_bytes / 2 / 4096 * 4096;
-  uint64_t window_elems = half / esize;
+  if (!(zin && zout) && half < 8192)
+    IBCOMM_FAIL(NOT_SUPPORTED, "Two-shot allreduce of ordinary buffers needs a pool of at least 16 KiB (IBCOMM_MEMORY_POOL_PRE_ALLOC).\n");
+  // The last 4 KiB of the input half hold the ragged end (< 16 bytes) of a message.
+  const uint64_t window_elems = TwoShotWindowElems(n, (half - 4096) / esize, esize, ws_, channels);
+  p.tail_in_off = half - 4096;
   p.stage_in = zin ? 0 : 1;
   p.stage_out = zout ? 0 : 1;
   if (zin) {
@@ -465,39 +468,6 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   }
   p.window_elems = (zin && zout) ? n : window_elems;
   if (p.window_elems == 0) p.window_elems = 1;
-  // Optional (IBCOMM_STAGE_PIPELINE=1): both buffers staged and a large
-  // message: mover CTAs copy the neighbouring windows while reducer CTAs work.
-  // Off by default: on 2 B200 it measured no faster than the sequential
-  // windows (which put every CTA on every phase) for the switch path and
-  // slower for the direct path, whose peer loads want all the CTAs.
-  const uint64_t quarter = layout_.pool_bytes / 4 / 4096 * 4096;
-  const char* pipe_env = getenv("IBCOMM_STAGE_PIPELINE");
-  const bool pipelined = pipe_env != nullptr && pipe_env[0] == '1' && !zin && !zout && bytes >= (4u << 20) && quarter / esize >= 1024;
-  if (pipelined) {
-    static int max_pairs = StagedTwoShotMaxPairs(device_);
-    int pairs = static_cast<int>(std::min<size_t>(64, std::max<size_t>(1, bytes / (256u << 10))));
-    pairs = std::min(pairs, std::min(max_pairs, std::max(1, max_channels_ / 2)));
-    if (pairs >= 1) {
-      p.window_elems = quarter / esize;
-      p.window_stride = quarter;
-      const uint64_t in_off = layout_.pool_offset, out_off = layout_.pool_offset + 2 * quarter;
-      p.mc_in = mc_arena ? mc_arena + in_off : nullptr;
-      p.mc_out = mc_arena ? mc_arena + out_off : nullptr;
-      p.local_in = arena_.ptr() + in_off;
-      p.local_out = arena_.ptr() + out_off;
-      for (int q = 0; q < ws_; ++q) {
-        p.peer_in[q] = rr_.peers.arena[q] + in_off;
-        p.peer_out[q] = rr_.peers.arena[q] + out_off;
-      }
-      IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
-      CUDACHECK(LaunchStagedTwoShotKernel(p, nullptr, 1, pairs, stream));
-      ++kernel_launches_;
-      IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
-      last_channels_override_ = 2 * pairs;
-      return;
-    }
-  }
-  last_channels_override_ = 0;
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
   CUDACHECK(LaunchNvlsKernel(p, nullptr, 1, channels, stream));
   ++kernel_launches_;
@@ -569,8 +539,7 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
   }
   MarkIssued(stream);
   last_algo_ = static_cast<int>(algo);
-  last_channels_ = last_channels_override_ > 0 ? last_channels_override_ : channels;
-  last_channels_override_ = 0;
+  last_channels_ = channels;
   Finish(stream, opts.async);
 }
 

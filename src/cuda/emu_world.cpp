@@ -23,7 +23,7 @@ struct EmuWorld::Impl {
   int max_blocks = 0;
   int last_channels = 0;
   int silent_rank = -1;
-  int direct_staging = 0;  // 0 in place, 1 staged window by window, 2 staged and pipelined
+  int direct_staging = 0;  // 0 in place, 1 staged window by window
   uint32_t last_status = 0;
   DeviceStatus last_report{};
 
@@ -118,10 +118,9 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
     // The two-shot kernel with peer loads and stores.  All ranks' buffers live
     // on this GPU, so they can be used in place; with `direct_staging` they
     // go through the pool windows like buffers the peers cannot map.
-    uint64_t half = m.layout.pool_bytes / 2 / 4096 * 4096;
-    const bool pipelined = m.direct_staging == 2;
-    const uint64_t quarter = m.layout.pool_bytes / 4 / 4096 * 4096;
-    if (pipelined) half = 2 * quarter;
+    const uint64_t half = m.layout.pool_bytes / 2 / 4096 * 4096;
+    int ch = channels > 0 ? channels : ChooseChannels(Algo::kDirect, bytes, m.ws, kMaxChannels);
+    ch = std::min(ch, cap);
     std::vector<NvlsParams> ps(static_cast<size_t>(m.ws));
     for (int r = 0; r < m.ws; ++r) {
       NvlsParams& p = ps[static_cast<size_t>(r)];
@@ -143,6 +142,8 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
       for (int q = 0; q < m.ws; ++q)
         aligned = aligned && ((reinterpret_cast<uintptr_t>(sendbufs[static_cast<size_t>(q)]) | reinterpret_cast<uintptr_t>(recvbufs[static_cast<size_t>(q)])) & 15u) == 0;
       const bool staged = m.direct_staging != 0 || !aligned;
+      if (staged && half < 8192)
+        IBCOMM_FAIL(NOT_SUPPORTED, "Two-shot allreduce through the pool needs a pool of at least 16 KiB.\n");
       p.stage_in = staged ? 1 : 0;
       p.stage_out = staged ? 1 : 0;
       for (int q = 0; q < m.ws; ++q) {
@@ -156,24 +157,12 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
       }
       p.local_in = p.peer_in[r];
       p.local_out = p.peer_out[r];
-      p.window_elems = staged ? std::max<uint64_t>(1, half / esize) : n;
-      if (pipelined) {
-        p.stage_in = p.stage_out = 1;
-        p.window_elems = std::max<uint64_t>(1, quarter / esize);
-        p.window_stride = quarter;
-      }
+      p.window_elems = staged ? TwoShotWindowElems(n, (half - 4096) / esize, esize, m.ws, ch) : std::max<uint64_t>(1, n);
+      p.tail_in_off = half - 4096;  // the ragged end of a staged message lives past every window
     }
-    int ch = channels > 0 ? channels : ChooseChannels(Algo::kDirect, bytes, m.ws, kMaxChannels);
-    ch = std::min(ch, cap);
     void* d = m.Params(ps.size() * sizeof(NvlsParams));
     CUDACHECK(cudaMemcpyAsync(d, ps.data(), ps.size() * sizeof(NvlsParams), cudaMemcpyHostToDevice, stream));
-    if (pipelined) {
-      const int pairs = std::max(1, std::min(ch, StagedTwoShotMaxPairs(m.device) / m.ws));
-      CUDACHECK(LaunchStagedTwoShotKernel(ps[0], static_cast<const NvlsParams*>(d), m.ws, pairs, stream));
-      ch = 2 * pairs;
-    } else {
-      CUDACHECK(LaunchNvlsKernel(ps[0], static_cast<const NvlsParams*>(d), m.ws, ch, stream));
-    }
+    CUDACHECK(LaunchNvlsKernel(ps[0], static_cast<const NvlsParams*>(d), m.ws, ch, stream));
     m.last_channels = ch;
   } else if (algo == Algo::kOneShot) {
     if (bytes > m.layout.oneshot_slot_bytes)

@@ -56,18 +56,16 @@ struct NvlsParams {
   unsigned char* peer_in[kMaxRanks];
   unsigned char* peer_out[kMaxRanks];
   uint64_t window_elems;
-  // Pipelined staged kernel only: the input and output areas each hold two
-  // windows, this many bytes apart.
-  uint64_t window_stride;
+  // Staged input only: byte offset (from local_in / peer_in) of the 16 bytes
+  // that hold the ragged end of the message, outside every window, so that
+  // CTA 0, which moves the ragged end, touches no bytes that belong to another
+  // CTA's part of a window.
+  uint64_t tail_in_off;
   uint64_t timeout_ns;
   DeviceStatus* status;
   uint32_t* doorbell;
 };
 cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
-// Staged buffers, pipelined: `pairs` reducer CTAs and `pairs` mover CTAs per
-// rank in one cooperative launch (they hand windows to each other).
-cudaError_t LaunchStagedTwoShotKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int pairs, cudaStream_t stream);
-int StagedTwoShotMaxPairs(int device);
 
 // ---- one-shot allreduce for small messages (push to every peer, sum locally) ----
 struct OneShotParams {

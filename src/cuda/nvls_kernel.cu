@@ -52,6 +52,7 @@ __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
   T* recvbuf = static_cast<T*>(p.recvbuf);
   const bool do_scale = p.scale != 1.0;
   uint32_t phase = 0;
+  const uint64_t full_nvec = (p.window_elems + kVecElems - 1) / kVecElems;
 
   for (uint64_t w0 = 0; w0 < p.len_elements; w0 += p.window_elems) {
     const uint64_t wn = (p.len_elements - w0 < p.window_elems) ? p.len_elements - w0 : p.window_elems;
@@ -66,9 +67,8 @@ __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
       uint4* dst = reinterpret_cast<uint4*>(p.local_in);
       const bool src_aligned = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
       for (int s = 0; s < p.world_size; ++s) {
-        uint64_t sb, se, b, e;
-        SubRange(0, nvec, s, p.world_size, &sb, &se);
-        SubRange(sb, se, cta, ncta, &b, &e);
+        uint64_t b, e;
+        WindowPart(full_nvec, nvec, s, p.world_size, cta, ncta, &b, &e);
         if (src_aligned) {
           CopyVectors<false>(dst, src, b, e);
         } else {
@@ -78,17 +78,16 @@ __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
         }
       }
       if (cta == 0) {
-        T* dt = reinterpret_cast<T*>(p.local_in);
-        for (uint64_t i = tail0 + threadIdx.x; i < wn; i += blockDim.x) dt[i] = sendbuf[w0 + i];
+        T* dt = reinterpret_cast<T*>(p.local_in + p.tail_in_off);
+        for (uint64_t i = tail0 + threadIdx.x; i < wn; i += blockDim.x) dt[i - tail0] = sendbuf[w0 + i];
       }
     }
     if (!CrossRankBarrier(p, w, cta, ++phase, &s_stop)) return;
 
     // (2) reduce my shard in the switch and broadcast it.
     {
-      uint64_t sb, se, b, e;
-      SubRange(0, nvec, p.rank, p.world_size, &sb, &se);
-      SubRange(sb, se, cta, ncta, &b, &e);
+      uint64_t b, e;
+      WindowPart(full_nvec, nvec, p.rank, p.world_size, cta, ncta, &b, &e);
       const unsigned char* mi = p.mc_in + win_bytes_off;
       unsigned char* mo = p.mc_out + wout_bytes_off;
       if (kMultimem) {
@@ -147,8 +146,11 @@ __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
     const bool has_tail = cta == 0 && tail0 + threadIdx.x < wn;
     if (has_tail) {
       const uint64_t i = tail0 + threadIdx.x;
-      for (int q = 0; q < p.world_size; ++q)
-        tail_acc += ToAcc<A, T>(LdScalarStrong<T>(reinterpret_cast<const T*>(p.peer_in[q] + win_bytes_off) + i));
+      for (int q = 0; q < p.world_size; ++q) {
+        const T* src = p.stage_in ? reinterpret_cast<const T*>(p.peer_in[q] + p.tail_in_off) + (i - tail0)
+                                  : reinterpret_cast<const T*>(p.peer_in[q] + win_bytes_off) + i;
+        tail_acc += ToAcc<A, T>(LdScalarStrong<T>(src));
+      }
       if (do_scale) tail_acc = ScaleAcc<A>(tail_acc, p.scale);
     }
     if (!CrossRankBarrier(p, w, cta, ++phase, &s_stop)) return;
@@ -164,9 +166,8 @@ __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
       uint4* dst = reinterpret_cast<uint4*>(recvbuf + w0);
       const bool dst_aligned = (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
       for (int s = 0; s < p.world_size; ++s) {
-        uint64_t sb, se, b, e;
-        SubRange(0, nvec, s, p.world_size, &sb, &se);
-        SubRange(sb, se, cta, ncta, &b, &e);
+        uint64_t b, e;
+        WindowPart(full_nvec, nvec, s, p.world_size, cta, ncta, &b, &e);
         if (dst_aligned) {
           CopyVectors<true>(dst, src, b, e);
         } else {

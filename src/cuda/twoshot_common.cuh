@@ -1,5 +1,4 @@
-// Helpers shared by the two-shot allreduce kernels (nvls_kernel.cu and
-// staged_kernel.cu): multimem accessors, vector copies, range splitting and
+// Helpers of the two-shot allreduce kernel (nvls_kernel.cu): multimem accessors, vector copies, range splitting and
 // the per-CTA cross-rank barrier.
 #pragma once
 
@@ -86,6 +85,23 @@ __device__ __forceinline__ void SubRange(uint64_t lo, uint64_t hi, int part, int
   if (y > hi) y = hi;
   *b = x;
   *e = y;
+}
+
+// Part `part` of `parts` of shard `s` of a window, in 16-byte vectors.  The
+// split is that of a FULL window (`full_nvec` vectors) clipped to the `nvec`
+// vectors this window holds: a CTA then covers the same bytes of the staging
+// windows in every window of a call, the short last one included.  The
+// barriers are per CTA, so they order a CTA's accesses only against the same
+// CTA of the other ranks; a split that moved with the window's length would
+// let a CTA that is one window ahead overwrite bytes that another CTA has not
+// copied out yet.
+__device__ __forceinline__ void WindowPart(uint64_t full_nvec, uint64_t nvec, int s, int ws, int part, int parts, uint64_t* b,
+                                           uint64_t* e) {
+  uint64_t sb, se;
+  SubRange(0, full_nvec, s, ws, &sb, &se);
+  SubRange(sb, se, part, parts, b, e);
+  if (*b > nvec) *b = nvec;
+  if (*e > nvec) *e = nvec;
 }
 
 // Barrier between CTA `cta` of every rank.  Returns false when it gave up.

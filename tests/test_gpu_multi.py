@@ -43,8 +43,8 @@ def test_symmetric_zero_copy(bins, np_):
 
 
 @needs2
-def test_pipelined_staging_kernel(bins):
-    code, err = run(bins, min(NGPU, 4), "pipeline", env={"IBCOMM_STAGE_PIPELINE": "1"})
+def test_staged_buffers_over_several_windows(bins):
+    code, err = run(bins, min(NGPU, 4), "staged")
     assert code == 0, err
 
 
