@@ -75,6 +75,8 @@ def _declare(lib) -> None:
         "ibcomm_check": [vp],
         "ibcomm_symmetric_alloc": [vp, sz, C.POINTER(vp)],
         "ibcomm_symmetric_free": [vp, vp],
+        "ibcomm_register_buffer": [vp, vp, sz, C.POINTER(C.c_int)],
+        "ibcomm_deregister_buffer": [vp, C.c_int],
         "ibcomm_get_device_info": [vp, i, C.POINTER(DeviceInfo)],
         "ibcomm_set_timer_base": [vp],
         "ibcomm_dump_trace": [vp],

@@ -61,6 +61,7 @@ class Communicator:
         self.world_size = world_size
         self.rank = -1
         self._symmetric = []
+        self._registered = {}
         if rank is not None:
             self.register_myself(rank)
 
@@ -264,6 +265,31 @@ class Communicator:
         raw = torch.as_tensor(_CudaArray(out.value, max(nbytes, 16), self), device=torch.device("cuda", torch.cuda.current_device()))
         self._symmetric.append(out.value)
         return raw[:nbytes].view(dtype)
+
+    def register(self, tensor: torch.Tensor) -> int:
+        """Maps an ordinary CUDA tensor of every rank (same byte size) into the peers.
+
+        Collective.  Allreduces on the tensor (or on the same slice of it on every
+        rank) then run without staging copies, like tensors from `symmetric_empty`
+        but with peer loads/stores instead of the switch reduction.  Returns a
+        registration id, or -1 (on every rank) when the allocator's memory cannot
+        be shared through CUDA IPC (e.g. expandable segments); the tensor keeps
+        working through the staging pool then.  The communicator holds a
+        reference to the tensor until `deregister`."""
+        if not tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError("register needs a contiguous CUDA tensor")
+        rid = C.c_int(-1)
+        check(_native.lib().ibcomm_register_buffer(self._h, C.c_void_p(tensor.data_ptr()),
+                                                   tensor.numel() * tensor.element_size(), C.byref(rid)))
+        if rid.value >= 0:
+            self._registered[rid.value] = tensor
+        return rid.value
+
+    def deregister(self, rid: int) -> None:
+        """Collective: drops a registration made by `register`."""
+        if rid in self._registered:
+            check(_native.lib().ibcomm_deregister_buffer(self._h, int(rid)))
+            del self._registered[rid]
 
     def device_info(self, connect: bool = False) -> dict:
         info = _native.DeviceInfo()

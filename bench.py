@@ -260,6 +260,17 @@ def main() -> int:
                 t = time_steps(lambda: comm.allreduce(a, b, algo=algo, scale=scale), k, w)
                 per_algo[name] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world),
                                   "channels": comm.device_info()["last_channels"]}
+            # Ordinary tensors registered with the communicator (CUDA IPC): no staging.
+            reg_in, reg_out = plain_in.clone(), torch.empty_like(plain_in)
+            rids = [comm.register(reg_in), comm.register(reg_out)]
+            if min(rids) >= 0:
+                t = time_steps(lambda: comm.allreduce(reg_in, reg_out, scale=scale), k, w)
+                per_algo["auto_registered"] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world),
+                                               "algo": comm.device_info()["last_algo"],
+                                               "channels": comm.device_info()["last_channels"]}
+            for rid in rids:
+                comm.deregister(rid)
+            del reg_in, reg_out
             t = time_steps(lambda: comm.allreduce(plain_in, plain_out, algo="ring", scale=scale, wire=torch.bfloat16), k, w)
             per_algo["ring_bf16_wire"] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world)}
             nccl_buf = plain_in.clone()
@@ -352,6 +363,10 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
     plain_in.copy_(torch.rand(nmax, dtype=torch.float32, device=dev, generator=g) * 2 - 1)
     sym_in.copy_(plain_in)
     nccl_buf = torch.empty(nmax, dtype=torch.float32, device=dev)
+    registered = False
+    if world > 1:
+        reg_in, reg_out = plain_in.clone(), torch.empty_like(plain_in)
+        registered = min(comm.register(reg_in), comm.register(reg_out)) >= 0
     size = 4096
     while size <= max_bytes:
         n = size // 4
@@ -366,6 +381,8 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
             if info["nvls"]:
                 algos += [("nvls", plain_in, plain_out), ("nvls_zero_copy", sym_in, sym_out)]
             algos.append(("auto_plain", plain_in, plain_out))
+            if registered:
+                algos.append(("auto_registered", reg_in, reg_out))
             algos.append(("auto", sym_in, sym_out))
         else:
             algos.append(("auto", plain_in, plain_out))

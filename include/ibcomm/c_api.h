@@ -59,6 +59,11 @@ int ibcomm_check(ibcomm_comm* c);
  * Collective: every rank calls with the same size in the same order. */
 int ibcomm_symmetric_alloc(ibcomm_comm* c, size_t bytes, void** out);
 int ibcomm_symmetric_free(ibcomm_comm* c, void* ptr);
+/* Collective: maps a cudaMalloc'ed buffer of every rank (same size) into the
+ * peers, so that allreduces on it skip the staging copies.  *id = -1 (on every
+ * rank) when the memory cannot be shared; that is not an error. */
+int ibcomm_register_buffer(ibcomm_comm* c, void* ptr, size_t bytes, int* id);
+int ibcomm_deregister_buffer(ibcomm_comm* c, int id);
 
 typedef struct {
   int device;

@@ -126,6 +126,16 @@ class Communicator {
                      const CudaAllreduceOptions& opts);
   // Allocates the staging pool and the work region (lazily called by Init).
   void PrepareMemoryPool();
+  // Collective: maps this rank's device buffer (cudaMalloc'ed memory, any
+  // position inside its allocation) into every peer, the device analogue of
+  // the reference's memory registration (ibv_reg_mr of a user region).
+  // Allreduces on the buffer, or on the same sub-range of it on every rank,
+  // then skip the staging copies (direct algorithm).  Every rank passes the
+  // same size.  Returns a registration id, or -1 on every rank when some
+  // rank's memory cannot be shared (the buffers then keep going through the
+  // pool).  The caller keeps the memory allocated until DeregisterCudaBuffer.
+  int RegisterCudaBuffer(void* ptr, size_t bytes);
+  void DeregisterCudaBuffer(int id);
   DeviceContext* device() { return device_.get(); }
 #endif
 

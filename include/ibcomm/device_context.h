@@ -72,6 +72,10 @@ void DeviceContextSetMaxChannels(DeviceContext* d, int channels);
 void* DeviceContextSymmetricAlloc(Communicator* comm, size_t bytes);
 void DeviceContextSymmetricFree(Communicator* comm, void* ptr);
 
+// Buffer registration (see Communicator::RegisterCudaBuffer).
+int DeviceContextRegisterBuffer(Communicator* comm, void* ptr, size_t bytes);
+void DeviceContextDeregisterBuffer(Communicator* comm, int id);
+
 // Reads the failure doorbell; on failure fetches the report, resets it and
 // raises TRANSPORT_ERROR.  Called after every synchronous collective; callers
 // of asynchronous collectives call it after they synchronised their stream.

@@ -37,6 +37,36 @@ struct SymmetricAlloc {
   size_t bytes = 0;
 };
 
+// A user buffer (any cudaMalloc'ed memory, e.g. a tensor of a framework's
+// caching allocator) that the peers have mapped through CUDA IPC.
+struct RegisteredBuffer {
+  int id = -1;
+  unsigned char* ptr = nullptr;
+  size_t bytes = 0;
+  unsigned char* peer_ptr[kMaxRanks] = {nullptr};
+  unsigned long long peer_alloc[kMaxRanks] = {0};  // key of the peer's imported allocation
+};
+
+// One peer allocation opened with cudaIpcOpenMemHandle.  A process may open a
+// given allocation only once, so registrations inside the same allocation
+// share the mapping.
+struct ImportedIpc {
+  int peer = -1;
+  unsigned long long alloc_id = 0;  // the exporter's CU_POINTER_ATTRIBUTE_BUFFER_ID
+  void* base = nullptr;
+  int refs = 0;
+};
+
+// What the ranks tell each other about a buffer they register.
+struct RegisterMsg {
+  cudaIpcMemHandle_t handle;
+  uint64_t offset;    // of the buffer inside the allocation
+  uint64_t bytes;
+  uint64_t alloc_id;
+  int32_t ok;
+  int32_t pid;
+};
+
 struct LoopbackSend {
   const void* buf;
   size_t len;
@@ -63,6 +93,8 @@ class DeviceContext {
 
   void* SymmetricAlloc_(size_t bytes);
   void SymmetricFree_(void* ptr);
+  int RegisterBuffer(void* ptr, size_t bytes);
+  void DeregisterBuffer(int id);
   void CollectTrace(Tracer* tracer);
   DeviceInfo Info() const;
   void SetMaxChannels(int c) { max_channels_ = c > 0 ? std::min(c, kMaxChannels) : std::min(env::ReadNumCudaStream(), kMaxChannels); }
@@ -81,6 +113,10 @@ class DeviceContext {
   void Finish(cudaStream_t stream, bool async);
   bool IsLoopback(int peer) const;
   const SymmetricAlloc* FindSymmetric(const void* p, size_t bytes) const;
+  // Peer pointers of a buffer every rank has mapped (symmetric memory or a
+  // registered buffer); false when the buffer is neither.
+  bool FindPeerMapped(const void* p, size_t bytes, unsigned char** peer_ptr) const;
+  template <typename M> void ExchangeWithAll(const M& mine, std::vector<M>* all);
 
   void RunCopy(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, cudaStream_t stream);
   void RunProgram(Algo algo, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
@@ -117,6 +153,9 @@ class DeviceContext {
   int max_channels_ = env::kDefaultNumCudaStream;
   std::vector<P2pState> p2p_;
   std::vector<std::unique_ptr<SymmetricAlloc>> symm_;
+  std::vector<RegisteredBuffer> registered_;
+  std::vector<ImportedIpc> ipc_imports_;
+  int next_registration_ = 0;
   // tracing
   DeviceTraceRec* d_trace_ = nullptr;
   int trace_capacity_ = 0;
@@ -175,6 +214,9 @@ DeviceContext::~DeviceContext() {
     if (s.recv_done) cudaEventDestroy(s.recv_done);
   }
   cache_.Clear();
+  for (ImportedIpc& imp : ipc_imports_) cudaIpcCloseMemHandle(imp.base);
+  ipc_imports_.clear();
+  registered_.clear();
   symm_.clear();
   mc_.reset();
   peer_arenas_.clear();
@@ -371,6 +413,159 @@ const SymmetricAlloc* DeviceContext::FindSymmetric(const void* p, size_t bytes) 
   return nullptr;
 }
 
+bool DeviceContext::FindPeerMapped(const void* p, size_t bytes, unsigned char** peer_ptr) const {
+  const unsigned char* c = static_cast<const unsigned char*>(p);
+  if (const SymmetricAlloc* s = FindSymmetric(p, bytes)) {
+    const size_t off = static_cast<size_t>(c - s->mine->ptr());
+    for (int q = 0; q < ws_; ++q) peer_ptr[q] = s->peer_ptr[q] + off;
+    return true;
+  }
+  for (const RegisteredBuffer& r : registered_) {
+    if (c >= r.ptr && c + bytes <= r.ptr + r.bytes) {
+      const size_t off = static_cast<size_t>(c - r.ptr);
+      for (int q = 0; q < ws_; ++q) peer_ptr[q] = r.peer_ptr[q] + off;
+      return true;
+    }
+  }
+  return false;
+}
+
+template <typename M>
+void DeviceContext::ExchangeWithAll(const M& mine, std::vector<M>* all) {
+  all->assign(static_cast<size_t>(ws_), mine);
+  for (int q = 0; q < ws_; ++q) {
+    if (q == rank_) continue;
+    comm_->PostSend(q, &mine, sizeof(M));
+    comm_->PostRecv(q, &(*all)[static_cast<size_t>(q)], sizeof(M));
+  }
+  for (int q = 0; q < ws_; ++q) {
+    if (q == rank_) continue;
+    comm_->WaitRecvCompletion(q);
+    --comm_->eps_[static_cast<size_t>(q)].recv_completions;
+    comm_->WaitSendCompletion(q);
+    --comm_->eps_[static_cast<size_t>(q)].send_completions;
+  }
+}
+
+// Collective.  Every rank passes its own buffer (the addresses and the
+// positions inside the underlying allocations may differ, the sizes may
+// not); afterwards two-shot collectives on the buffer, or on the same
+// sub-range of it on every rank, load from and store into the peers' copies
+// directly.  Returns -1, on every rank alike, when some rank's memory cannot
+// be shared this way (not from cudaMalloc, e.g. a virtual-memory allocation,
+// or a peer in the same process); such buffers keep going through the pool.
+int DeviceContext::RegisterBuffer(void* ptr, size_t bytes) {
+  if (ptr == nullptr || bytes == 0) IBCOMM_FAIL(INVALID_ARGUMENT, "RegisterBuffer: empty buffer.\n");
+  ConnectPeers();
+  RegisteredBuffer reg;
+  reg.ptr = static_cast<unsigned char*>(ptr);
+  reg.bytes = bytes;
+  reg.peer_ptr[rank_] = reg.ptr;
+  if (ws_ == 1) {
+    reg.id = next_registration_++;
+    registered_.push_back(reg);
+    return reg.id;
+  }
+  RegisterMsg mine;
+  memset(&mine, 0, sizeof(mine));
+  mine.bytes = bytes;
+  mine.pid = static_cast<int32_t>(getpid());
+  const drv::Api* api = drv::Get();
+  if (api != nullptr) {
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    unsigned long long alloc_id = 0;
+    const CUdeviceptr p = reinterpret_cast<CUdeviceptr>(ptr);
+    if (api->MemGetAddressRange(&base, &size, p) == CUDA_SUCCESS && p + bytes <= base + size &&
+        api->PointerGetAttribute(&alloc_id, CU_POINTER_ATTRIBUTE_BUFFER_ID, p) == CUDA_SUCCESS &&
+        cudaIpcGetMemHandle(&mine.handle, reinterpret_cast<void*>(base)) == cudaSuccess) {
+      mine.offset = p - base;
+      mine.alloc_id = alloc_id;
+      mine.ok = 1;
+    }
+    (void)cudaGetLastError();
+  }
+  std::vector<RegisterMsg> all;
+  ExchangeWithAll(mine, &all);
+  bool ok = true;
+  for (int q = 0; q < ws_; ++q) {
+    const RegisterMsg& m = all[static_cast<size_t>(q)];
+    ok = ok && m.ok != 0 && m.bytes == bytes && (q == rank_ || m.pid != mine.pid);
+  }
+  // Map the peers' allocations (once per allocation).
+  std::vector<size_t> opened;  // entries of ipc_imports_ whose count this call raised
+  if (ok) {
+    for (int q = 0; q < ws_ && ok; ++q) {
+      if (q == rank_) continue;
+      const RegisterMsg& m = all[static_cast<size_t>(q)];
+      size_t at = ipc_imports_.size();
+      for (size_t i = 0; i < ipc_imports_.size(); ++i)
+        if (ipc_imports_[i].peer == q && ipc_imports_[i].alloc_id == m.alloc_id) at = i;
+      if (at == ipc_imports_.size()) {
+        void* base = nullptr;
+        if (cudaIpcOpenMemHandle(&base, m.handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+          (void)cudaGetLastError();
+          ok = false;
+          break;
+        }
+        ImportedIpc imp;
+        imp.peer = q;
+        imp.alloc_id = m.alloc_id;
+        imp.base = base;
+        ipc_imports_.push_back(imp);
+      }
+      ++ipc_imports_[at].refs;
+      opened.push_back(at);
+      reg.peer_ptr[q] = static_cast<unsigned char*>(ipc_imports_[at].base) + m.offset;
+      reg.peer_alloc[q] = m.alloc_id;
+    }
+  }
+  // Second round: all ranks mapped everything, or nobody keeps anything.
+  int32_t mapped = ok ? 1 : 0;
+  std::vector<int32_t> all_mapped;
+  ExchangeWithAll(mapped, &all_mapped);
+  for (int32_t v : all_mapped) ok = ok && v != 0;
+  if (!ok) {
+    for (size_t at : opened) --ipc_imports_[at].refs;
+    for (size_t i = ipc_imports_.size(); i-- > 0;) {
+      if (ipc_imports_[i].refs == 0) {
+        (void)cudaIpcCloseMemHandle(ipc_imports_[i].base);
+        ipc_imports_.erase(ipc_imports_.begin() + static_cast<long>(i));
+      }
+    }
+    (void)cudaGetLastError();
+    return -1;
+  }
+  reg.id = next_registration_++;
+  registered_.push_back(reg);
+  return reg.id;
+}
+
+// Collective by contract: no rank may still run a collective on the buffer.
+void DeviceContext::DeregisterBuffer(int id) {
+  for (size_t i = 0; i < registered_.size(); ++i) {
+    if (registered_[i].id != id) continue;
+    CUDACHECK(cudaDeviceSynchronize());
+    if (ws_ > 1) comm_->Barrier();  // the peers' kernels on this buffer are done, too
+    const RegisteredBuffer reg = registered_[i];
+    registered_.erase(registered_.begin() + static_cast<long>(i));
+    for (int q = 0; q < ws_; ++q) {
+      if (q == rank_ || reg.peer_ptr[q] == nullptr) continue;
+      for (size_t k = 0; k < ipc_imports_.size(); ++k) {
+        ImportedIpc& imp = ipc_imports_[k];
+        if (imp.peer != q || imp.alloc_id != reg.peer_alloc[q]) continue;
+        if (--imp.refs == 0) {
+          CUDACHECK(cudaIpcCloseMemHandle(imp.base));
+          ipc_imports_.erase(ipc_imports_.begin() + static_cast<long>(k));
+        }
+        break;
+      }
+    }
+    return;
+  }
+  IBCOMM_FAIL(INVALID_ARGUMENT, "DeregisterBuffer: unknown registration %d.\n", id);
+}
+
 void DeviceContext::RunCopy(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, cudaStream_t stream) {
   if (sendbuf == recvbuf && scale == 1.0) return;
   CopyParams cp{sendbuf, recvbuf, n, static_cast<int32_t>(dtype), static_cast<int32_t>(dtype), scale};
@@ -434,8 +629,20 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   const SymmetricAlloc* sout = FindSymmetric(recvbuf, bytes);
   // Zero-copy needs the buffer mapped by the peers and, for the switch path,
   // bound to a multicast object.
-  const bool zin = sin != nullptr && (sin->mc || !multimem) && (reinterpret_cast<uintptr_t>(sendbuf) & 15u) == 0;
-  const bool zout = sout != nullptr && (sout->mc || !multimem) && (reinterpret_cast<uintptr_t>(recvbuf) & 15u) == 0;
+  // The direct variant also takes buffers the peers mapped by registration.
+  unsigned char* reg_in[kMaxRanks];
+  unsigned char* reg_out[kMaxRanks];
+  bool rin = !multimem && sin == nullptr && FindPeerMapped(sendbuf, bytes, reg_in);
+  bool rout = !multimem && sout == nullptr && FindPeerMapped(recvbuf, bytes, reg_out);
+  // Registered buffers sit at different offsets on different ranks: all
+  // ranks must come to the same verdict, so every rank's pointer has to be
+  // 16-byte aligned (the mappings' bases are), not only this rank's.
+  for (int q = 0; q < ws_; ++q) {
+    if (rin && (reinterpret_cast<uintptr_t>(reg_in[q]) & 15u) != 0) rin = false;
+    if (rout && (reinterpret_cast<uintptr_t>(reg_out[q]) & 15u) != 0) rout = false;
+  }
+  const bool zin = (rin || (sin != nullptr && (sin->mc || !multimem))) && (reinterpret_cast<uintptr_t>(sendbuf) & 15u) == 0;
+  const bool zout = (rout || (sout != nullptr && (sout->mc || !multimem))) && (reinterpret_cast<uintptr_t>(recvbuf) & 15u) == 0;
   unsigned char* const mc_arena = mc_ ? mc_->ptr() : nullptr;
   // Staging windows: first half of the pool for inputs, second half for outputs.
   const uint64_t half = layout_.pool_bytes / 2 / 4096 * 4096;
@@ -446,7 +653,11 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   p.tail_in_off = half - 4096;
   p.stage_in = zin ? 0 : 1;
   p.stage_out = zout ? 0 : 1;
-  if (zin) {
+  if (zin && rin) {
+    p.mc_in = nullptr;
+    p.local_in = reg_in[rank_];
+    for (int q = 0; q < ws_; ++q) p.peer_in[q] = reg_in[q];
+  } else if (zin) {
     const size_t off = static_cast<const unsigned char*>(sendbuf) - sin->mine->ptr();
     p.mc_in = sin->mc ? sin->mc->ptr() + off : nullptr;
     p.local_in = sin->mine->ptr() + off;
@@ -456,7 +667,11 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
     p.local_in = arena_.ptr() + layout_.pool_offset;
     for (int q = 0; q < ws_; ++q) p.peer_in[q] = rr_.peers.arena[q] + layout_.pool_offset;
   }
-  if (zout) {
+  if (zout && rout) {
+    p.mc_out = nullptr;
+    p.local_out = reg_out[rank_];
+    for (int q = 0; q < ws_; ++q) p.peer_out[q] = reg_out[q];
+  } else if (zout) {
     const size_t off = static_cast<unsigned char*>(recvbuf) - sout->mine->ptr();
     p.mc_out = sout->mc ? sout->mc->ptr() + off : nullptr;
     p.local_out = sout->mine->ptr() + off;
@@ -498,8 +713,12 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
   const bool nvls_ok = mc_ != nullptr && NvlsSupportsDType(dtype) && wire == dtype;
   int channels;
   if (algo == Algo::kAuto) {
-    const bool zero_copy = FindSymmetric(sendbuf, bytes) != nullptr && FindSymmetric(recvbuf, bytes) != nullptr;
-    TunerChoice c = ChooseAlgorithm(bytes, ws_, nvls_ok, zero_copy, max_channels_);
+    const bool symmetric = FindSymmetric(sendbuf, bytes) != nullptr && FindSymmetric(recvbuf, bytes) != nullptr;
+    unsigned char* unused[kMaxRanks];
+    // Registered buffers are mapped by the peers but not bound to the
+    // multicast object: zero-copy for the direct algorithm only.
+    const bool mapped = symmetric || (FindPeerMapped(sendbuf, bytes, unused) && FindPeerMapped(recvbuf, bytes, unused));
+    TunerChoice c = ChooseAlgorithm(bytes, ws_, nvls_ok && (symmetric || !mapped), mapped, max_channels_);
     algo = c.algo;
     channels = c.channels;
     if ((algo == Algo::kOneShot && (bytes > layout_.oneshot_slot_bytes || wire != dtype)) ||
@@ -768,6 +987,17 @@ void DeviceContextSymmetricFree(Communicator* comm, void* ptr) {
   if (comm->device() == nullptr) IBCOMM_FAIL(INVALID_ARGUMENT, "SymmetricFree: no device context.\n");
   comm->device()->SymmetricFree_(ptr);
 }
+
+int DeviceContextRegisterBuffer(Communicator* comm, void* ptr, size_t bytes) {
+  comm->PrepareMemoryPool();
+  return comm->device()->RegisterBuffer(ptr, bytes);
+}
+void DeviceContextDeregisterBuffer(Communicator* comm, int id) {
+  if (comm->device() == nullptr) IBCOMM_FAIL(INVALID_ARGUMENT, "DeregisterBuffer: no device context.\n");
+  comm->device()->DeregisterBuffer(id);
+}
+int Communicator::RegisterCudaBuffer(void* ptr, size_t bytes) { return DeviceContextRegisterBuffer(this, ptr, bytes); }
+void Communicator::DeregisterCudaBuffer(int id) { DeviceContextDeregisterBuffer(this, id); }
 
 void DeviceContextDeleter::operator()(DeviceContext* d) const { delete d; }
 

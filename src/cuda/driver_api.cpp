@@ -41,6 +41,8 @@ static void LoadAll() {
   ok &= Load("cuMemSetAccess", &g_api.MemSetAccess);
   ok &= Load("cuMemExportToShareableHandle", &g_api.MemExportToShareableHandle);
   ok &= Load("cuMemImportFromShareableHandle", &g_api.MemImportFromShareableHandle);
+  ok &= Load("cuMemGetAddressRange", &g_api.MemGetAddressRange);
+  ok &= Load("cuPointerGetAttribute", &g_api.PointerGetAttribute);
   bool mc = true;
   mc &= Load("cuMulticastCreate", &g_api.MulticastCreate);
   mc &= Load("cuMulticastAddDevice", &g_api.MulticastAddDevice);

@@ -237,6 +237,28 @@ int ibcomm_symmetric_free(ibcomm_comm* c, void* ptr) {
   });
 }
 
+int ibcomm_register_buffer(ibcomm_comm* c, void* ptr, size_t bytes, int* id) {
+  return Guard([&] {
+    NeedCuda();
+#ifdef USE_CUDA
+    *id = ibcomm::DeviceContextRegisterBuffer(&c->comm, ptr, bytes);
+#else
+    (void)c; (void)ptr; (void)bytes; (void)id;
+#endif
+  });
+}
+
+int ibcomm_deregister_buffer(ibcomm_comm* c, int id) {
+  return Guard([&] {
+    NeedCuda();
+#ifdef USE_CUDA
+    ibcomm::DeviceContextDeregisterBuffer(&c->comm, id);
+#else
+    (void)c; (void)id;
+#endif
+  });
+}
+
 int ibcomm_get_device_info(ibcomm_comm* c, int connect, ibcomm_device_info* out) {
   return Guard([&] {
     NeedCuda();

@@ -114,6 +114,51 @@ def case_symmetric(comm):
     return 0
 
 
+def case_registered(comm):
+    """Ordinary torch tensors mapped into the peers (CUDA IPC): direct two-shot without staging."""
+    rc = 0
+    # Ranks allocate differently first, so that the tensors sit at different
+    # offsets of their allocations on different ranks.
+    pad = torch.empty(1000 * (RANK + 1), device="cuda")
+    for n in (1000, (4 << 20) + 4):
+        x = torch.empty(n, device="cuda")
+        y = torch.empty(n, device="cuda")
+        rx, ry = comm.register(x), comm.register(y)
+        if rx < 0 or ry < 0:
+            print(f"rank {RANK}: registration not available", file=sys.stderr)
+            return 1
+        for it in range(2):
+            x.copy_(seeded(n, torch.float32, RANK, seed=it))
+            comm.allreduce(x, y, scale=1.0 / WS, sync=True)
+            algo = comm.device_info()["last_algo"]
+            if n > (1 << 20) and algo != "direct":
+                print(f"rank {RANK}: registered buffers ran {algo}", file=sys.stderr)
+                rc = 1
+            if not close(y, expected(n, torch.float32, 1.0 / WS, seed=it), torch.float32):
+                print(f"rank {RANK}: registered out-of-place n={n} mismatch", file=sys.stderr)
+                rc = 1
+            # A slice at an odd element (not 16-byte aligned): staged on every rank alike.
+            comm.allreduce(x[1:], y[1:], algo="direct", sync=True)
+            if not close(y[1:], expected(n, torch.float32, 1.0, seed=it)[1:], torch.float32):
+                print(f"rank {RANK}: registered odd slice n={n} mismatch", file=sys.stderr)
+                rc = 1
+            # An aligned slice, in place.
+            comm.allreduce(x[4:], algo="direct", sync=True)
+            if not close(x[4:], expected(n, torch.float32, 1.0, seed=it)[4:], torch.float32):
+                print(f"rank {RANK}: registered in-place slice n={n} mismatch", file=sys.stderr)
+                rc = 1
+        comm.deregister(rx)
+        comm.deregister(ry)
+        # Without the registration the same tensors go through the pool again.
+        x.copy_(seeded(n, torch.float32, RANK, seed=7))
+        comm.allreduce(x, y, sync=True)
+        if not close(y, expected(n, torch.float32, 1.0, seed=7), torch.float32):
+            print(f"rank {RANK}: after deregistration n={n} mismatch", file=sys.stderr)
+            rc = 1
+    del pad
+    return rc
+
+
 def case_sendrecv(comm):
     """Device buffers through the mailbox kernels; ring of neighbours plus a broadcast."""
     comm.device_info(connect=True)

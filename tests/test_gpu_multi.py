@@ -43,6 +43,12 @@ def test_symmetric_zero_copy(bins, np_):
 
 
 @needs2
+def test_registered_user_buffers(bins):
+    code, err = run(bins, min(NGPU, 4), "registered")
+    assert code == 0, err
+
+
+@needs2
 def test_staged_buffers_over_several_windows(bins):
     code, err = run(bins, min(NGPU, 4), "staged")
     assert code == 0, err
