@@ -55,6 +55,7 @@ def parse_args():
     ap.add_argument("--algo", default="auto")
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--sweep-max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--sweep-algos", default="", help="comma-separated columns of the sweep to measure (default: all)")
     ap.add_argument("--out", default=None)
     ap.add_argument("--write-tuning", default=None, metavar="PATH",
                     help="with --sweep: write the fastest algorithm per size as an IBCOMM_TUNING_FILE table")
@@ -367,6 +368,14 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
     if world > 1:
         reg_in, reg_out = plain_in.clone(), torch.empty_like(plain_in)
         registered = min(comm.register(reg_in), comm.register(reg_out)) >= 0
+    # Bring the clocks up before the smallest (latency-bound) sizes are timed.
+    burn = torch.randn(4096, 4096, device=dev, dtype=torch.bfloat16)
+    t_end = time.time() + 1.0
+    while time.time() < t_end:
+        for _ in range(20):
+            burn @ burn
+        torch.cuda.synchronize()
+    del burn
     size = 4096
     while size <= max_bytes:
         n = size // 4
@@ -386,7 +395,10 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
             algos.append(("auto", sym_in, sym_out))
         else:
             algos.append(("auto", plain_in, plain_out))
+        only = [s for s in args.sweep_algos.split(",") if s]
         for name, a, b in algos:
+            if only and name not in only:
+                continue
             algo = name.split("_")[0]
             try:
                 t = time_steps(lambda: comm.allreduce(a[:n], b[:n], algo=algo, scale=1.0 / world), steps, warm)

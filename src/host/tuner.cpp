@@ -107,7 +107,9 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
       // messages go direct there.
       a = Algo::kNvls;
     } else {
-      a = bytes <= (256u << 10) ? Algo::kOneShot : Algo::kDirect;
+      // Peer-mapped without the switch (registered buffers, no multicast, two
+      // ranks): one push per peer wins while the fan-out is small.
+      a = bytes <= (world_size > 4 ? (16u << 10) : (512u << 10)) ? Algo::kOneShot : Algo::kDirect;
     }
   } else if (bytes <= (512u << 10)) {
     a = Algo::kOneShot;  // ordinary buffers: one push per peer beats three staged phases
