@@ -65,6 +65,8 @@ PROGRAMS = [
     ("sendrecv", "tests/cpp/sendrecv_test.cpp", False),
     ("unittest", "tests/cpp/unittest.cpp", False),
     ("schedule_sim", "tests/cpp/schedule_sim.cpp", False),
+    ("threads_test", "tests/cpp/threads_test.cpp", False),
+    ("threads_test_cuda", "tests/cpp/threads_test.cpp", True),
 ]
 
 CXXFLAGS = ["-std=c++17", "-O2", "-g", "-fPIC", "-Wall", "-Wextra", "-pthread", f"-I{ROOT / 'include'}"]

@@ -1,6 +1,7 @@
 """Multi-GPU tests: one process per GPU over real peer mappings (and NVSwitch
 multicast where the box has it).  Skipped on machines with one GPU, where the
 same kernels are covered by the emulated ranks of test_gpu_emu.py."""
+import os
 import subprocess
 import sys
 from pathlib import Path
@@ -40,6 +41,16 @@ def test_allreduce_every_algorithm(bins, np_):
 def test_symmetric_zero_copy(bins, np_):
     code, err = run(bins, np_, "symmetric")
     assert code == 0, err
+
+
+@needs2
+def test_ranks_as_threads_of_one_process(bins):
+    # One process, one host thread and one communicator per GPU.
+    np_ = min(NGPU, 4)
+    p = subprocess.run(["timeout", "300s", bins["threads_test_cuda"], "cuda", str(np_)], stdout=subprocess.PIPE,
+                       stderr=subprocess.PIPE, text=True, env={**os.environ, "IBCOMM_TIMEOUT_MS": "5000"})
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert "threads_test OK" in p.stdout
 
 
 @needs2

@@ -35,6 +35,15 @@ def test_allreduce_non_power_of_two(bins, np_):
     assert code == 0, err
 
 
+@pytest.mark.parametrize("np_", [1, 2, 5, 8])
+def test_ranks_as_threads_of_one_process(bins, np_):
+    # The second process model: N host threads, one communicator each.
+    p = subprocess.run(["timeout", "120s", bins["threads_test"], "cpu", str(np_)], stdout=subprocess.PIPE,
+                       stderr=subprocess.PIPE, text=True)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert "threads_test OK" in p.stdout
+
+
 def test_messaging_and_bcast(bins):
     code, err = run(bins, 3, "messaging")
     assert code == 0, err
