@@ -86,6 +86,7 @@ def _declare(lib) -> None:
         "ibcomm_emu_set_timeout_ms": [vp, i],
         "ibcomm_emu_last_channels": [vp],
         "ibcomm_emu_set_silent_rank": [vp, i],
+        "ibcomm_emu_set_bad_program_rank": [vp, i],
         "ibcomm_emu_set_direct_staging": [vp, i],
         "ibcomm_emu_last_status": [vp, C.POINTER(StatusReport)],
         "ibcomm_copy_scale": [vp, vp, sz, i, i, dbl, vp],

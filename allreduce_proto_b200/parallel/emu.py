@@ -53,6 +53,10 @@ class EmuWorld:
         """Test hook: ``rank`` skips the following collectives (-1: nobody does)."""
         check(_native.lib().ibcomm_emu_set_silent_rank(self._h, rank))
 
+    def set_bad_program_rank(self, rank: int) -> None:
+        """Test hook: ``rank`` fails the executor's per-op bounds check (-1: nobody does)."""
+        check(_native.lib().ibcomm_emu_set_bad_program_rank(self._h, rank))
+
     def set_direct_staging(self, mode) -> None:
         """Direct algorithm: 0/False in place, 1/True staged through the pool windows."""
         check(_native.lib().ibcomm_emu_set_direct_staging(self._h, int(mode)))

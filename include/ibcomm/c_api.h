@@ -94,6 +94,9 @@ int ibcomm_emu_last_channels(ibcomm_emu* w);
 /* Test hook: rank `rank` does not take part in the following collectives
  * (-1 = everybody takes part), so its peers' bounded waits run out. */
 int ibcomm_emu_set_silent_rank(ibcomm_emu* w, int rank);
+/* Test hook: rank `rank` fails the executor's per-op bounds check (-1 = nobody);
+ * no memory is touched out of range, the call reports "bad program". */
+int ibcomm_emu_set_bad_program_rank(ibcomm_emu* w, int rank);
 /* Direct algorithm: in place (0, default) or staged through the pool windows (1). */
 int ibcomm_emu_set_direct_staging(ibcomm_emu* w, int on);
 typedef struct {

@@ -40,6 +40,11 @@ class EmuWorld {
   // return at once), so its peers' bounded waits run out and they report a
   // timeout; nothing faults or hangs.  -1 restores normal operation.
   void SetSilentRank(int r);
+  // Test hook for the executor's self-check: rank `r` is told a message length
+  // of one element for programs cut for the real length, so its first op fails
+  // the bounds check before any memory is touched; the rank reports "bad
+  // program", the others are told to stop.  -1 restores normal operation.
+  void SetBadProgramRank(int r);
   // How the direct algorithm treats the buffers: 0 in place, 1 staged through
   // the pool window by window (as for buffers the peers cannot map).
   void SetDirectStaging(int mode);

@@ -73,4 +73,12 @@ std::vector<Range> SplitForDevice(size_t len_elements, size_t elem_bytes, size_t
 
 std::string DescribeOp(const Op& op);
 
+// Bounds check of a program before it is handed to the device: every op's
+// message range inside `len_elements`, its place inside a staging slot, and
+// its slot, region and peer indices inside the program's stage geometry.
+// Returns an empty string, or a description of the first offending op.  The
+// executor kernel repeats the check per op and reports "bad program" instead
+// of touching memory.
+std::string ValidateProgram(const Program& prog, uint64_t len_elements, size_t wire_elem_bytes, int world_size);
+
 }  // namespace ibcomm

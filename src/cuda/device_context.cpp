@@ -2,6 +2,7 @@
 #include "ibcomm/device_context.h"
 
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -65,6 +66,16 @@ struct RegisterMsg {
   uint64_t alloc_id;
   int32_t ok;
   int32_t pid;
+};
+
+// NVTX range around a host call (shows up in timeline tools next to the
+// kernels; costs a few nanoseconds when no tool is attached).
+class NvtxRange {
+ public:
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
 };
 
 struct LoopbackSend {
@@ -329,6 +340,7 @@ void DeviceContext::ExchangeAllocation(SharedAllocation* mine, std::vector<std::
 
 void DeviceContext::ConnectPeers() {
   if (connected_) return;
+  NvtxRange nvtx("ibcomm::ConnectPeers");
   rank_ = comm_->rank();
   if (rank_ < 0) IBCOMM_FAIL(INVALID_ARGUMENT, "Device collectives need RegisterMyself first.\n");
   rr_.rank = rank_;
@@ -456,6 +468,7 @@ void DeviceContext::ExchangeWithAll(const M& mine, std::vector<M>* all) {
 // or a peer in the same process); such buffers keep going through the pool.
 int DeviceContext::RegisterBuffer(void* ptr, size_t bytes) {
   if (ptr == nullptr || bytes == 0) IBCOMM_FAIL(INVALID_ARGUMENT, "RegisterBuffer: empty buffer.\n");
+  NvtxRange nvtx("ibcomm::RegisterBuffer");
   ConnectPeers();
   RegisteredBuffer reg;
   reg.ptr = static_cast<unsigned char*>(ptr);
@@ -690,6 +703,7 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
 }
 
 void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, size_t n, const CudaAllreduceOptions& opts) {
+  NvtxRange nvtx("ibcomm::AllreduceCuda");
   if (sendbuf == nullptr || recvbuf == nullptr) IBCOMM_FAIL(INVALID_ARGUMENT, "AllreduceCuda: null buffer.\n");
   cudaStream_t stream = StreamFor(opts);
   const size_t esize = DTypeSize(dtype);
@@ -764,6 +778,7 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
 
 // ------------------------------------------------------------ point to point
 void DeviceContext::Send(int dest, const void* buf, size_t len) {
+  NvtxRange nvtx("ibcomm::Send(device)");
   P2pState& s = p2p_[static_cast<size_t>(dest)];
   if (s.send_done == nullptr) CUDACHECK(cudaEventCreateWithFlags(&s.send_done, cudaEventDisableTiming));
   if (IsLoopback(dest)) {
@@ -805,6 +820,7 @@ void DeviceContext::Send(int dest, const void* buf, size_t len) {
 }
 
 void DeviceContext::Recv(int src, void* buf, size_t len) {
+  NvtxRange nvtx("ibcomm::Recv(device)");
   P2pState& s = p2p_[static_cast<size_t>(src)];
   if (s.recv_done == nullptr) CUDACHECK(cudaEventCreateWithFlags(&s.recv_done, cudaEventDisableTiming));
   if (IsLoopback(src)) {

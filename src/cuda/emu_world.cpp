@@ -23,6 +23,7 @@ struct EmuWorld::Impl {
   int max_blocks = 0;
   int last_channels = 0;
   int silent_rank = -1;
+  int bad_program_rank = -1;
   int direct_staging = 0;  // 0 in place, 1 staged window by window
   uint32_t last_status = 0;
   DeviceStatus last_report{};
@@ -77,6 +78,7 @@ EmuWorld::~EmuWorld() {
 }
 
 void EmuWorld::SetSilentRank(int r) { impl_->silent_rank = r; }
+void EmuWorld::SetBadProgramRank(int r) { impl_->bad_program_rank = r; }
 void EmuWorld::SetDirectStaging(int mode) { impl_->direct_staging = mode; }
 void EmuWorld::SetTimeoutMs(int ms) { impl_->timeout_ms = ms > 0 ? ms : env::ReadTimeoutMs(); }
 int EmuWorld::last_channels() const { return impl_->last_channels; }
@@ -186,6 +188,7 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
       ps.push_back(MakeExecParams(m.ranks[static_cast<size_t>(r)], cp, dtype, wire, sendbufs[static_cast<size_t>(r)],
                                   recvbufs[static_cast<size_t>(r)], n, scale, timeout_ns, nullptr, 0));
       if (r == m.silent_rank) ps.back().num_ops = 0;
+      if (r == m.bad_program_rank) ps.back().len_elements = 1;
     }
     int ch = channels > 0 ? channels : ChooseChannels(algo, bytes, m.ws, kMaxChannels);
     ch = std::min(ch, cap);
@@ -199,7 +202,8 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
   for (int r = 0; r < m.ws; ++r) {
     DeviceStatus st;
     uint32_t code = m.status[static_cast<size_t>(r)].Consume(&st, stream);
-    if (code != 0 && m.last_status == 0) {
+    // The report of the rank that found the problem beats "aborted by a peer".
+    if (code != 0 && (m.last_status == 0 || (m.last_status == kStatusPeerAbort && code != kStatusPeerAbort))) {
       m.last_status = code;
       m.last_report = st;
     }

@@ -152,12 +152,20 @@ const CachedProgram& ProgramCache::Get(Algo algo, int rank, int world_size, size
   req.apply_scale = apply_scale;
   std::unique_ptr<CachedProgram> cp(new CachedProgram());
   cp->prog = BuildProgram(req);
+  {
+    const std::string bad = ValidateProgram(cp->prog, len_elements, wsize, world_size);
+    if (!bad.empty()) IBCOMM_FAIL(INVALID_ARGUMENT, "Internal error: the %s program for %zu elements on %d ranks is out of bounds (%s).\n",
+                                  ring ? "ring" : "Rabenseifner", len_elements, world_size, bad.c_str());
+  }
   if (!cp->prog.ops.empty()) {
     const size_t bytes = cp->prog.ops.size() * sizeof(Op);
     CUDACHECK(cudaMalloc(&cp->d_ops, bytes));
     CUDACHECK(cudaMemcpy(cp->d_ops, cp->prog.ops.data(), bytes, cudaMemcpyHostToDevice));
   }
-  if (cache_.size() > 256) Clear();
+  // Programs are small (tens of KiB); they are kept, because a captured CUDA
+  // graph holds the device pointer of the program it was recorded with.  The
+  // bound only stops a pathological stream of distinct lengths.
+  if (cache_.size() > 4096) Clear();
   const CachedProgram& ref = *cp;
   cache_[key] = std::move(cp);
   return ref;

@@ -178,6 +178,28 @@ __device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch) {
 }
 
 // Body of the executor for one CTA; returns when the program is done or a wait gave up.
+// Self-check of an op before any of its addresses is formed: the message
+// range, the place inside the staging slot and the slot, region and peer
+// indices.  A failing op is reported (status "bad program") and the call
+// stops; nothing is accessed out of range and nothing traps.
+template <typename W>
+__device__ __forceinline__ bool OpInBounds(const Op& op, const ExecParams& p) {
+  if (op.elem_begin > p.len_elements || op.elem_count > p.len_elements - op.elem_begin) return false;
+  if (op.cell_begin > op.elem_begin) return false;
+  const bool reads_stage = op.src_a == kSrcStage || op.src_b == kSrcStage;
+  const bool writes_stage = (op.flags & kOpStoreRemote) != 0;
+  if (reads_stage || writes_stage) {
+    if ((op.elem_begin - op.cell_begin + op.elem_count) * sizeof(W) > p.stage.slot_bytes) return false;
+  }
+  if (reads_stage && (op.region_in >= p.stage.regions || op.slot_in >= p.stage.slots)) return false;
+  if (writes_stage && (op.region_out >= p.stage.regions || op.slot_out >= p.stage.slots || op.peer_out < 0 ||
+                       op.peer_out >= p.world_size))
+    return false;
+  if ((op.wait_in != 0 || op.post_credit != 0) && (op.peer_in < 0 || op.peer_in >= p.world_size)) return false;
+  if ((op.wait_credit != 0 || op.post_out != 0) && (op.peer_out < 0 || op.peer_out >= p.world_size)) return false;
+  return true;
+}
+
 template <typename T, typename W>
 __device__ void ExecBody(const ExecParams& p, uint64_t seq, int* s_stop) {
   const int ch = blockIdx.x, nch = gridDim.x;
@@ -207,8 +229,12 @@ __device__ void ExecBody(const ExecParams& p, uint64_t seq, int* s_stop) {
   for (int oi = 0; oi < p.num_ops; ++oi) {
     const Op op = p.ops[oi];
     if (threadIdx.x == 0) {
-      bool ok = true;
-      if (op.wait_in != 0) ok = WaitGE(&me->inflag[ch][op.peer_in], base | op.wait_in, w, kWaitData, op.peer_in, oi);
+      bool ok = OpInBounds<W>(op, p);
+      if (!ok) {
+        ReportFailure(w, kStatusBadProgram, 0, -1, oi, op.elem_begin, op.elem_count);
+        BroadcastAbort(w);
+      }
+      if (ok && op.wait_in != 0) ok = WaitGE(&me->inflag[ch][op.peer_in], base | op.wait_in, w, kWaitData, op.peer_in, oi);
       if (ok && op.wait_credit != 0)
         ok = WaitGE(&me->credit[ch][op.peer_out], base | op.wait_credit, w, kWaitCredit, op.peer_out, oi);
       if (!ok) *s_stop = 1;

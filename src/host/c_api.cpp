@@ -344,6 +344,16 @@ int ibcomm_emu_last_channels(ibcomm_emu* w) {
 #endif
 }
 
+int ibcomm_emu_set_bad_program_rank(ibcomm_emu* w, int rank) {
+  return Guard([&] {
+#ifdef USE_CUDA
+    w->world.SetBadProgramRank(rank);
+#else
+    (void)w; (void)rank;
+#endif
+  });
+}
+
 int ibcomm_emu_set_silent_rank(ibcomm_emu* w, int rank) {
   return Guard([&] {
 #ifdef USE_CUDA

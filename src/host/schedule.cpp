@@ -336,6 +336,33 @@ std::vector<Range> SplitForDevice(size_t len_elements, size_t elem_bytes, size_t
   return out;
 }
 
+std::string ValidateProgram(const Program& prog, uint64_t len_elements, size_t wire_elem_bytes, int world_size) {
+  for (size_t i = 0; i < prog.ops.size(); ++i) {
+    const Op& op = prog.ops[i];
+    const char* why = nullptr;
+    const bool reads_stage = op.src_a == kSrcStage || op.src_b == kSrcStage;
+    const bool writes_stage = (op.flags & kOpStoreRemote) != 0;
+    if (op.elem_begin > len_elements || op.elem_count > len_elements - op.elem_begin) {
+      why = "range outside the message";
+    } else if (op.cell_begin > op.elem_begin) {
+      why = "cell starts after the range";
+    } else if ((reads_stage || writes_stage) &&
+               (op.elem_begin - op.cell_begin + op.elem_count) * wire_elem_bytes > prog.stage.slot_bytes) {
+      why = "range does not fit its staging slot";
+    } else if (reads_stage && (op.region_in >= prog.stage.regions || op.slot_in >= prog.stage.slots)) {
+      why = "input slot outside the staging area";
+    } else if (writes_stage && (op.region_out >= prog.stage.regions || op.slot_out >= prog.stage.slots)) {
+      why = "output slot outside the staging area";
+    } else if ((writes_stage || op.wait_credit != 0 || op.post_out != 0) && (op.peer_out < 0 || op.peer_out >= world_size)) {
+      why = "peer_out is not a rank";
+    } else if ((op.wait_in != 0 || op.post_credit != 0) && (op.peer_in < 0 || op.peer_in >= world_size)) {
+      why = "peer_in is not a rank";
+    }
+    if (why != nullptr) return "op " + std::to_string(i) + ": " + why + ": " + DescribeOp(op);
+  }
+  return std::string();
+}
+
 std::string DescribeOp(const Op& op) {
   static const char* const src[] = {"-", "send", "recv", "stage"};
   char buf[256];

@@ -138,4 +138,28 @@ MINI_TEST(RingOwnershipAfterReduceScatter) {
   }
 }
 
+MINI_TEST(ValidateProgramFindsOutOfBoundsOps) {
+  // Every program the builders cut passes; an op pushed out of the message,
+  // out of its slot or out of the staging area is named.
+  for (Algo algo : {Algo::kRing, Algo::kRabenseifner})
+    for (int ws : {2, 3, 5, 8}) {
+      const size_t n = 100003;
+      std::vector<Range> rg = SplitForDevice(n, 4, ws, 0, 0);
+      for (int r = 0; r < ws; ++r) {
+        ProgramRequest q;
+        q.algo = algo; q.rank = r; q.world_size = ws; q.ranges = rg; q.stage_bytes = 1 << 20;
+        Program p = BuildProgram(q);
+        CHECK_TRUE(ValidateProgram(p, n, 4, ws).empty());
+        CHECK_TRUE(!ValidateProgram(p, n / 2, 4, ws).empty());  // the same ops against a shorter message
+        Program bad = p;
+        for (Op& op : bad.ops)
+          if (op.flags & kOpStoreRemote) { op.slot_out = bad.stage.slots; break; }
+        CHECK_TRUE(ValidateProgram(bad, n, 4, ws).find("output slot") != std::string::npos);
+        bad = p;
+        bad.stage.slot_bytes = 64;
+        CHECK_TRUE(ValidateProgram(bad, n, 4, ws).find("does not fit") != std::string::npos);
+      }
+    }
+}
+
 int main(int argc, char** argv) { return mini::RunAll(argc > 1 ? argv[1] : nullptr); }

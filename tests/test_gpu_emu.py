@@ -212,6 +212,28 @@ def test_bounded_wait_reports_timeout():
     check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
 
 
+def test_executor_self_check_reports_bad_program():
+    # A rank whose ops do not fit the message it was given stops at the bounds
+    # check of its first op (before any access), reports "bad program" and
+    # tells the others to stop; the world stays usable.
+    ws = 4
+    w = ar.EmuWorld(ws, 1 << 20, 1 << 20)
+    w.set_timeout_ms(2000)
+    n = 8192
+    ins = make_inputs(ws, n, torch.float32)
+    outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+    w.set_bad_program_rank(1)
+    with pytest.raises(ar.IbcommError) as e:
+        w.allreduce(ins, outs, algo="ring")
+    assert e.value.code == ar.TRANSPORT_ERROR
+    assert "bad program" in str(e.value)
+    st = w.last_status()
+    assert st["code"] == 3 and st["rank"] == 1 and st["op_index"] == 0
+    w.set_bad_program_rank(-1)
+    w.allreduce(ins, outs, algo="rabenseifner")
+    check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+
+
 def test_world_size_one_copy_scale_kernel():
     comm = ar.Communicator(1, 0)
     for n in (1, 5, 4096, (1 << 20) + 7):
