@@ -72,6 +72,8 @@ def _declare(lib) -> None:
         "ibcomm_barrier": [vp],
         "ibcomm_allreduce_host": [vp, i, i, vp, vp, sz],
         "ibcomm_allreduce_cuda": [vp, i, i, vp, vp, sz, dbl, i, vp, i],
+        "ibcomm_reduce_scatter_cuda": [vp, i, i, vp, vp, sz, dbl, vp, i],
+        "ibcomm_all_gather_cuda": [vp, i, i, vp, vp, sz, vp, i],
         "ibcomm_check": [vp],
         "ibcomm_symmetric_alloc": [vp, sz, C.POINTER(vp)],
         "ibcomm_symmetric_free": [vp, vp],
@@ -83,6 +85,7 @@ def _declare(lib) -> None:
         "ibcomm_emu_create": [i, sz, sz, C.POINTER(vp)],
         "ibcomm_emu_destroy": [vp],
         "ibcomm_emu_allreduce": [vp, i, i, C.POINTER(vp), C.POINTER(vp), sz, dbl, i, i, vp, i],
+        "ibcomm_emu_rsag": [vp, i, i, C.POINTER(vp), C.POINTER(vp), sz, dbl, i, vp, i],
         "ibcomm_emu_set_timeout_ms": [vp, i],
         "ibcomm_emu_last_channels": [vp],
         "ibcomm_emu_set_silent_rank": [vp, i],

@@ -46,6 +46,24 @@ class EmuWorld:
                                                  C.c_void_p(s.cuda_stream), 0 if sync else 1))
         return recvbufs
 
+    def reduce_scatter(self, sendbufs: Sequence[torch.Tensor], recvbufs: Sequence[torch.Tensor], *, scale: float = 1.0,
+                       channels: int = 0):
+        """``recvbufs[r]`` = scale * sum over ranks q of block r of ``sendbufs[q]`` (direct algorithm)."""
+        return self._rsag(0, sendbufs, recvbufs, recvbufs[0].numel(), scale, channels)
+
+    def all_gather(self, sendbufs: Sequence[torch.Tensor], recvbufs: Sequence[torch.Tensor], *, channels: int = 0):
+        """Block q of every ``recvbufs[r]`` = ``sendbufs[q]`` (direct algorithm)."""
+        return self._rsag(1, sendbufs, recvbufs, sendbufs[0].numel(), 1.0, channels)
+
+    def _rsag(self, all_gather, sendbufs, recvbufs, block, scale, channels):
+        d = dtype_code(sendbufs[0].dtype)
+        ins = (C.c_void_p * self.num_ranks)(*[_ptr(t) for t in sendbufs])
+        outs = (C.c_void_p * self.num_ranks)(*[_ptr(t) for t in recvbufs])
+        s = torch.cuda.current_stream()
+        check(_native.lib().ibcomm_emu_rsag(self._h, all_gather, d, ins, outs, block, float(scale), channels,
+                                            C.c_void_p(s.cuda_stream), 0))
+        return recvbufs
+
     def set_timeout_ms(self, ms: int) -> None:
         check(_native.lib().ibcomm_emu_set_timeout_ms(self._h, ms))
 

@@ -31,6 +31,16 @@ void Communicator::AllreduceRingCuda(const T* sendbuf, T* recvbuf, size_t len_el
 }
 
 template <typename T>
+void Communicator::ReduceScatterCuda(const T* sendbuf, T* recvbuf, size_t block_elements) {
+  ReduceScatterCuda(DTypeOf<T>::value, sendbuf, recvbuf, block_elements, CudaAllreduceOptions());
+}
+
+template <typename T>
+void Communicator::AllGatherCuda(const T* sendbuf, T* recvbuf, size_t block_elements) {
+  AllGatherCuda(DTypeOf<T>::value, sendbuf, recvbuf, block_elements, CudaAllreduceOptions());
+}
+
+template <typename T>
 void Communicator::AllreduceRabenseifnerCuda(const T* sendbuf, T* recvbuf, size_t len_elements) {
   CudaAllreduceOptions o;
   o.algo = Algo::kRabenseifner;

@@ -53,6 +53,13 @@ int ibcomm_allreduce_host(ibcomm_comm* c, int algo, int dtype, const void* sendb
 #define IBCOMM_USE_STREAM 2
 int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t len_elements,
                           double scale, int wire_dtype, void* stream, int flags);
+/* Halves of the allreduce: block r belongs to rank r.  reduce_scatter: sendbuf
+ * holds world_size blocks, recvbuf one; all_gather: the other way round.
+ * algo: auto, nvls or direct. */
+int ibcomm_reduce_scatter_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
+                               double scale, void* stream, int flags);
+int ibcomm_all_gather_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
+                           void* stream, int flags);
 int ibcomm_check(ibcomm_comm* c);
 
 /* Peer-mapped (and, with NVSwitch multicast, switch-reducible) device memory.
@@ -90,6 +97,8 @@ int ibcomm_emu_destroy(ibcomm_emu* w);
 int ibcomm_emu_allreduce(ibcomm_emu* w, int algo, int dtype, const void* const* sendbufs, void* const* recvbufs,
                          size_t len_elements, double scale, int wire_dtype, int channels, void* stream, int async);
 int ibcomm_emu_set_timeout_ms(ibcomm_emu* w, int ms);
+int ibcomm_emu_rsag(ibcomm_emu* w, int all_gather, int dtype, const void* const* sendbufs, void* const* recvbufs,
+                    size_t block_elements, double scale, int channels, void* stream, int async);
 int ibcomm_emu_last_channels(ibcomm_emu* w);
 /* Test hook: rank `rank` does not take part in the following collectives
  * (-1 = everybody takes part), so its peers' bounded waits run out. */

@@ -124,6 +124,20 @@ class Communicator {
   // caller's stream.  Exposed for the C API and the PyTorch binding.
   void AllreduceCuda(DType dtype, const void* sendbuf, void* recvbuf, size_t len_elements,
                      const CudaAllreduceOptions& opts);
+  // The halves of the allreduce as collectives (no counterpart in the
+  // reference).  Block r of the message belongs to rank r.  ReduceScatterCuda:
+  // sendbuf holds world_size blocks of `block_elements`, recvbuf receives the
+  // sum of block `rank` over the ranks (times opts.scale).  AllGatherCuda:
+  // sendbuf holds one block, recvbuf receives world_size blocks.  opts.algo:
+  // kAuto, kNvls or kDirect; opts.wire is ignored.
+  void ReduceScatterCuda(DType dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
+                         const CudaAllreduceOptions& opts);
+  void AllGatherCuda(DType dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
+                     const CudaAllreduceOptions& opts);
+  template <typename T>
+  void ReduceScatterCuda(const T* sendbuf, T* recvbuf, size_t block_elements);
+  template <typename T>
+  void AllGatherCuda(const T* sendbuf, T* recvbuf, size_t block_elements);
   // Allocates the staging pool and the work region (lazily called by Init).
   void PrepareMemoryPool();
   // Collective: maps this rank's device buffer (cudaMalloc'ed memory, any

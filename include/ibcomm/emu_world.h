@@ -29,6 +29,13 @@ class EmuWorld {
   void Allreduce(Algo algo, DType dtype, const std::vector<const void*>& sendbufs,
                  const std::vector<void*>& recvbufs, size_t len_elements, double scale = 1.0,
                  DType wire = DType::kFloat32, int channels = 0, void* stream = nullptr, bool async = false);
+  // Reduce-scatter (`all_gather` false: sendbufs hold num_ranks blocks,
+  // recvbufs one) or all-gather (the other way round) with the direct
+  // algorithm; the remote side is used in place or, with SetDirectStaging(1),
+  // goes through the pool.
+  void ReduceScatterOrAllGather(bool all_gather, DType dtype, const std::vector<const void*>& sendbufs,
+                                const std::vector<void*>& recvbufs, size_t block_elements, double scale = 1.0,
+                                int channels = 0, void* stream = nullptr, bool async = false);
   // Convenience for the tester: host buffers in, host buffers out.
   void AllreduceHostBuffers(Algo algo, DType dtype, const std::vector<const void*>& in,
                             const std::vector<void*>& out, size_t len_elements);

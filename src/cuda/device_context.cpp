@@ -92,6 +92,9 @@ class DeviceContext {
 
   void ConnectPeers();
   void Allreduce(DType dtype, const void* sendbuf, void* recvbuf, size_t n, const CudaAllreduceOptions& opts);
+  // mode: kRsAgReduceScatter or kRsAgAllGather; `block_elems` per rank.
+  void ReduceScatterOrAllGather(int mode, DType dtype, const void* sendbuf, void* recvbuf, size_t block_elems,
+                                const CudaAllreduceOptions& opts);
   void Check();
   uint32_t Peek(DeviceStatus* out);
 
@@ -776,6 +779,97 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
   Finish(stream, opts.async);
 }
 
+// ------------------------------------------- reduce-scatter and all-gather
+void DeviceContext::ReduceScatterOrAllGather(int mode, DType dtype, const void* sendbuf, void* recvbuf, size_t block_elems,
+                                             const CudaAllreduceOptions& opts) {
+  const bool rs = mode == kRsAgReduceScatter;
+  NvtxRange nvtx(rs ? "ibcomm::ReduceScatterCuda" : "ibcomm::AllGatherCuda");
+  if (sendbuf == nullptr || recvbuf == nullptr) IBCOMM_FAIL(INVALID_ARGUMENT, "%s: null buffer.\n", rs ? "ReduceScatterCuda" : "AllGatherCuda");
+  if (block_elems == 0) IBCOMM_FAIL(NOT_SUPPORTED, "%s: empty block.\n", rs ? "ReduceScatterCuda" : "AllGatherCuda");
+  cudaStream_t stream = StreamFor(opts);
+  const size_t esize = DTypeSize(dtype);
+  const size_t block_bytes = block_elems * esize;
+  if (ws_ == 1) {
+    OrderAfterPrevious(stream);
+    RunCopy(dtype, sendbuf, recvbuf, block_elems, rs ? opts.scale : 1.0, stream);
+    MarkIssued(stream);
+    last_algo_ = 0;
+    last_channels_ = 0;
+    Finish(stream, opts.async);
+    return;
+  }
+  ConnectPeers();
+  Algo algo = opts.algo;
+  if (algo == Algo::kAuto) algo = AlgoFromName(env::ReadAlgo());
+  if (algo != Algo::kAuto && algo != Algo::kNvls && algo != Algo::kDirect)
+    IBCOMM_FAIL(NOT_SUPPORTED, "Reduce-scatter and all-gather run the nvls or the direct algorithm.\n");
+
+  RsAgParams p;
+  memset(&p, 0, sizeof(p));
+  p.rank = rank_;
+  p.world_size = ws_;
+  p.dtype = static_cast<int32_t>(dtype);
+  p.mode = mode;
+  p.peers = rr_.peers;
+  p.sendbuf = sendbuf;
+  p.recvbuf = recvbuf;
+  p.block_elems = block_elems;
+  p.scale = rs ? opts.scale : 1.0;
+  p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
+  p.status = rr_.d_status;
+  p.doorbell = rr_.d_doorbell;
+
+  // The remote side: the input of a reduce-scatter, the output of an all-gather.
+  const void* remote = rs ? sendbuf : recvbuf;
+  const size_t remote_bytes = block_bytes * static_cast<size_t>(ws_);
+  const bool vec = block_bytes % 16 == 0;
+  unsigned char* mapped[kMaxRanks];
+  bool zero_copy = vec && FindPeerMapped(remote, remote_bytes, mapped);
+  for (int q = 0; q < ws_ && zero_copy; ++q)
+    if ((reinterpret_cast<uintptr_t>(mapped[q]) & 15u) != 0) zero_copy = false;  // the same verdict on every rank
+  const SymmetricAlloc* sym = FindSymmetric(remote, remote_bytes);
+  const bool nvls_possible = mc_ != nullptr && NvlsSupportsDType(dtype) && vec && (!zero_copy || (sym != nullptr && sym->mc));
+  if (algo == Algo::kNvls && !nvls_possible)
+    IBCOMM_FAIL(NOT_SUPPORTED, "The NVLS algorithm needs NVSwitch multicast, a float32/float16/bfloat16 buffer and blocks of whole 16-byte vectors.\n");
+  // The switch wins from 3 ranks on (1 + 1/ws of the block per direction
+  // against (ws-1)/ws per direction and phase); 2 ranks go direct.
+  if (algo == Algo::kAuto) algo = (nvls_possible && ws_ > 2) ? Algo::kNvls : Algo::kDirect;
+  p.use_multimem = algo == Algo::kNvls ? 1 : 0;
+
+  if (zero_copy) {
+    p.staged = 0;
+    for (int q = 0; q < ws_; ++q) p.peer_buf[q] = mapped[q];
+    if (p.use_multimem) p.mc_buf = sym->mc->ptr() + (static_cast<const unsigned char*>(remote) - sym->mine->ptr());
+    p.window_elems = block_elems;
+    p.sub_stride_bytes = block_bytes;
+  } else {
+    // The whole pool is one window of ws sub-blocks.
+    const uint64_t sub = layout_.pool_bytes / static_cast<uint64_t>(ws_) / 4096 * 4096;
+    if (sub < 4096) IBCOMM_FAIL(NOT_SUPPORTED, "Reduce-scatter / all-gather of ordinary buffers need a pool of at least %d KiB.\n", 4 * ws_);
+    p.staged = 1;
+    for (int q = 0; q < ws_; ++q) p.peer_buf[q] = rr_.peers.arena[q] + layout_.pool_offset;
+    if (p.use_multimem) p.mc_buf = mc_->ptr() + layout_.pool_offset;
+    p.sub_stride_bytes = sub;
+    p.window_elems = std::min<uint64_t>(block_elems, sub / esize);
+  }
+  int channels = ChooseChannels(p.use_multimem && zero_copy ? Algo::kNvls : Algo::kDirect, remote_bytes, ws_, max_channels_);
+  if (p.staged) {
+    // Equal windows, each a whole number of units per channel.
+    const uint64_t cap = p.sub_stride_bytes / esize;
+    p.window_elems = TwoShotWindowElems(block_elems, cap, esize, 1, channels);
+    if (!vec) p.window_elems = std::min<uint64_t>(std::max<uint64_t>(p.window_elems, 1), cap);
+  }
+  OrderAfterPrevious(stream);
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+  CUDACHECK(LaunchRsAgKernel(p, nullptr, 1, channels, stream));
+  ++kernel_launches_;
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+  MarkIssued(stream);
+  last_algo_ = static_cast<int>(algo);
+  last_channels_ = channels;
+  Finish(stream, opts.async);
+}
+
 // ------------------------------------------------------------ point to point
 void DeviceContext::Send(int dest, const void* buf, size_t len) {
   NvtxRange nvtx("ibcomm::Send(device)");
@@ -1032,6 +1126,24 @@ void Communicator::AllreduceCuda(DType dtype, const void* sendbuf, void* recvbuf
   CollectiveLease lease(this);
   PrepareMemoryPool();
   device_->Allreduce(dtype, sendbuf, recvbuf, len_elements, opts);
+}
+
+void Communicator::ReduceScatterCuda(DType dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
+                                     const CudaAllreduceOptions& opts) {
+  if (!initialized_) IBCOMM_FAIL(INVALID_ARGUMENT, "ReduceScatterCuda: communicator is not initialized.\n");
+  if (world_size_ > 1 && my_rank_ < 0) IBCOMM_FAIL(INVALID_ARGUMENT, "ReduceScatterCuda: call RegisterMyself first.\n");
+  CollectiveLease lease(this);
+  PrepareMemoryPool();
+  device_->ReduceScatterOrAllGather(kRsAgReduceScatter, dtype, sendbuf, recvbuf, block_elements, opts);
+}
+
+void Communicator::AllGatherCuda(DType dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
+                                 const CudaAllreduceOptions& opts) {
+  if (!initialized_) IBCOMM_FAIL(INVALID_ARGUMENT, "AllGatherCuda: communicator is not initialized.\n");
+  if (world_size_ > 1 && my_rank_ < 0) IBCOMM_FAIL(INVALID_ARGUMENT, "AllGatherCuda: call RegisterMyself first.\n");
+  CollectiveLease lease(this);
+  PrepareMemoryPool();
+  device_->ReduceScatterOrAllGather(kRsAgAllGather, dtype, sendbuf, recvbuf, block_elements, opts);
 }
 
 }  // namespace ibcomm

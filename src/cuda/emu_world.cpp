@@ -211,6 +211,87 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
   if (m.last_status != 0) IBCOMM_FAIL(TRANSPORT_ERROR, "%s\n", DescribeStatus(m.last_report).c_str());
 }
 
+void EmuWorld::ReduceScatterOrAllGather(bool all_gather, DType dtype, const std::vector<const void*>& sendbufs,
+                                        const std::vector<void*>& recvbufs, size_t block_elems, double scale, int channels,
+                                        void* stream_v, bool async) {
+  Impl& m = *impl_;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (static_cast<int>(sendbufs.size()) != m.ws || static_cast<int>(recvbufs.size()) != m.ws)
+    IBCOMM_FAIL(INVALID_ARGUMENT, "EmuWorld::ReduceScatterOrAllGather needs one buffer pair per rank.\n");
+  if (block_elems == 0) IBCOMM_FAIL(NOT_SUPPORTED, "EmuWorld::ReduceScatterOrAllGather: empty block.\n");
+  const size_t esize = DTypeSize(dtype);
+  const size_t block_bytes = block_elems * esize;
+  m.last_status = 0;
+  if (m.ws == 1) {
+    CopyParams cp{sendbufs[0], recvbufs[0], block_elems, static_cast<int32_t>(dtype), static_cast<int32_t>(dtype), all_gather ? 1.0 : scale};
+    CUDACHECK(LaunchCopyKernel(cp, kCopyDefaultBlocks, stream));
+    if (!async) CUDACHECK(cudaStreamSynchronize(stream));
+    return;
+  }
+  const bool vec = block_bytes % 16 == 0;
+  bool aligned = vec;
+  for (int q = 0; q < m.ws; ++q) {
+    const void* remote = all_gather ? recvbufs[static_cast<size_t>(q)] : sendbufs[static_cast<size_t>(q)];
+    aligned = aligned && (reinterpret_cast<uintptr_t>(remote) & 15u) == 0;
+  }
+  const bool staged = m.direct_staging != 0 || !aligned;
+  const uint64_t sub = m.layout.pool_bytes / static_cast<uint64_t>(m.ws) / 4096 * 4096;
+  if (staged && sub < 4096) IBCOMM_FAIL(NOT_SUPPORTED, "Reduce-scatter / all-gather through the pool need a larger pool.\n");
+  const int cap = std::max(1, m.max_blocks / m.ws);
+  int ch = channels > 0 ? channels : ChooseChannels(Algo::kDirect, block_bytes * static_cast<size_t>(m.ws), m.ws, kMaxChannels);
+  ch = std::min(ch, cap);
+  std::vector<RsAgParams> ps(static_cast<size_t>(m.ws));
+  for (int r = 0; r < m.ws; ++r) {
+    RsAgParams& p = ps[static_cast<size_t>(r)];
+    memset(&p, 0, sizeof(p));
+    const RankResources& rr = m.ranks[static_cast<size_t>(r)];
+    p.rank = r;
+    p.world_size = m.ws;
+    p.dtype = static_cast<int32_t>(dtype);
+    p.mode = all_gather ? kRsAgAllGather : kRsAgReduceScatter;
+    p.staged = staged ? 1 : 0;
+    p.peers = rr.peers;
+    p.sendbuf = sendbufs[static_cast<size_t>(r)];
+    p.recvbuf = recvbufs[static_cast<size_t>(r)];
+    p.block_elems = block_elems;
+    p.scale = all_gather ? 1.0 : scale;
+    p.timeout_ns = static_cast<uint64_t>(m.timeout_ms) * 1000000ull;
+    p.status = rr.d_status;
+    p.doorbell = rr.d_doorbell;
+    for (int q = 0; q < m.ws; ++q) {
+      if (staged) {
+        p.peer_buf[q] = rr.peers.arena[q] + m.layout.pool_offset;
+      } else {
+        p.peer_buf[q] = all_gather ? static_cast<unsigned char*>(recvbufs[static_cast<size_t>(q)])
+                                   : static_cast<unsigned char*>(const_cast<void*>(sendbufs[static_cast<size_t>(q)]));
+      }
+    }
+    if (staged) {
+      p.sub_stride_bytes = sub;
+      p.window_elems = TwoShotWindowElems(block_elems, sub / esize, esize, 1, ch);
+      if (!vec) p.window_elems = std::min<uint64_t>(std::max<uint64_t>(p.window_elems, 1), sub / esize);
+    } else {
+      p.sub_stride_bytes = block_bytes;
+      p.window_elems = block_elems;
+    }
+  }
+  void* d = m.Params(ps.size() * sizeof(RsAgParams));
+  CUDACHECK(cudaMemcpyAsync(d, ps.data(), ps.size() * sizeof(RsAgParams), cudaMemcpyHostToDevice, stream));
+  CUDACHECK(LaunchRsAgKernel(ps[0], static_cast<const RsAgParams*>(d), m.ws, ch, stream));
+  m.last_channels = ch;
+  if (async) return;
+  CUDACHECK(cudaStreamSynchronize(stream));
+  for (int r = 0; r < m.ws; ++r) {
+    DeviceStatus st;
+    uint32_t code = m.status[static_cast<size_t>(r)].Consume(&st, stream);
+    if (code != 0 && (m.last_status == 0 || (m.last_status == kStatusPeerAbort && code != kStatusPeerAbort))) {
+      m.last_status = code;
+      m.last_report = st;
+    }
+  }
+  if (m.last_status != 0) IBCOMM_FAIL(TRANSPORT_ERROR, "%s\n", DescribeStatus(m.last_report).c_str());
+}
+
 void EmuWorld::AllreduceHostBuffers(Algo algo, DType dtype, const std::vector<const void*>& in, const std::vector<void*>& out,
                                     size_t n) {
   const size_t bytes = n * DTypeSize(dtype);

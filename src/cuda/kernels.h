@@ -67,6 +67,35 @@ struct NvlsParams {
 };
 cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
 
+// ---- reduce-scatter / all-gather (the halves of the two-shot allreduce) ----
+enum RsAgMode : int32_t { kRsAgReduceScatter = 1, kRsAgAllGather = 2 };
+struct RsAgParams {
+  int32_t rank;
+  int32_t world_size;
+  int32_t dtype;
+  int32_t use_multimem;  // 1: multimem.ld_reduce / multimem.st; 0: peer loads / peer stores
+  int32_t mode;          // RsAgMode
+  int32_t staged;        // the remote side is the pool (window by window), not a mapped user buffer
+  PeerTable peers;
+  const void* sendbuf;   // reduce-scatter: ws blocks; all-gather: one block
+  void* recvbuf;         // reduce-scatter: one block; all-gather: ws blocks
+  uint64_t block_elems;  // elements per block (per rank)
+  double scale;          // reduce-scatter only
+  // The remote side as every rank sees it (reduce-scatter: the inputs,
+  // all-gather: the outputs): user buffers or pool windows, and their
+  // multicast alias (null without multimem).
+  unsigned char* peer_buf[kMaxRanks];
+  unsigned char* mc_buf;
+  // Block elements per window (the whole block when not staged) and the
+  // distance in bytes between two sub-blocks of the remote side.
+  uint64_t window_elems;
+  uint64_t sub_stride_bytes;
+  uint64_t timeout_ns;
+  DeviceStatus* status;
+  uint32_t* doorbell;
+};
+cudaError_t LaunchRsAgKernel(const RsAgParams& p, const RsAgParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
+
 // ---- one-shot allreduce for small messages (push to every peer, sum locally) ----
 struct OneShotParams {
   int32_t rank;

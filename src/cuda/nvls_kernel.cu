@@ -82,7 +82,7 @@ __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
         for (uint64_t i = tail0 + threadIdx.x; i < wn; i += blockDim.x) dt[i - tail0] = sendbuf[w0 + i];
       }
     }
-    if (!CrossRankBarrier(p, w, cta, ++phase, &s_stop)) return;
+    if (!CrossRankBarrier(p.peers, w, cta, ++phase, &s_stop)) return;
 
     // (2) reduce my shard in the switch and broadcast it.
     {
@@ -153,7 +153,7 @@ __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
       }
       if (do_scale) tail_acc = ScaleAcc<A>(tail_acc, p.scale);
     }
-    if (!CrossRankBarrier(p, w, cta, ++phase, &s_stop)) return;
+    if (!CrossRankBarrier(p.peers, w, cta, ++phase, &s_stop)) return;
     if (has_tail) {
       const uint64_t i = tail0 + threadIdx.x;
       if (p.stage_out) recvbuf[w0 + i] = FromAcc<T, A>(tail_acc);

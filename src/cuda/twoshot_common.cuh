@@ -105,14 +105,14 @@ __device__ __forceinline__ void WindowPart(uint64_t full_nvec, uint64_t nvec, in
 }
 
 // Barrier between CTA `cta` of every rank.  Returns false when it gave up.
-__device__ inline bool CrossRankBarrier(const NvlsParams& p, const WaitCtx& w, int cta, uint32_t phase, int* s_stop) {
+__device__ inline bool CrossRankBarrier(const PeerTable& peers, const WaitCtx& w, int cta, uint32_t phase, int* s_stop) {
   __syncthreads();
   const uint64_t val = (w.seq << 32) | phase;
-  if (threadIdx.x < p.world_size && static_cast<int>(threadIdx.x) != p.rank) {
+  if (threadIdx.x < w.world_size && static_cast<int>(threadIdx.x) != w.rank) {
     // The release store orders everything this CTA wrote before the barrier
     // (observed by this thread through __syncthreads) ahead of the flag.
-    StReleaseSys(&Ctl(p.peers, threadIdx.x)->bar[cta][p.rank], val);
-    if (!WaitGE(&Ctl(p.peers, p.rank)->bar[cta][threadIdx.x], val, w, kWaitBarrier, threadIdx.x, static_cast<int>(phase)))
+    StReleaseSys(&Ctl(peers, threadIdx.x)->bar[cta][w.rank], val);
+    if (!WaitGE(&Ctl(peers, w.rank)->bar[cta][threadIdx.x], val, w, kWaitBarrier, threadIdx.x, static_cast<int>(phase)))
       *s_stop = 1;
   }
   __syncthreads();

@@ -205,6 +205,41 @@ int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendb
   });
 }
 
+int ibcomm_reduce_scatter_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
+                               double scale, void* stream, int flags) {
+  return Guard([&] {
+    NeedCuda();
+#ifdef USE_CUDA
+    ibcomm::CudaAllreduceOptions o;
+    o.algo = CheckAlgo(algo);
+    o.scale = scale;
+    o.stream = stream;
+    o.use_stream = (flags & IBCOMM_USE_STREAM) != 0;
+    o.async = (flags & IBCOMM_ASYNC) != 0;
+    c->comm.ReduceScatterCuda(CheckDType(dtype), sendbuf, recvbuf, block_elements, o);
+#else
+    (void)c; (void)algo; (void)dtype; (void)sendbuf; (void)recvbuf; (void)block_elements; (void)scale; (void)stream; (void)flags;
+#endif
+  });
+}
+
+int ibcomm_all_gather_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
+                           void* stream, int flags) {
+  return Guard([&] {
+    NeedCuda();
+#ifdef USE_CUDA
+    ibcomm::CudaAllreduceOptions o;
+    o.algo = CheckAlgo(algo);
+    o.stream = stream;
+    o.use_stream = (flags & IBCOMM_USE_STREAM) != 0;
+    o.async = (flags & IBCOMM_ASYNC) != 0;
+    c->comm.AllGatherCuda(CheckDType(dtype), sendbuf, recvbuf, block_elements, o);
+#else
+    (void)c; (void)algo; (void)dtype; (void)sendbuf; (void)recvbuf; (void)block_elements; (void)stream; (void)flags;
+#endif
+  });
+}
+
 int ibcomm_check(ibcomm_comm* c) {
   return Guard([&] {
 #ifdef USE_CUDA
@@ -321,6 +356,21 @@ int ibcomm_emu_allreduce(ibcomm_emu* w, int algo, int dtype, const void* const* 
     w->world.Allreduce(CheckAlgo(algo), CheckDType(dtype), in, out, n, scale, CheckDType(wire_dtype), channels, stream, async != 0);
 #else
     (void)w; (void)algo; (void)dtype; (void)sendbufs; (void)recvbufs; (void)n; (void)scale; (void)wire_dtype; (void)channels; (void)stream; (void)async;
+#endif
+  });
+}
+
+int ibcomm_emu_rsag(ibcomm_emu* w, int all_gather, int dtype, const void* const* sendbufs, void* const* recvbufs,
+                    size_t block_elements, double scale, int channels, void* stream, int async) {
+  return Guard([&] {
+    NeedCuda();
+#ifdef USE_CUDA
+    const int ws = w->world.num_ranks();
+    std::vector<const void*> in(sendbufs, sendbufs + ws);
+    std::vector<void*> out(recvbufs, recvbufs + ws);
+    w->world.ReduceScatterOrAllGather(all_gather != 0, CheckDType(dtype), in, out, block_elements, scale, channels, stream, async != 0);
+#else
+    (void)w; (void)all_gather; (void)dtype; (void)sendbufs; (void)recvbufs; (void)block_elements; (void)scale; (void)channels; (void)stream; (void)async;
 #endif
   });
 }

@@ -159,6 +159,60 @@ def case_registered(comm):
     return rc
 
 
+def case_rsag(comm):
+    """Reduce-scatter and all-gather: ordinary, registered and symmetric buffers; every algorithm the box has."""
+    rc = 0
+    info = comm.device_info(connect=True)
+    algos = ["auto", "direct"] + (["nvls"] if info["nvls"] else [])
+    for m in (4, 1000, (1 << 20) + 8, 3_000_001):
+        x = seeded(m * WS, torch.float32, RANK, seed=m)
+        want = expected(m * WS, torch.float32, 0.5, seed=m)
+        for algo in algos:
+            if algo == "nvls" and (m * 4) % 16 != 0:
+                continue
+            y = torch.zeros(m, device="cuda")
+            comm.reduce_scatter(x, y, algo=algo, scale=0.5, sync=True)
+            if not close(y, want[RANK * m:(RANK + 1) * m], torch.float32):
+                print(f"rank {RANK}: reduce_scatter {algo} m={m} mismatch", file=sys.stderr)
+                rc = 1
+            z = torch.zeros(m * WS, device="cuda")
+            comm.all_gather(y, z, algo=algo, sync=True)
+            if not close(z, want, torch.float32):
+                print(f"rank {RANK}: all_gather {algo} m={m} mismatch", file=sys.stderr)
+                rc = 1
+    # Zero-copy: symmetric memory (switch path where available) and registered tensors (direct).
+    m = (1 << 20) + 16
+    sx = comm.symmetric_empty(m * WS, torch.float32)
+    sz = comm.symmetric_empty(m * WS, torch.float32)
+    rx = torch.empty(m * WS, device="cuda")
+    rz = torch.empty(m * WS, device="cuda")
+    ids = [comm.register(rx), comm.register(rz)]
+    for name, bx, bz in (("symmetric", sx, sz), ("registered", rx, rz)):
+        for it in range(2):
+            bx.copy_(seeded(m * WS, torch.float32, RANK, seed=it + 50))
+            want = expected(m * WS, torch.float32, 1.0, seed=it + 50)
+            y = torch.zeros(m, device="cuda")
+            comm.reduce_scatter(bx, y, sync=True)
+            if not close(y, want[RANK * m:(RANK + 1) * m], torch.float32):
+                print(f"rank {RANK}: {name} reduce_scatter mismatch ({comm.device_info()['last_algo']})", file=sys.stderr)
+                rc = 1
+            comm.all_gather(y, bz, sync=True)
+            if not close(bz, want, torch.float32):
+                print(f"rank {RANK}: {name} all_gather mismatch ({comm.device_info()['last_algo']})", file=sys.stderr)
+                rc = 1
+            # in place: my block of the input is the output, then gathered in place
+            mine = bx[RANK * m:(RANK + 1) * m]
+            comm.reduce_scatter(bx, mine, sync=True)
+            comm.all_gather(mine, bx, sync=True)
+            if not close(bx, want, torch.float32):
+                print(f"rank {RANK}: {name} in-place reduce_scatter + all_gather mismatch", file=sys.stderr)
+                rc = 1
+    for rid in ids:
+        if rid >= 0:
+            comm.deregister(rid)
+    return rc
+
+
 def case_sendrecv(comm):
     """Device buffers through the mailbox kernels; ring of neighbours plus a broadcast."""
     comm.device_info(connect=True)

@@ -212,6 +212,44 @@ def test_bounded_wait_reports_timeout():
     check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
 
 
+@pytest.mark.parametrize("ws", [2, 3, 5, 8])
+def test_reduce_scatter_and_all_gather(ws):
+    # The halves of the two-shot allreduce as collectives: in place on the
+    # ranks' buffers and through pool windows (1 MiB pool, so the larger
+    # blocks take several windows, the last one short); blocks of whole
+    # 16-byte vectors and ragged ones (element units); every element type.
+    w = world(ws, 1 << 20, 1 << 20)
+    for staged in (0, 1):
+        w.set_direct_staging(staged)
+        for m in (1, 37, 4096, 100000 // ws * 4, 70001):
+            for dtype in (torch.float32, torch.bfloat16, torch.int32, torch.float64):
+                ins = make_inputs(ws, m * ws, dtype, seed=m + ws)
+                scale = 0.5 if dtype not in (torch.int32,) else 1.0
+                want = reference(ins, scale, dtype)
+                outs = [torch.zeros(m, device="cuda", dtype=dtype) for _ in range(ws)]
+                w.reduce_scatter(ins, outs, scale=scale)
+                for r in range(ws):
+                    check([outs[r]], want[r * m:(r + 1) * m], dtype, ws)
+                gathered = [torch.zeros(m * ws, device="cuda", dtype=dtype) for _ in range(ws)]
+                w.all_gather(outs, gathered)
+                whole = torch.cat(outs)
+                for r in range(ws):
+                    assert torch.equal(gathered[r], whole), f"all-gather rank {r} m={m} {dtype}"
+        # element-aligned user buffers (odd offset) in vector-sized blocks
+        m = 4096
+        ins = [t[1:] for t in make_inputs(ws, m * ws + 1, torch.float32, seed=5)]
+        outs = [torch.zeros(m + 1, device="cuda")[1:] for _ in range(ws)]
+        w.reduce_scatter(ins, outs)
+        want = reference(ins, 1.0, torch.float32)
+        for r in range(ws):
+            check([outs[r]], want[r * m:(r + 1) * m], torch.float32, ws)
+        gathered = [torch.zeros(m * ws + 1, device="cuda")[1:] for _ in range(ws)]
+        w.all_gather(outs, gathered)
+        for r in range(ws):
+            assert torch.equal(gathered[r], torch.cat(outs))
+    w.set_direct_staging(0)
+
+
 def test_executor_self_check_reports_bad_program():
     # A rank whose ops do not fit the message it was given stops at the bounds
     # check of its first op (before any access), reports "bad program" and

@@ -54,6 +54,13 @@ def test_ranks_as_threads_of_one_process(bins):
 
 
 @needs2
+@pytest.mark.parametrize("np_", [n for n in (2, 3, 8) if n <= NGPU])
+def test_reduce_scatter_and_all_gather(bins, np_):
+    code, err = run(bins, np_, "rsag")
+    assert code == 0, err
+
+
+@needs2
 def test_registered_user_buffers(bins):
     code, err = run(bins, min(NGPU, 4), "registered")
     assert code == 0, err
