@@ -59,6 +59,8 @@ def parse_args():
     ap.add_argument("--out", default=None)
     ap.add_argument("--write-tuning", default=None, metavar="PATH",
                     help="with --sweep: write the fastest algorithm per size as an IBCOMM_TUNING_FILE table")
+    ap.add_argument("--rsag", action="store_true",
+                    help="time reduce-scatter and all-gather (fp32, 1 MiB .. 1 GiB per rank in total) against NCCL")
     ap.add_argument("--no-extras", action="store_true", help="skip per-algorithm and NCCL measurements")
     ap.add_argument("--kernel-case", default=None,
                     choices=["copy", "exec_ring_emu8", "exec_rabenseifner_emu8", "oneshot_emu8"],
@@ -180,6 +182,8 @@ def main() -> int:
 
     if args.sweep:
         return sweep(args, comm, world, rank, dev, time_steps, barrier)
+    if args.rsag:
+        return rsag_sweep(args, comm, world, rank, dev, time_steps)
     if args.kernel_case:
         return kernel_case(args, comm, dev, time_steps)
 
@@ -336,6 +340,75 @@ def kernel_case(args, comm, dev, time_steps) -> int:
         moved = None
     print(json.dumps({"kernel_case": case, "ms": ms, "steps": args.steps,
                       "gbs_read_plus_write": (moved / (ms / 1e3) / 1e9) if moved else None}))
+    return 0
+
+
+def rsag_sweep(args, comm, world, rank, dev, time_steps) -> int:
+    """Reduce-scatter and all-gather, fp32: symmetric, registered and ordinary tensors, and NCCL's
+    reduce_scatter_tensor / all_gather_into_tensor on the same box.  `bytes` is the size of the full
+    (world_size blocks) buffer; bus bandwidth = bytes / time x (N-1)/N."""
+    import torch
+    import torch.distributed as dist
+
+    if world < 2:
+        if rank == 0:
+            print(json.dumps({"rsag": None, "reason": "needs at least two GPUs"}))
+        return 0
+    out_path = args.out or f"gpurun_out/rsag_{world}gpu.jsonl"
+    max_bytes = min(args.sweep_max_bytes, 1 << 30)
+    nmax = max_bytes // 4
+    full = {"symmetric": comm.symmetric_empty(nmax, torch.float32), "plain": torch.empty(nmax, device=dev),
+            "registered": torch.empty(nmax, device=dev)}
+    rid = comm.register(full["registered"])
+    if rid < 0:
+        del full["registered"]
+    g = torch.Generator(device=dev)
+    g.manual_seed(rank)
+    full["plain"].copy_(torch.rand(nmax, device=dev, generator=g) * 2 - 1)
+    for k in full:
+        if k != "plain":
+            full[k].copy_(full["plain"])
+    shard = torch.empty(nmax // world, device=dev)
+    nccl_full = full["plain"].clone()
+    burn = torch.randn(4096, 4096, device=dev, dtype=torch.bfloat16)
+    t_end = time.time() + 1.0
+    while time.time() < t_end:
+        for _ in range(20):
+            burn @ burn
+        torch.cuda.synchronize()
+    del burn
+    rows = []
+    size = 1 << 20
+    while size <= max_bytes:
+        m = size // 4 // world
+        n = m * world
+        steps, warm = (100, 10) if size <= (16 << 20) else (20, 5)
+        factor = (world - 1) / world
+        for kind, buf in full.items():
+            t = time_steps(lambda: comm.reduce_scatter(buf[:n], shard[:m], scale=1.0 / world), steps, warm)
+            comm.check()
+            rows.append({"bytes": n * 4, "op": "reduce_scatter", "buffers": kind, "us": t * 1e3,
+                         "busbw_gbs": n * 4 * factor / (t / 1e3) / 1e9, "algo": comm.device_info()["last_algo"]})
+            t = time_steps(lambda: comm.all_gather(shard[:m], buf[:n]), steps, warm)
+            comm.check()
+            rows.append({"bytes": n * 4, "op": "all_gather", "buffers": kind, "us": t * 1e3,
+                         "busbw_gbs": n * 4 * factor / (t / 1e3) / 1e9, "algo": comm.device_info()["last_algo"]})
+        t = time_steps(lambda: dist.reduce_scatter_tensor(shard[:m], nccl_full[:n]), steps, warm)
+        rows.append({"bytes": n * 4, "op": "reduce_scatter", "buffers": "nccl", "us": t * 1e3,
+                     "busbw_gbs": n * 4 * factor / (t / 1e3) / 1e9})
+        t = time_steps(lambda: dist.all_gather_into_tensor(nccl_full[:n], shard[:m]), steps, warm)
+        rows.append({"bytes": n * 4, "op": "all_gather", "buffers": "nccl", "us": t * 1e3,
+                     "busbw_gbs": n * 4 * factor / (t / 1e3) / 1e9})
+        size *= 4
+    if rank == 0:
+        os.makedirs(os.path.dirname(out_path) or ".", exist_ok=True)
+        with open(out_path, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+        print(json.dumps({"rsag": out_path, "rows": len(rows), "n_gpus": world}))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
     return 0
 
 

@@ -33,7 +33,7 @@ namespace ibcomm {
 namespace dev {
 
 // Body of the two-shot kernel for one CTA; returns early when a barrier gave up.
-template <typename T, int U, bool kMultimem>
+template <typename T, int U, bool kMultimem, int kR>
 __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
   using A = typename Acc<T>::type;
   constexpr int kVecElems = 16 / static_cast<int>(sizeof(T));
@@ -114,29 +114,16 @@ __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
           }
         }
       } else {
-        // Direct variant: one 16-byte load per peer, all issued before the
-        // adds; the sum runs in rank order, so whoever reduces a shard, the
-        // bits are the same.
+        // Direct variant: 16-byte loads from every peer, several in flight per
+        // thread; the sum runs in rank order, so whoever reduces a shard, the
+        // bits are the same.  The result goes to every rank's output window.
         const int ws = p.world_size;
-        for (uint64_t i = b + threadIdx.x; i < e; i += blockDim.x) {
-          uint4 v[kMaxRanks];
+        unsigned char* const* outs = p.peer_out;
+        PeerReduce<T, kR>(p.peer_in, ws, win_bytes_off, b, e, do_scale, p.scale, [&](uint64_t idx, uint4 r) {
 #pragma unroll
           for (int q = 0; q < kMaxRanks; ++q)
-            if (q < ws) v[q] = Ld16Strong(p.peer_in[q] + win_bytes_off + i * 16);
-          A acc[kVecElems];
-          VecIO<T>::Load(v[0], acc);
-#pragma unroll
-          for (int q = 1; q < kMaxRanks; ++q)
-            if (q < ws) VecIO<T>::Add(v[q], acc);
-          if (do_scale) {
-#pragma unroll
-            for (int k = 0; k < kVecElems; ++k) acc[k] = ScaleAcc<A>(acc[k], p.scale);
-          }
-          const uint4 r = VecIO<T>::Store(acc);
-#pragma unroll
-          for (int q = 0; q < kMaxRanks; ++q)
-            if (q < ws) St16(p.peer_out[q] + wout_bytes_off + i * 16, r);
-        }
+            if (q < ws) St16(outs[q] + wout_bytes_off + idx * 16, r);
+        });
       }
     }
     // Ragged end (< 16 bytes): every rank sums it itself from the peers'
@@ -179,7 +166,7 @@ __device__ void TwoShotBody(const NvlsParams& p, uint64_t seq, int& s_stop) {
   }
 }
 
-template <typename T, int U, bool kMultimem>
+template <typename T, int U, bool kMultimem, int kR>
 __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_constant__ NvlsParams p0, const NvlsParams* __restrict__ emu) {
   __shared__ NvlsParams p;
   __shared__ int s_stop;
@@ -191,7 +178,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
   }
   __syncthreads();
   const uint64_t seq = BeginCollective(p.peers, p.rank, &s_seq);
-  TwoShotBody<T, U, kMultimem>(p, seq, s_stop);
+  TwoShotBody<T, U, kMultimem, kR>(p, seq, s_stop);
   EndCollective(p.peers, p.rank, seq, gridDim.x);
 }
 
@@ -202,14 +189,14 @@ static int EnvInt(const char* name, int dflt) {
   return s ? atoi(s) : dflt;
 }
 
-template <typename T, int U, bool kMultimem>
+template <typename T, int U, bool kMultimem, int kR>
 static cudaError_t LaunchNvlsU(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, int threads, cudaStream_t stream) {
   dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(emu != nullptr ? emu_ranks : 1));
   if (emu != nullptr) {
     void* args[] = {const_cast<NvlsParams*>(&p), &emu};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::NvlsKernel<T, U, kMultimem>), grid, dim3(threads), args, 0, stream);
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::NvlsKernel<T, U, kMultimem, kR>), grid, dim3(threads), args, 0, stream);
   }
-  dev::NvlsKernel<T, U, kMultimem><<<grid, threads, 0, stream>>>(p, nullptr);
+  dev::NvlsKernel<T, U, kMultimem, kR><<<grid, threads, 0, stream>>>(p, nullptr);
   return cudaGetLastError();
 }
 
@@ -219,11 +206,18 @@ static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, i
   static const int unroll = EnvInt("IBCOMM_NVLS_UNROLL", 4);
   static const int threads_env = EnvInt("IBCOMM_NVLS_THREADS", dev::kNvlsThreads);
   const int threads = (threads_env >= 64 && threads_env <= dev::kNvlsThreads && threads_env % 32 == 0) ? threads_env : dev::kNvlsThreads;
-  if (!p.use_multimem) return LaunchNvlsU<T, 4, false>(p, emu, emu_ranks, blocks, threads, stream);
+  if (!p.use_multimem) {
+    // Direct variant: compiled per world-size class (loads in flight per rank).
+    switch (dev::RankClass(p.world_size)) {
+      case 2: return LaunchNvlsU<T, 4, false, 2>(p, emu, emu_ranks, blocks, threads, stream);
+      case 4: return LaunchNvlsU<T, 4, false, 4>(p, emu, emu_ranks, blocks, threads, stream);
+      default: return LaunchNvlsU<T, 4, false, kMaxRanks>(p, emu, emu_ranks, blocks, threads, stream);
+    }
+  }
   if constexpr (dev::HasMultimem<T>::value) {
-    if (unroll == 8) return LaunchNvlsU<T, 8, true>(p, emu, emu_ranks, blocks, threads, stream);
-    if (unroll == 2) return LaunchNvlsU<T, 2, true>(p, emu, emu_ranks, blocks, threads, stream);
-    return LaunchNvlsU<T, 4, true>(p, emu, emu_ranks, blocks, threads, stream);
+    if (unroll == 8) return LaunchNvlsU<T, 8, true, kMaxRanks>(p, emu, emu_ranks, blocks, threads, stream);
+    if (unroll == 2) return LaunchNvlsU<T, 2, true, kMaxRanks>(p, emu, emu_ranks, blocks, threads, stream);
+    return LaunchNvlsU<T, 4, true, kMaxRanks>(p, emu, emu_ranks, blocks, threads, stream);
   } else {
     return cudaErrorInvalidValue;
   }

@@ -65,7 +65,7 @@ __device__ __forceinline__ void StUser16(unsigned char* p, uint4 v, bool aligned
   for (int k = 0; k < kN; ++k) d[k] = u.e[k];
 }
 
-template <typename T, bool kMultimem, bool kVec>
+template <typename T, bool kMultimem, bool kVec, int kR>
 __device__ void RsAgBody(const RsAgParams& p, uint64_t seq, int& s_stop) {
   using A = typename Acc<T>::type;
   constexpr int kUnitElems = kVec ? 16 / static_cast<int>(sizeof(T)) : 1;
@@ -120,36 +120,23 @@ __device__ void RsAgBody(const RsAgParams& p, uint64_t seq, int& s_stop) {
       }
       const uint64_t off = static_cast<uint64_t>(me) * p.sub_stride_bytes + remote_base;
       unsigned char* out = recv + w0 * kUnitBytes;
-      for (uint64_t i = b + threadIdx.x; i < e; i += blockDim.x) {
-        if constexpr (kVec) {
-          uint4 r;
-          if constexpr (kMultimem) {
-            r = Multimem<T>::LdReduce(p.mc_buf + off + i * 16);
-            if (do_scale) {
-              A acc[kUnitElems];
-              VecIO<T>::Load(r, acc);
-#pragma unroll
-              for (int k = 0; k < kUnitElems; ++k) acc[k] = ScaleAcc<A>(acc[k], p.scale);
-              r = VecIO<T>::Store(acc);
-            }
-          } else {
-            uint4 v[kMaxRanks];
-#pragma unroll
-            for (int q = 0; q < kMaxRanks; ++q)
-              if (q < ws) v[q] = Ld16Strong(p.peer_buf[q] + off + i * 16);
+      if constexpr (kVec && kMultimem) {
+        for (uint64_t i = b + threadIdx.x; i < e; i += blockDim.x) {
+          uint4 r = Multimem<T>::LdReduce(p.mc_buf + off + i * 16);
+          if (do_scale) {
             A acc[kUnitElems];
-            VecIO<T>::Load(v[0], acc);
+            VecIO<T>::Load(r, acc);
 #pragma unroll
-            for (int q = 1; q < kMaxRanks; ++q)
-              if (q < ws) VecIO<T>::Add(v[q], acc);
-            if (do_scale) {
-#pragma unroll
-              for (int k = 0; k < kUnitElems; ++k) acc[k] = ScaleAcc<A>(acc[k], p.scale);
-            }
+            for (int k = 0; k < kUnitElems; ++k) acc[k] = ScaleAcc<A>(acc[k], p.scale);
             r = VecIO<T>::Store(acc);
           }
           StUser16<T>(out + i * 16, r, recv_aligned);
-        } else {
+        }
+      } else if constexpr (kVec) {
+        PeerReduce<T, kR>(p.peer_buf, ws, off, b, e, do_scale, p.scale,
+                      [&](uint64_t idx, uint4 r) { StUser16<T>(out + idx * 16, r, recv_aligned); });
+      } else {
+        for (uint64_t i = b + threadIdx.x; i < e; i += blockDim.x) {
           A acc = A(0);
           for (int q = 0; q < ws; ++q) acc += ToAcc<A, T>(LdScalarStrong<T>(reinterpret_cast<const T*>(p.peer_buf[q] + off) + i));
           if (do_scale) acc = ScaleAcc<A>(acc, p.scale);
@@ -198,7 +185,7 @@ __device__ void RsAgBody(const RsAgParams& p, uint64_t seq, int& s_stop) {
   }
 }
 
-template <typename T, bool kMultimem, bool kVec>
+template <typename T, bool kMultimem, bool kVec, int kR>
 __global__ void __launch_bounds__(kNvlsThreads, 1) RsAgKernel(const __grid_constant__ RsAgParams p0, const RsAgParams* __restrict__ emu) {
   __shared__ RsAgParams p;
   __shared__ int s_stop;
@@ -210,22 +197,22 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) RsAgKernel(const __grid_const
   }
   __syncthreads();
   const uint64_t seq = BeginCollective(p.peers, p.rank, &s_seq);
-  RsAgBody<T, kMultimem, kVec>(p, seq, s_stop);
+  RsAgBody<T, kMultimem, kVec, kR>(p, seq, s_stop);
   EndCollective(p.peers, p.rank, seq, gridDim.x);
 }
 
 }  // namespace dev
 
-template <typename T, bool kMultimem, bool kVec>
+template <typename T, bool kMultimem, bool kVec, int kR>
 static cudaError_t LaunchRsAgU(const RsAgParams& p, const RsAgParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
   dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(emu != nullptr ? emu_ranks : 1));
   if (emu != nullptr) {
     // Emulated ranks wait on each other inside this launch: cooperative, so
     // the runtime refuses a grid that cannot be co-resident.
     void* args[] = {const_cast<RsAgParams*>(&p), &emu};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::RsAgKernel<T, kMultimem, kVec>), grid, dim3(dev::kNvlsThreads), args, 0, stream);
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(dev::RsAgKernel<T, kMultimem, kVec, kR>), grid, dim3(dev::kNvlsThreads), args, 0, stream);
   }
-  dev::RsAgKernel<T, kMultimem, kVec><<<grid, dev::kNvlsThreads, 0, stream>>>(p, nullptr);
+  dev::RsAgKernel<T, kMultimem, kVec, kR><<<grid, dev::kNvlsThreads, 0, stream>>>(p, nullptr);
   return cudaGetLastError();
 }
 
@@ -235,13 +222,18 @@ static cudaError_t LaunchRsAgTyped(const RsAgParams& p, const RsAgParams* emu, i
   if (p.use_multimem) {
     if constexpr (dev::HasMultimem<T>::value) {
       if (!vec) return cudaErrorInvalidValue;
-      return LaunchRsAgU<T, true, true>(p, emu, emu_ranks, blocks, stream);
+      return LaunchRsAgU<T, true, true, kMaxRanks>(p, emu, emu_ranks, blocks, stream);
     } else {
       return cudaErrorInvalidValue;
     }
   }
-  return vec ? LaunchRsAgU<T, false, true>(p, emu, emu_ranks, blocks, stream)
-             : LaunchRsAgU<T, false, false>(p, emu, emu_ranks, blocks, stream);
+  if (!vec) return LaunchRsAgU<T, false, false, kMaxRanks>(p, emu, emu_ranks, blocks, stream);
+  // Peer loads: compiled per world-size class (loads in flight per rank).
+  switch (dev::RankClass(p.world_size)) {
+    case 2: return LaunchRsAgU<T, false, true, 2>(p, emu, emu_ranks, blocks, stream);
+    case 4: return LaunchRsAgU<T, false, true, 4>(p, emu, emu_ranks, blocks, stream);
+    default: return LaunchRsAgU<T, false, true, kMaxRanks>(p, emu, emu_ranks, blocks, stream);
+  }
 }
 
 cudaError_t LaunchRsAgKernel(const RsAgParams& p, const RsAgParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {

@@ -104,6 +104,53 @@ __device__ __forceinline__ void WindowPart(uint64_t full_nvec, uint64_t nvec, in
   if (*e > nvec) *e = nvec;
 }
 
+// Units [b, e) of 16 bytes at `off` in every rank's buffer, summed in rank
+// order (so the bits do not depend on who reduces), scaled, and handed to
+// `store(index, value)`.  Peer loads are latency-bound: kU vectors per rank
+// are in flight per thread, for at most kR ranks (kU * kR <= 8 keeps the
+// loads in registers).
+template <typename T, int kU, int kR, typename Store>
+__device__ __forceinline__ void PeerReduceUnits(unsigned char* const* peer, int ws, uint64_t off, uint64_t b, uint64_t e,
+                                                bool do_scale, double scale, Store store) {
+  using A = typename Acc<T>::type;
+  constexpr int kVecElems = 16 / static_cast<int>(sizeof(T));
+  for (uint64_t i = b + threadIdx.x; i < e; i += static_cast<uint64_t>(blockDim.x) * kU) {
+    uint4 v[kU][kR];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+#pragma unroll
+      for (int q = 0; q < kR; ++q)
+        if (q < ws && idx < e) v[u][q] = Ld16Strong(peer[q] + off + idx * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+      if (idx < e) {
+        A acc[kVecElems];
+        VecIO<T>::Load(v[u][0], acc);
+#pragma unroll
+        for (int q = 1; q < kR; ++q)
+          if (q < ws) VecIO<T>::Add(v[u][q], acc);
+        if (do_scale) {
+#pragma unroll
+          for (int k = 0; k < kVecElems; ++k) acc[k] = ScaleAcc<A>(acc[k], scale);
+        }
+        store(idx, VecIO<T>::Store(acc));
+      }
+    }
+  }
+}
+
+// The kernels are compiled per world-size class kR (2, 4 or 8 ranks at most)
+// with 8 / kR vectors in flight per rank: 2 ranks x 4 vectors, 4 x 2, 8 x 1.
+template <typename T, int kR, typename Store>
+__device__ __forceinline__ void PeerReduce(unsigned char* const* peer, int ws, uint64_t off, uint64_t b, uint64_t e,
+                                           bool do_scale, double scale, Store store) {
+  PeerReduceUnits<T, kMaxRanks / kR, kR>(peer, ws, off, b, e, do_scale, scale, store);
+}
+inline int RankClass(int world_size) { return world_size <= 2 ? 2 : (world_size <= 4 ? 4 : kMaxRanks); }
+
 // Barrier between CTA `cta` of every rank.  Returns false when it gave up.
 __device__ inline bool CrossRankBarrier(const PeerTable& peers, const WaitCtx& w, int cta, uint32_t phase, int* s_stop) {
   __syncthreads();
