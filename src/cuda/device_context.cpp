@@ -831,9 +831,11 @@ void DeviceContext::ReduceScatterOrAllGather(int mode, DType dtype, const void* 
   const bool nvls_possible = mc_ != nullptr && NvlsSupportsDType(dtype) && vec && (!zero_copy || (sym != nullptr && sym->mc));
   if (algo == Algo::kNvls && !nvls_possible)
     IBCOMM_FAIL(NOT_SUPPORTED, "The NVLS algorithm needs NVSwitch multicast, a float32/float16/bfloat16 buffer and blocks of whole 16-byte vectors.\n");
-  // The switch wins from 3 ranks on (1 + 1/ws of the block per direction
-  // against (ws-1)/ws per direction and phase); 2 ranks go direct.
-  if (algo == Algo::kAuto) algo = (nvls_possible && ws_ > 2) ? Algo::kNvls : Algo::kDirect;
+  // Each half moves (ws-1)/ws of the message per direction whichever way it
+  // runs, so the switch has no bandwidth edge here: mapped buffers go direct
+  // (measured faster on 8 B200 at all sizes but 16 MiB); through the pool the
+  // switch saves the reducing rank its peer loads.
+  if (algo == Algo::kAuto) algo = (nvls_possible && ws_ > 2 && !zero_copy) ? Algo::kNvls : Algo::kDirect;
   p.use_multimem = algo == Algo::kNvls ? 1 : 0;
 
   if (zero_copy) {
