@@ -253,13 +253,19 @@ class Communicator:
                        stream: Optional[torch.cuda.Stream] = None, sync: bool = False) -> torch.Tensor:
         """``recvbuf`` = ``scale`` * sum over ranks of block ``rank`` of ``sendbuf``.
 
-        ``sendbuf`` holds ``world_size`` blocks of ``recvbuf.numel()`` elements (CUDA
-        tensors; ``algo``: auto, nvls or direct).  ``recvbuf`` may be block ``rank`` of
+        ``sendbuf`` holds ``world_size`` blocks of ``recvbuf.numel()`` elements.  CUDA
+        tensors: ``algo`` auto, nvls or direct; CPU tensors: a ring over the host transport.  ``recvbuf`` may be block ``rank`` of
         ``sendbuf`` (in place)."""
         if sendbuf.dtype != recvbuf.dtype or sendbuf.numel() != recvbuf.numel() * self.world_size:
             raise IbcommError(_native.INVALID_ARGUMENT, "sendbuf must hold world_size blocks of recvbuf's size and dtype")
-        if not (sendbuf.is_cuda and recvbuf.is_cuda):
-            raise IbcommError(_native.NOT_SUPPORTED, "reduce_scatter takes CUDA tensors")
+        if sendbuf.is_cuda != recvbuf.is_cuda:
+            raise IbcommError(_native.INVALID_ARGUMENT, "sendbuf and recvbuf must live on the same kind of device")
+        if not sendbuf.is_cuda:
+            check(_native.lib().ibcomm_reduce_scatter_host(self._h, dtype_code(sendbuf.dtype), _ptr(sendbuf), _ptr(recvbuf),
+                                                           recvbuf.numel()))
+            if scale != 1.0:
+                recvbuf.mul_(scale)
+            return recvbuf
         s = stream if stream is not None else torch.cuda.current_stream(sendbuf.device)
         check(_native.lib().ibcomm_reduce_scatter_cuda(self._h, ALGO_CODES[algo], dtype_code(sendbuf.dtype), _ptr(sendbuf),
                                                        _ptr(recvbuf), recvbuf.numel(), float(scale),
@@ -268,13 +274,18 @@ class Communicator:
 
     def all_gather(self, sendbuf: torch.Tensor, recvbuf: torch.Tensor, *, algo: str = "auto",
                    stream: Optional[torch.cuda.Stream] = None, sync: bool = False) -> torch.Tensor:
-        """Block ``r`` of ``recvbuf`` = rank ``r``'s ``sendbuf`` (CUDA tensors; ``algo``: auto, nvls or direct).
+        """Block ``r`` of ``recvbuf`` = rank ``r``'s ``sendbuf`` (CUDA tensors: ``algo`` auto, nvls or direct;
+        CPU tensors: a ring over the host transport).
 
         ``sendbuf`` may be block ``rank`` of ``recvbuf`` (in place)."""
         if sendbuf.dtype != recvbuf.dtype or recvbuf.numel() != sendbuf.numel() * self.world_size:
             raise IbcommError(_native.INVALID_ARGUMENT, "recvbuf must hold world_size blocks of sendbuf's size and dtype")
-        if not (sendbuf.is_cuda and recvbuf.is_cuda):
-            raise IbcommError(_native.NOT_SUPPORTED, "all_gather takes CUDA tensors")
+        if sendbuf.is_cuda != recvbuf.is_cuda:
+            raise IbcommError(_native.INVALID_ARGUMENT, "sendbuf and recvbuf must live on the same kind of device")
+        if not sendbuf.is_cuda:
+            check(_native.lib().ibcomm_all_gather_host(self._h, dtype_code(sendbuf.dtype), _ptr(sendbuf), _ptr(recvbuf),
+                                                       sendbuf.numel()))
+            return recvbuf
         s = stream if stream is not None else torch.cuda.current_stream(sendbuf.device)
         check(_native.lib().ibcomm_all_gather_cuda(self._h, ALGO_CODES[algo], dtype_code(sendbuf.dtype), _ptr(sendbuf),
                                                    _ptr(recvbuf), sendbuf.numel(), C.c_void_p(s.cuda_stream),

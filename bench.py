@@ -26,7 +26,7 @@ nodes = 4.818 GB/s bus bandwidth).  Rank 0 prints ONE JSON line:
 
 `--impl reference` reports why the reference cannot run on this box.
 `--sweep` runs the 4 KiB - 1 GiB message-size sweep per algorithm and writes
-JSON lines to --out (default gpurun_out/sweep_<N>gpu.jsonl).
+JSON lines to --out (default bench_out/sweep_<N>gpu.jsonl).
 """
 from __future__ import annotations
 
@@ -354,7 +354,7 @@ def rsag_sweep(args, comm, world, rank, dev, time_steps) -> int:
         if rank == 0:
             print(json.dumps({"rsag": None, "reason": "needs at least two GPUs"}))
         return 0
-    out_path = args.out or f"gpurun_out/rsag_{world}gpu.jsonl"
+    out_path = args.out or f"bench_out/rsag_{world}gpu.jsonl"
     max_bytes = min(args.sweep_max_bytes, 1 << 30)
     nmax = max_bytes // 4
     full = {"symmetric": comm.symmetric_empty(nmax, torch.float32), "plain": torch.empty(nmax, device=dev),
@@ -419,7 +419,7 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
 
     from allreduce_proto_b200.utils import busbw_gbs
 
-    out_path = args.out or f"gpurun_out/sweep_{world}gpu.jsonl"
+    out_path = args.out or f"bench_out/sweep_{world}gpu.jsonl"
     info = comm.device_info(connect=world > 1)
     rows = []
     max_bytes = args.sweep_max_bytes

@@ -53,6 +53,9 @@ int ibcomm_allreduce_host(ibcomm_comm* c, int algo, int dtype, const void* sendb
 #define IBCOMM_USE_STREAM 2
 int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t len_elements,
                           double scale, int wire_dtype, void* stream, int flags);
+/* Host buffers: the halves of the ring allreduce (float32, float64, int32, int64). */
+int ibcomm_reduce_scatter_host(ibcomm_comm* c, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements);
+int ibcomm_all_gather_host(ibcomm_comm* c, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements);
 /* Halves of the allreduce: block r belongs to rank r.  reduce_scatter: sendbuf
  * holds world_size blocks, recvbuf one; all_gather: the other way round.
  * algo: auto, nvls or direct. */

@@ -115,6 +115,14 @@ class Communicator {
   void AllreduceRing(const T* sendbuf, T* recvbuf, size_t len_elements);
   template <typename T>
   void AllreduceRabenseifner(const T* sendbuf, T* recvbuf, size_t len_elements);
+  // The halves of the ring allreduce on host buffers (no counterpart in the
+  // reference): block r belongs to rank r.  ReduceScatter: sendbuf holds
+  // world_size blocks of `block_elements`, recvbuf one; AllGather: the other
+  // way round.
+  template <typename T>
+  void ReduceScatter(const T* sendbuf, T* recvbuf, size_t block_elements);
+  template <typename T>
+  void AllGather(const T* sendbuf, T* recvbuf, size_t block_elements);
 #ifdef USE_CUDA
   template <typename T>
   void AllreduceRingCuda(const T* sendbuf, T* recvbuf, size_t len_elements);
@@ -248,6 +256,7 @@ struct CollectiveLease {
 using IBVerbsCommunicator = ibcomm::Communicator;
 
 #include "ibcomm/allreduce_cpu_impl.h"
+#include "ibcomm/rsag_cpu_impl.h"
 #ifdef USE_CUDA
 #include "ibcomm/allreduce_cuda_impl.h"
 #endif

@@ -651,7 +651,7 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   bool rin = !multimem && sin == nullptr && FindPeerMapped(sendbuf, bytes, reg_in);
   bool rout = !multimem && sout == nullptr && FindPeerMapped(recvbuf, bytes, reg_out);
   // Registered buffers sit at different offsets on different ranks: all
-  // ranks must come to the same verdict, so every rank's pointer has to be
+  // ranks must come to the same decision, so every rank's pointer has to be
   // 16-byte aligned (the mappings' bases are), not only this rank's.
   for (int q = 0; q < ws_; ++q) {
     if (rin && (reinterpret_cast<uintptr_t>(reg_in[q]) & 15u) != 0) rin = false;
@@ -826,7 +826,7 @@ void DeviceContext::ReduceScatterOrAllGather(int mode, DType dtype, const void* 
   unsigned char* mapped[kMaxRanks];
   bool zero_copy = vec && FindPeerMapped(remote, remote_bytes, mapped);
   for (int q = 0; q < ws_ && zero_copy; ++q)
-    if ((reinterpret_cast<uintptr_t>(mapped[q]) & 15u) != 0) zero_copy = false;  // the same verdict on every rank
+    if ((reinterpret_cast<uintptr_t>(mapped[q]) & 15u) != 0) zero_copy = false;  // the same decision on every rank
   const SymmetricAlloc* sym = FindSymmetric(remote, remote_bytes);
   const bool nvls_possible = mc_ != nullptr && NvlsSupportsDType(dtype) && vec && (!zero_copy || (sym != nullptr && sym->mc));
   if (algo == Algo::kNvls && !nvls_possible)

@@ -19,7 +19,7 @@
 // sub-block, on every rank and in every window, so the barriers are per CTA.
 //
 // Work is split in units of 16 bytes when a block is a whole number of them
-// (the same verdict on every rank), else in units of one element.  A user
+// (the same decision on every rank), else in units of one element.  A user
 // buffer that is only element-aligned is accessed element by element inside
 // the same split.
 #include <cooperative_groups.h>

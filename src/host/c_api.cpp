@@ -186,6 +186,33 @@ int ibcomm_allreduce_host(ibcomm_comm* c, int algo, int dtype, const void* sendb
   });
 }
 
+static int HostRsAg(ibcomm_comm* c, bool all_gather, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements) {
+  return Guard([&] {
+    Communicator& m = c->comm;
+#define IBCOMM_HOST_CASE(T)                                                                               \
+  do {                                                                                                    \
+    if (all_gather) m.AllGather(static_cast<const T*>(sendbuf), static_cast<T*>(recvbuf), block_elements); \
+    else m.ReduceScatter(static_cast<const T*>(sendbuf), static_cast<T*>(recvbuf), block_elements);       \
+  } while (0)
+    switch (CheckDType(dtype)) {
+      case ibcomm::DType::kFloat32: IBCOMM_HOST_CASE(float); break;
+      case ibcomm::DType::kFloat64: IBCOMM_HOST_CASE(double); break;
+      case ibcomm::DType::kInt32: IBCOMM_HOST_CASE(int32_t); break;
+      case ibcomm::DType::kInt64: IBCOMM_HOST_CASE(int64_t); break;
+      default: IBCOMM_FAIL(NOT_SUPPORTED, "Host reduce-scatter / all-gather support float32, float64, int32 and int64.\n");
+    }
+#undef IBCOMM_HOST_CASE
+  });
+}
+
+int ibcomm_reduce_scatter_host(ibcomm_comm* c, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements) {
+  return HostRsAg(c, false, dtype, sendbuf, recvbuf, block_elements);
+}
+
+int ibcomm_all_gather_host(ibcomm_comm* c, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements) {
+  return HostRsAg(c, true, dtype, sendbuf, recvbuf, block_elements);
+}
+
 int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t n, double scale,
                           int wire_dtype, void* stream, int flags) {
   return Guard([&] {

@@ -41,6 +41,35 @@ def case_allreduce(comm):
     return 0 if torch.allclose(d, torch.full((777,), float(WS * (WS + 1) / 2), dtype=torch.float64)) else 1
 
 
+def case_rsag(comm):
+    # Reduce-scatter and all-gather on host buffers: block r belongs to rank r.
+    for m in (1, 1000, 1_500_001):  # the last one is larger than a transport ring
+        n = m * WS
+        x = torch.from_numpy(np.random.default_rng(100 + RANK).integers(-1000, 1000, n).astype(np.int64))
+        want = np.zeros(n, dtype=np.int64)
+        for r in range(WS):
+            want += np.random.default_rng(100 + r).integers(-1000, 1000, n).astype(np.int64)
+        y = torch.zeros(m, dtype=torch.int64)
+        comm.reduce_scatter(x, y)
+        if not np.array_equal(y.numpy(), want[RANK * m:(RANK + 1) * m]):
+            print(f"rank {RANK}: reduce_scatter m={m} mismatch", file=sys.stderr)
+            return 1
+        z = torch.zeros(n, dtype=torch.int64)
+        comm.all_gather(y, z)
+        if not np.array_equal(z.numpy(), want):
+            print(f"rank {RANK}: all_gather m={m} mismatch", file=sys.stderr)
+            return 1
+        # in place, float, with the scale
+        f = x.to(torch.float64)
+        mine = f[RANK * m:(RANK + 1) * m]
+        comm.reduce_scatter(f, mine, scale=0.5)
+        comm.all_gather(mine, f)
+        if not np.allclose(f.numpy(), want * 0.5):
+            print(f"rank {RANK}: in-place reduce_scatter + all_gather m={m} mismatch", file=sys.stderr)
+            return 1
+    return 0
+
+
 def case_messaging(comm):
     to, frm = (RANK + 1) % WS, (RANK - 1) % WS
     out = np.arange(100000, dtype=np.int32) + RANK

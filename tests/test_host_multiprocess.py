@@ -44,6 +44,12 @@ def test_ranks_as_threads_of_one_process(bins, np_):
     assert "threads_test OK" in p.stdout
 
 
+@pytest.mark.parametrize("np_", [2, 3, 5])
+def test_reduce_scatter_and_all_gather_on_host_buffers(bins, np_):
+    code, err = run(bins, np_, "rsag")
+    assert code == 0, err
+
+
 def test_messaging_and_bcast(bins):
     code, err = run(bins, 3, "messaging")
     assert code == 0, err
