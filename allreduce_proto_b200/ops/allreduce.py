@@ -32,6 +32,18 @@ def allreduce(tensor: torch.Tensor, out: Optional[torch.Tensor] = None, *, algo:
     return (comm or default_communicator()).allreduce(tensor, out, algo=algo, scale=scale, wire=wire, sync=sync)
 
 
+def reduce_scatter(tensor: torch.Tensor, out: torch.Tensor, *, algo: str = "auto", scale: float = 1.0,
+                   sync: bool = False, comm: Optional[Communicator] = None) -> torch.Tensor:
+    """``out`` = ``scale`` * sum over ranks of block ``rank`` of ``tensor`` (``world_size`` blocks)."""
+    return (comm or default_communicator()).reduce_scatter(tensor, out, algo=algo, scale=scale, sync=sync)
+
+
+def all_gather(tensor: torch.Tensor, out: torch.Tensor, *, algo: str = "auto", sync: bool = False,
+               comm: Optional[Communicator] = None) -> torch.Tensor:
+    """Block ``r`` of ``out`` = rank ``r``'s ``tensor``."""
+    return (comm or default_communicator()).all_gather(tensor, out, algo=algo, sync=sync)
+
+
 def copy_scale(src: torch.Tensor, dst: Optional[torch.Tensor] = None, scale: float = 1.0,
                out_dtype=None) -> torch.Tensor:
     """``dst = cast(src * scale)`` with the library's bulk-copy kernel (the

@@ -279,6 +279,14 @@ def test_world_size_one_copy_scale_kernel():
         y = torch.empty_like(x)
         comm.allreduce(x, y, scale=0.5, sync=True)
         torch.testing.assert_close(y, x * 0.5)
+    # The halves at world size 1 are the same copy (the reduce-scatter with its scale).
+    x = torch.randn(4099, device="cuda")
+    y = torch.empty_like(x)
+    comm.reduce_scatter(x, y, scale=0.25, sync=True)
+    torch.testing.assert_close(y, x * 0.25)
+    z = torch.empty_like(x)
+    comm.all_gather(y, z, sync=True)
+    torch.testing.assert_close(z, y)
     x = torch.randn(100003, device="cuda")
     for out_dtype in (torch.bfloat16, torch.float16):
         y = ar.ops.copy_scale(x, scale=2.0, out_dtype=out_dtype)
