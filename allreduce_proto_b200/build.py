@@ -66,6 +66,7 @@ PROGRAMS = [
     ("sendrecv", "tests/cpp/sendrecv_test.cpp", False),
     ("unittest", "tests/cpp/unittest.cpp", False),
     ("schedule_sim", "tests/cpp/schedule_sim.cpp", False),
+    ("twoshot_sim", "tests/cpp/twoshot_sim.cpp", False),
     ("threads_test", "tests/cpp/threads_test.cpp", False),
     ("threads_test_cuda", "tests/cpp/threads_test.cpp", True),
 ]

@@ -148,6 +148,36 @@ IBCOMM_HD inline void ChannelSlice(uint64_t first, uint64_t count, uint64_t slot
   *hi = e;
 }
 
+// ---- how the two-shot kernels split a staging window among ranks and CTAs ----
+// [*b, *e) = part `part` of `parts` of the range [lo, hi).
+IBCOMM_HD inline void SubRange(uint64_t lo, uint64_t hi, int part, int parts, uint64_t* b, uint64_t* e) {
+  const uint64_t len = hi - lo;
+  const uint64_t per = (len + static_cast<uint64_t>(parts) - 1) / static_cast<uint64_t>(parts);
+  uint64_t x = lo + per * static_cast<uint64_t>(part);
+  if (x > hi) x = hi;
+  uint64_t y = x + per;
+  if (y > hi) y = hi;
+  *b = x;
+  *e = y;
+}
+
+// Part `part` of `parts` of shard `s` of a window, in 16-byte vectors.  The
+// split is that of a FULL window (`full_nvec` vectors) clipped to the `nvec`
+// vectors this window holds: a CTA then covers the same bytes of the staging
+// windows in every window of a call, the short last one included.  The
+// barriers are per CTA, so they order a CTA's accesses only against the same
+// CTA of the other ranks; a split that moved with the window's length would
+// let a CTA that is one window ahead overwrite bytes that another CTA has not
+// copied out yet.
+IBCOMM_HD inline void WindowPart(uint64_t full_nvec, uint64_t nvec, int s, int ws, int part, int parts, uint64_t* b,
+                                           uint64_t* e) {
+  uint64_t sb, se;
+  SubRange(0, full_nvec, s, ws, &sb, &se);
+  SubRange(sb, se, part, parts, b, e);
+  if (*b > nvec) *b = nvec;
+  if (*e > nvec) *e = nvec;
+}
+
 struct PeerTable {
   unsigned char* arena[kMaxRanks];  // every rank's arena as mapped here
   unsigned char* mc_arena;          // multicast alias of the arenas, or null

@@ -73,6 +73,13 @@ std::vector<Range> SplitForDevice(size_t len_elements, size_t elem_bytes, size_t
 
 std::string DescribeOp(const Op& op);
 
+// Elements per staging window of the two-shot kernel for a message of `n`
+// elements when a window can hold `cap_elems`: as few windows as fit, of equal
+// size (the kernel splits every window as a full one, so a much shorter last
+// window would leave most of its CTAs idle), a whole number of 16-byte
+// vectors per rank and channel.
+uint64_t TwoShotWindowElems(uint64_t n, uint64_t cap_elems, size_t esize, int world_size, int channels);
+
 // Bounds check of a program before it is handed to the device: every op's
 // message range inside `len_elements`, its place inside a staging slot, and
 // its slot, region and peer indices inside the program's stage geometry.

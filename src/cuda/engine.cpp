@@ -63,17 +63,6 @@ uint32_t StatusBlock::Consume(DeviceStatus* out, cudaStream_t stream) {
   return st.code;
 }
 
-uint64_t TwoShotWindowElems(uint64_t n, uint64_t cap_elems, size_t esize, int world_size, int channels) {
-  if (cap_elems == 0) cap_elems = 1;
-  if (n <= 1) return 1;
-  const uint64_t windows = (n + cap_elems - 1) / cap_elems;
-  const uint64_t per = (n + windows - 1) / windows;
-  const uint64_t granule = static_cast<uint64_t>(16 / esize) * static_cast<uint64_t>(world_size) * static_cast<uint64_t>(channels > 0 ? channels : 1);
-  const uint64_t rounded = (per + granule - 1) / granule * granule;
-  // The pool holds a whole number of vectors, so the cap keeps windows aligned.
-  return rounded < cap_elems ? rounded : cap_elems;
-}
-
 std::string DescribeStatus(const DeviceStatus& st) {
   static const char* const codes[] = {"ok", "wait timed out", "aborted by a peer", "bad program"};
   static const char* const kinds[] = {"?", "barrier", "data flag", "slot credit", "mailbox", "one-shot flag"};

@@ -63,13 +63,6 @@ ExecParams MakeExecParams(const RankResources& rr, const CachedProgram& cp, DTyp
 OneShotParams MakeOneShotParams(const RankResources& rr, DType dtype, const void* sendbuf, void* recvbuf,
                                 size_t len_elements, double scale, uint64_t timeout_ns);
 
-// Elements per staging window of the two-shot kernel for a message of `n`
-// elements when a window can hold `cap_elems`: as few windows as fit, of equal
-// size (the kernel splits every window as a full one, so a much shorter last
-// window would leave most of its CTAs idle), a whole number of 16-byte
-// vectors per rank and channel.
-uint64_t TwoShotWindowElems(uint64_t n, uint64_t cap_elems, size_t esize, int world_size, int channels);
-
 // Formats a failure report.
 std::string DescribeStatus(const DeviceStatus& st);
 

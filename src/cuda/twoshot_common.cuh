@@ -75,35 +75,6 @@ __device__ __forceinline__ void CopyVectors(uint4* dst, const uint4* src, uint64
   }
 }
 
-// [*b, *e) = part `part` of `parts` of the range [lo, hi).
-__device__ __forceinline__ void SubRange(uint64_t lo, uint64_t hi, int part, int parts, uint64_t* b, uint64_t* e) {
-  const uint64_t len = hi - lo;
-  const uint64_t per = (len + static_cast<uint64_t>(parts) - 1) / static_cast<uint64_t>(parts);
-  uint64_t x = lo + per * static_cast<uint64_t>(part);
-  if (x > hi) x = hi;
-  uint64_t y = x + per;
-  if (y > hi) y = hi;
-  *b = x;
-  *e = y;
-}
-
-// Part `part` of `parts` of shard `s` of a window, in 16-byte vectors.  The
-// split is that of a FULL window (`full_nvec` vectors) clipped to the `nvec`
-// vectors this window holds: a CTA then covers the same bytes of the staging
-// windows in every window of a call, the short last one included.  The
-// barriers are per CTA, so they order a CTA's accesses only against the same
-// CTA of the other ranks; a split that moved with the window's length would
-// let a CTA that is one window ahead overwrite bytes that another CTA has not
-// copied out yet.
-__device__ __forceinline__ void WindowPart(uint64_t full_nvec, uint64_t nvec, int s, int ws, int part, int parts, uint64_t* b,
-                                           uint64_t* e) {
-  uint64_t sb, se;
-  SubRange(0, full_nvec, s, ws, &sb, &se);
-  SubRange(sb, se, part, parts, b, e);
-  if (*b > nvec) *b = nvec;
-  if (*e > nvec) *e = nvec;
-}
-
 // Units [b, e) of 16 bytes at `off` in every rank's buffer, summed in rank
 // order (so the bits do not depend on who reduces), scaled, and handed to
 // `store(index, value)`.  Peer loads are latency-bound: kU vectors per rank

@@ -336,6 +336,17 @@ std::vector<Range> SplitForDevice(size_t len_elements, size_t elem_bytes, size_t
   return out;
 }
 
+uint64_t TwoShotWindowElems(uint64_t n, uint64_t cap_elems, size_t esize, int world_size, int channels) {
+  if (cap_elems == 0) cap_elems = 1;
+  if (n <= 1) return 1;
+  const uint64_t windows = (n + cap_elems - 1) / cap_elems;
+  const uint64_t per = (n + windows - 1) / windows;
+  const uint64_t granule = static_cast<uint64_t>(16 / esize) * static_cast<uint64_t>(world_size) * static_cast<uint64_t>(channels > 0 ? channels : 1);
+  const uint64_t rounded = (per + granule - 1) / granule * granule;
+  // The pool holds a whole number of vectors, so the cap keeps windows aligned.
+  return rounded < cap_elems ? rounded : cap_elems;
+}
+
 std::string ValidateProgram(const Program& prog, uint64_t len_elements, size_t wire_elem_bytes, int world_size) {
   for (size_t i = 0; i < prog.ops.size(); ++i) {
     const Op& op = prog.ops[i];
