@@ -800,9 +800,13 @@ void DeviceContext::ReduceScatterOrAllGather(int mode, DType dtype, const void* 
   }
   ConnectPeers();
   Algo algo = opts.algo;
-  if (algo == Algo::kAuto) algo = AlgoFromName(env::ReadAlgo());
   if (algo != Algo::kAuto && algo != Algo::kNvls && algo != Algo::kDirect)
     IBCOMM_FAIL(NOT_SUPPORTED, "Reduce-scatter and all-gather run the nvls or the direct algorithm.\n");
+  if (algo == Algo::kAuto) {
+    // IBCOMM_ALGO names an allreduce algorithm; it applies here when it names one of the two halves.
+    const Algo from_env = AlgoFromName(env::ReadAlgo());
+    if (from_env == Algo::kNvls || from_env == Algo::kDirect) algo = from_env;
+  }
 
   RsAgParams p;
   memset(&p, 0, sizeof(p));
@@ -828,6 +832,9 @@ void DeviceContext::ReduceScatterOrAllGather(int mode, DType dtype, const void* 
   for (int q = 0; q < ws_ && zero_copy; ++q)
     if ((reinterpret_cast<uintptr_t>(mapped[q]) & 15u) != 0) zero_copy = false;  // the same decision on every rank
   const SymmetricAlloc* sym = FindSymmetric(remote, remote_bytes);
+  // The switch path asked for by name on a buffer that is mapped but not bound
+  // to the multicast object (a registered one): through the pool.
+  if (algo == Algo::kNvls && zero_copy && !(sym != nullptr && sym->mc)) zero_copy = false;
   const bool nvls_possible = mc_ != nullptr && NvlsSupportsDType(dtype) && vec && (!zero_copy || (sym != nullptr && sym->mc));
   if (algo == Algo::kNvls && !nvls_possible)
     IBCOMM_FAIL(NOT_SUPPORTED, "The NVLS algorithm needs NVSwitch multicast, a float32/float16/bfloat16 buffer and blocks of whole 16-byte vectors.\n");
