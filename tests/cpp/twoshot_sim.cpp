@@ -1,6 +1,7 @@
 // CPU-thread model of the staged two-shot protocols (nvls_kernel.cu,
-// rsag_kernel.cu): one thread per (rank, CTA), the pool windows as plain
-// arrays, the per-CTA cross-rank barriers as release/acquire flags.  It uses
+// rsag_kernel.cu) and of the one-shot protocol (oneshot_kernel.cu): one thread
+// per (rank, CTA), the pool windows and push slots as plain arrays, the
+// per-CTA cross-rank barriers and flags as release/acquire atomics.  It uses
 // the kernels' own split (`WindowPart`) and window sizing
 // (`TwoShotWindowElems`), so a split that lets a CTA run ahead into bytes
 // another CTA still needs shows up here: as a wrong sum, and as a data race
@@ -54,10 +55,10 @@ int64_t Sum(int ws, uint64_t i) {
 }
 
 // TwoShotBody, direct variant, both buffers staged.
-void AllreduceCta(World* w, int rank, int cta, const std::vector<int64_t>& send, std::vector<int64_t>* recv, uint64_t n,
-                  uint64_t window_elems) {
+void AllreduceCta(World* w, uint64_t seq, int rank, int cta, const std::vector<int64_t>& send, std::vector<int64_t>* recv,
+                  uint64_t n, uint64_t window_elems) {
   const int ws = w->ws, ncta = w->ncta;
-  uint64_t phase = 0;
+  uint64_t phase = seq << 32;  // flag values only grow, call after call
   const uint64_t full_nvec = (window_elems + kVec - 1) / kVec;
   for (uint64_t w0 = 0; w0 < n; w0 += window_elems) {
     const uint64_t wn = std::min<uint64_t>(window_elems, n - w0);
@@ -103,29 +104,34 @@ bool RunAllreduce(int ws, int ncta, uint64_t n, uint64_t cap_elems) {
   std::vector<std::vector<int64_t>> send(ws, std::vector<int64_t>(n)), recv(ws, std::vector<int64_t>(n, -1));
   for (int r = 0; r < ws; ++r)
     for (uint64_t i = 0; i < n; ++i) send[r][i] = Value(r, i);
-  // Two calls back to back (the second reuses the windows the first one left).
-  for (int call = 0; call < 2; ++call) {
-    std::vector<std::thread> th;
-    for (int r = 0; r < ws; ++r)
-      for (int c = 0; c < ncta; ++c) th.emplace_back(AllreduceCta, &w, r, c, std::cref(send[r]), &recv[r], n, window);
-    for (auto& t : th) t.join();
-    for (auto& b : w.bar) b.store(0);
-    for (int r = 0; r < ws; ++r)
+  // Every rank runs two calls back to back, like two kernels of one stream
+  // (the second reuses the windows the first one left); the ranks are not
+  // synchronised with each other between the calls.
+  std::atomic<int> bad{0};
+  auto rank_body = [&](int r) {
+    for (uint64_t seq = 1; seq <= 2; ++seq) {
+      std::fill(recv[r].begin(), recv[r].end(), -1);
+      std::vector<std::thread> ctas;
+      for (int c = 0; c < ncta; ++c) ctas.emplace_back(AllreduceCta, &w, seq, r, c, std::cref(send[r]), &recv[r], n, window);
+      for (auto& t : ctas) t.join();
       for (uint64_t i = 0; i < n; ++i)
-        if (recv[r][i] != Sum(ws, i)) {
-          fprintf(stderr, "allreduce ws=%d ncta=%d n=%llu window=%llu: rank %d element %llu wrong\n", ws, ncta,
-                  static_cast<unsigned long long>(n), static_cast<unsigned long long>(window), r, static_cast<unsigned long long>(i));
-          return false;
-        }
-  }
-  return true;
+        if (recv[r][i] != Sum(ws, i)) ++bad;
+    }
+  };
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < ws; ++r) ranks.emplace_back(rank_body, r);
+  for (auto& t : ranks) t.join();
+  if (bad.load() != 0)
+    fprintf(stderr, "allreduce ws=%d ncta=%d n=%llu window=%llu: %d wrong elements\n", ws, ncta, static_cast<unsigned long long>(n),
+            static_cast<unsigned long long>(window), bad.load());
+  return bad.load() == 0;
 }
 
 // RsAgBody, direct variant, remote side staged; units of one vector.
-void RsAgCta(World* w, bool all_gather, int rank, int cta, const std::vector<int64_t>& send, std::vector<int64_t>* recv,
-             uint64_t block_units, uint64_t win_units, uint64_t sub_stride) {
+void RsAgCta(World* w, uint64_t seq, bool all_gather, int rank, int cta, const std::vector<int64_t>& send,
+             std::vector<int64_t>* recv, uint64_t block_units, uint64_t win_units, uint64_t sub_stride) {
   const int ws = w->ws, ncta = w->ncta;
-  uint64_t phase = 0;
+  uint64_t phase = seq << 32;
   w->Barrier(rank, cta, ++phase);
   for (uint64_t w0 = 0; w0 < block_units; w0 += win_units) {
     const uint64_t wn = std::min<uint64_t>(win_units, block_units - w0);
@@ -162,27 +168,111 @@ bool RunRsAg(int ws, int ncta, uint64_t block_units, uint64_t cap_units) {
       gathered(ws, std::vector<int64_t>(m * ws, -1));
   for (int r = 0; r < ws; ++r)
     for (uint64_t i = 0; i < m * ws; ++i) full[r][i] = Value(r, i);
-  for (int pass = 0; pass < 2; ++pass) {
-    const bool all_gather = pass == 1;
-    std::vector<std::thread> th;
-    for (int r = 0; r < ws; ++r)
-      for (int c = 0; c < ncta; ++c)
-        th.emplace_back(RsAgCta, &w, all_gather, r, c, std::cref(all_gather ? shard[r] : full[r]),
-                        all_gather ? &gathered[r] : &shard[r], block_units, window, sub_stride);
-    for (auto& t : th) t.join();
-    for (auto& b : w.bar) b.store(0);
-  }
-  for (int r = 0; r < ws; ++r)
-    for (uint64_t i = 0; i < m * ws; ++i)
-      if (gathered[r][i] != Sum(ws, i)) {
-        fprintf(stderr, "rs+ag ws=%d ncta=%d block=%llu window=%llu: rank %d element %llu wrong\n", ws, ncta,
-                static_cast<unsigned long long>(m), static_cast<unsigned long long>(window * kVec), r, static_cast<unsigned long long>(i));
-        return false;
+  // Every rank runs the reduce-scatter and then the all-gather of its shard,
+  // as two kernels of one stream, twice; nothing else synchronises the ranks.
+  std::atomic<int> bad{0};
+  auto rank_body = [&](int r) {
+    uint64_t seq = 0;
+    for (int rep = 0; rep < 2; ++rep)
+      for (int pass = 0; pass < 2; ++pass) {
+        const bool all_gather = pass == 1;
+        ++seq;
+        std::vector<std::thread> ctas;
+        for (int c = 0; c < ncta; ++c)
+          ctas.emplace_back(RsAgCta, &w, seq, all_gather, r, c, std::cref(all_gather ? shard[r] : full[r]),
+                            all_gather ? &gathered[r] : &shard[r], block_units, window, sub_stride);
+        for (auto& t : ctas) t.join();
+        if (all_gather)
+          for (uint64_t i = 0; i < m * ws; ++i)
+            if (gathered[r][i] != Sum(ws, i)) ++bad;
       }
-  return true;
+  };
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < ws; ++r) ranks.emplace_back(rank_body, r);
+  for (auto& t : ranks) t.join();
+  if (bad.load() != 0)
+    fprintf(stderr, "rs+ag ws=%d ncta=%d block=%llu window=%llu: %d wrong elements\n", ws, ncta, static_cast<unsigned long long>(m),
+            static_cast<unsigned long long>(window * kVec), bad.load());
+  return bad.load() == 0;
+}
+
+// ---- one-shot: push to every peer's slot, flag, sum locally; slots are
+// double-buffered by the parity of the call number and there is no barrier at
+// the end of a call.  A rank runs its calls one after the other (kernels of
+// one stream), every call with its own number of CTAs.
+struct OneShotWorld {
+  int ws;
+  size_t cap;
+  static constexpr int kMaxCta = 8;
+  std::vector<std::vector<int64_t>> slots;  // [rank][(parity * ws + src) * cap + i]
+  std::vector<std::atomic<uint64_t>> flag;  // [rank][parity][cta][src]
+  OneShotWorld(int ws_, size_t cap_) : ws(ws_), cap(cap_), slots(ws_, std::vector<int64_t>(2 * ws_ * cap_)), flag(static_cast<size_t>(ws_) * 2 * kMaxCta * ws_) {
+    for (auto& f : flag) f.store(0);
+  }
+  int64_t* Slot(int owner, unsigned parity, int src) { return slots[owner].data() + (static_cast<size_t>(parity) * ws + src) * cap; }
+  std::atomic<uint64_t>& Flag(int owner, unsigned parity, int cta, int src) {
+    return flag[((static_cast<size_t>(owner) * 2 + parity) * kMaxCta + cta) * ws + src];
+  }
+};
+
+void OneShotCta(OneShotWorld* w, int me, int cta, int ncta, uint64_t seq, const std::vector<int64_t>& send, std::vector<int64_t>* recv) {
+  const int ws = w->ws;
+  const uint64_t n = send.size();
+  const unsigned parity = static_cast<unsigned>(seq & 1u);
+  const uint64_t nvec = (n + kVec - 1) / kVec, per = (nvec + ncta - 1) / ncta;
+  const uint64_t lo = std::min<uint64_t>(per * cta * kVec, n), hi = std::min<uint64_t>(lo + per * kVec, n);
+  for (int k = 1; k < ws; ++k) {
+    const int q = (me + k) % ws;
+    int64_t* dst = w->Slot(q, parity, me);
+    for (uint64_t i = lo; i < hi; ++i) dst[i] = send[i];
+  }
+  for (int q = 0; q < ws; ++q)
+    if (q != me) w->Flag(q, parity, cta, me).store(seq, std::memory_order_release);
+  for (int q = 0; q < ws; ++q)
+    if (q != me)
+      while (w->Flag(me, parity, cta, q).load(std::memory_order_acquire) < seq) std::this_thread::yield();
+  for (uint64_t i = lo; i < hi; ++i) {
+    int64_t acc = 0;
+    for (int q = 0; q < ws; ++q) acc += (q == me) ? send[i] : w->Slot(me, parity, q)[i];
+    (*recv)[i] = acc;
+  }
+}
+
+bool RunOneShot(int ws, const std::vector<std::pair<uint64_t, int>>& calls) {
+  OneShotWorld w(ws, 1024);
+  std::atomic<int> bad{0};
+  auto rank_body = [&](int me) {
+    uint64_t seq = 0;
+    for (size_t c = 0; c < calls.size(); ++c) {
+      const uint64_t n = calls[c].first;
+      const int ncta = calls[c].second;
+      ++seq;
+      std::vector<int64_t> send(n), recv(n, -1);
+      for (uint64_t i = 0; i < n; ++i) send[i] = Value(me, i + 31 * c);
+      std::vector<std::thread> ctas;
+      for (int b = 0; b < ncta; ++b) ctas.emplace_back(OneShotCta, &w, me, b, ncta, seq, std::cref(send), &recv);
+      for (auto& t : ctas) t.join();  // the kernel is over before the next one starts
+      for (uint64_t i = 0; i < n; ++i)
+        if (recv[i] != Sum(ws, i + 31 * c)) ++bad;
+    }
+  };
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < ws; ++r) ranks.emplace_back(rank_body, r);
+  for (auto& t : ranks) t.join();
+  if (bad.load() != 0) fprintf(stderr, "one-shot ws=%d: %d wrong elements\n", ws, bad.load());
+  return bad.load() == 0;
 }
 
 }  // namespace
+
+MINI_TEST(OneShotParityProtocol) {
+  // Calls of changing length and CTA count back to back, no barrier between them.
+  std::vector<std::pair<uint64_t, int>> calls;
+  const std::pair<uint64_t, int> pattern[] = {{100, 1}, {1000, 4}, {37, 1}, {1000, 3}, {1024, 8}, {64, 2}, {5, 1}, {999, 5}};
+  for (int rep = 0; rep < 6; ++rep)
+    for (const auto& c : pattern) calls.push_back(c);
+  for (int ws : {2, 3, 4}) CHECK_TRUE(RunOneShot(ws, calls));
+}
 
 MINI_TEST(PartOfAShortWindowLiesInsideThePartOfAFullOne) {
   // What the per-CTA barriers rely on: in every window of a call, CTA b only
