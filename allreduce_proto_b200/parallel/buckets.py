@@ -6,7 +6,12 @@ default) in parameter order; ``param.grad`` becomes a view into its bucket, so
 nothing is copied before or after the allreduce, which runs in place with the
 ``1 / world_size`` scale fused into the reduction kernel.  Buckets are taken
 from the communicator's symmetric memory when possible, which lets the switch
-reduce them without staging."""
+reduce them without staging.
+
+For sharded optimizers (each rank updates 1/world_size of every bucket) the
+same storage offers the two halves: :meth:`GradientBuckets.reduce_scatter`
+leaves a rank with the reduced block it owns, :meth:`GradientBuckets.all_gather`
+puts the blocks together again, both in place."""
 from __future__ import annotations
 
 from typing import Iterable, Optional, Sequence
@@ -41,9 +46,11 @@ class GradientBuckets:
     world size 1) for single-process use; then :meth:`allreduce` only scales."""
 
     def __init__(self, shapes: Sequence[Sequence[int]], *, dtype=torch.float32, device="cuda",
-                 comm: Optional[Communicator] = None, bucket_bytes: int = 25 << 20, symmetric: bool = True):
+                 comm: Optional[Communicator] = None, bucket_bytes: int = 25 << 20, symmetric: bool = True,
+                 shardable: bool = False):
         self.comm = comm
         self.dtype = dtype
+        self.shardable = shardable
         self.shapes = [tuple(s) for s in shapes]
         numels = [int(torch.Size(s).numel()) for s in self.shapes]
         esize = torch.empty((), dtype=dtype).element_size()
@@ -57,6 +64,10 @@ class GradientBuckets:
             for i in idxs:
                 offs.append(total)
                 total += (numels[i] + align - 1) // align * align
+            if shardable and comm is not None:
+                # world_size equal blocks of whole 16-byte vectors
+                unit = align * comm.world_size
+                total = (total + unit - 1) // unit * unit
             if comm is not None and comm.world_size > 1 and symmetric:
                 buf = comm.symmetric_empty(total, dtype)
             else:
@@ -93,3 +104,39 @@ class GradientBuckets:
             return
         for buf in self.flat:
             self.comm.allreduce(buf, algo=algo, scale=scale, wire=wire if buf.dtype == torch.float32 else None, sync=sync)
+
+    def shards(self) -> list[torch.Tensor]:
+        """This rank's block of every bucket (views; needs ``shardable=True``)."""
+        if not self.shardable:
+            raise ValueError("construct GradientBuckets with shardable=True")
+        ws = 1 if self.comm is None else self.comm.world_size
+        r = 0 if self.comm is None or ws == 1 else self.comm.rank
+        out = []
+        for buf in self.flat:
+            m = buf.numel() // ws
+            out.append(buf[r * m:(r + 1) * m])
+        return out
+
+    def reduce_scatter(self, *, average: bool = True, algo: str = "auto", sync: bool = False) -> list[torch.Tensor]:
+        """Sum (or mean) over the ranks of this rank's block of every bucket, in place.
+
+        Returns the blocks (the same views as :meth:`shards`); the rest of a bucket
+        is left as it was."""
+        mine = self.shards()
+        ws = 1 if self.comm is None else self.comm.world_size
+        scale = 1.0 / ws if average else 1.0
+        if self.comm is None or ws == 1:
+            if scale != 1.0:
+                torch._foreach_mul_(mine, scale)
+            return mine
+        for buf, shard in zip(self.flat, mine):
+            self.comm.reduce_scatter(buf, shard, algo=algo, scale=scale, sync=sync)
+        return mine
+
+    def all_gather(self, *, algo: str = "auto", sync: bool = False) -> None:
+        """Every bucket = the ranks' blocks side by side (in place, from :meth:`shards`)."""
+        mine = self.shards()
+        if self.comm is None or self.comm.world_size == 1:
+            return
+        for buf, shard in zip(self.flat, mine):
+            self.comm.all_gather(shard, buf, algo=algo, sync=sync)

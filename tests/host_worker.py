@@ -70,6 +70,34 @@ def case_rsag(comm):
     return 0
 
 
+def case_sharded_buckets(comm):
+    # Gradient buckets on host tensors: reduce-scatter leaves a rank its block
+    # of the mean, all-gather rebuilds the whole; the result equals the allreduce.
+    shapes = [(64, 3, 7, 7), (64,), (1000, 33), (5,), (12345,)]
+    def grads(r):
+        g = torch.Generator().manual_seed(r)
+        return [torch.rand(s, generator=g) * 2 - 1 for s in shapes]
+    want = [sum(gs) / WS for gs in zip(*[grads(r) for r in range(WS)])]
+    b = ar.GradientBuckets(shapes, device="cpu", comm=comm, bucket_bytes=64 << 10, symmetric=False, shardable=True)
+    b.load(grads(RANK))
+    mine = b.reduce_scatter(average=True)
+    if len(mine) != b.num_buckets or any(s.numel() * WS != f.numel() for s, f in zip(mine, b.flat)):
+        return 1
+    b.all_gather()
+    for v, w in zip(b.views, want):
+        if not torch.allclose(v, w, rtol=1e-5, atol=1e-6):
+            print(f"rank {RANK}: sharded buckets mismatch", file=sys.stderr)
+            return 1
+    ref = ar.GradientBuckets(shapes, device="cpu", comm=comm, bucket_bytes=64 << 10, symmetric=False)
+    ref.load(grads(RANK))
+    ref.allreduce(average=True, sync=True)
+    for v, w in zip(ref.views, want):
+        if not torch.allclose(v, w, rtol=1e-5, atol=1e-6):
+            print(f"rank {RANK}: bucket allreduce mismatch", file=sys.stderr)
+            return 1
+    return 0
+
+
 def case_messaging(comm):
     to, frm = (RANK + 1) % WS, (RANK - 1) % WS
     out = np.arange(100000, dtype=np.int32) + RANK

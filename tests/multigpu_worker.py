@@ -260,6 +260,27 @@ def case_buckets(comm):
     return 0
 
 
+def case_sharded_buckets(comm):
+    """ResNet-50 gradients in shardable buckets: reduce-scatter (mean), then all-gather, equals the allreduce."""
+    from allreduce_proto_b200.models import resnet50_param_shapes, synthetic_grads
+    shapes = [s for _, s in resnet50_param_shapes()]
+    buckets = ar.GradientBuckets(shapes, comm=comm, bucket_bytes=25 << 20, shardable=True)
+    buckets.load(synthetic_grads("cuda", seed=RANK))
+    mine = buckets.reduce_scatter(average=True, sync=True)
+    if any(s.numel() * WS != f.numel() for s, f in zip(mine, buckets.flat)):
+        return 1
+    buckets.all_gather(sync=True)
+    want = [torch.zeros(s, dtype=torch.float64, device="cuda") for s in shapes]
+    for r in range(WS):
+        for w, g in zip(want, synthetic_grads("cuda", seed=r)):
+            w += g.double()
+    for v, w in zip(buckets.views, want):
+        if not torch.allclose(v.double(), w / WS, rtol=1e-5, atol=1e-7):
+            print(f"rank {RANK}: sharded bucket mismatch", file=sys.stderr)
+            return 1
+    return 0
+
+
 def case_graph(comm):
     """Collectives captured in a CUDA graph and replayed: the kernels take their
     call number from device memory, so a replay is a new, correctly sequenced call."""

@@ -61,6 +61,12 @@ def test_reduce_scatter_and_all_gather(bins, np_):
 
 
 @needs2
+def test_sharded_gradient_buckets(bins):
+    code, err = run(bins, min(NGPU, 4), "sharded_buckets")
+    assert code == 0, err
+
+
+@needs2
 def test_registered_user_buffers(bins):
     code, err = run(bins, min(NGPU, 4), "registered")
     assert code == 0, err

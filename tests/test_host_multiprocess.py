@@ -50,6 +50,11 @@ def test_reduce_scatter_and_all_gather_on_host_buffers(bins, np_):
     assert code == 0, err
 
 
+def test_sharded_gradient_buckets_on_host_tensors(bins):
+    code, err = run(bins, 3, "sharded_buckets")
+    assert code == 0, err
+
+
 def test_messaging_and_bcast(bins):
     code, err = run(bins, 3, "messaging")
     assert code == 0, err
