@@ -17,6 +17,14 @@
 //                --emulate N              run N ranks inside this one process
 //                                         on one GPU (single cooperative kernel)
 //                --iters K                repeat the allreduce K times
+//                --op allreduce|reduce_scatter|all_gather
+//                                         the collective (default allreduce).  For
+//                                         the halves <bytes> is the full buffer
+//                                         (np blocks, block p belongs to rank p),
+//                                         `i` is the index in the full buffer in
+//                                         both expressions, and <algorithm> is
+//                                         ring on host buffers, auto | nvls |
+//                                         direct on device buffers
 //
 // The exit status is the number of ranks whose check failed, or one of the
 // library's error codes (1 invalid argument, 2 transport, 3 CUDA, 4 not
@@ -47,6 +55,7 @@ struct Args {
   std::string dtype = "int";
   int emulate = 0;
   int iters = 1;
+  std::string op = "allreduce";
   std::string algorithm;
   size_t nbytes = 0;
   std::string init_expr, check_expr;
@@ -56,6 +65,7 @@ struct Args {
   if (!why.empty()) std::cerr << "allreduce_tester: " << why << std::endl;
   std::cerr << "usage: " << prog
             << " [--device cpu|cuda|auto] [--dtype int|float|double] [--emulate N] [--iters K]"
+               " [--op allreduce|reduce_scatter|all_gather]"
                " <algorithm> <bytes> <init expr> <check expr>"
             << std::endl;
   exit(1);
@@ -74,6 +84,7 @@ Args ParseArgs(int argc, char** argv) {
     else if (s == "--dtype") a.dtype = need("--dtype");
     else if (s == "--emulate") a.emulate = atoi(need("--emulate").c_str());
     else if (s == "--iters") a.iters = atoi(need("--iters").c_str());
+    else if (s == "--op") a.op = need("--op");
     else pos.push_back(s);
   }
   if (pos.size() != 4) Usage(argv[0], "four positional arguments expected");
@@ -88,6 +99,7 @@ Args ParseArgs(int argc, char** argv) {
   a.init_expr = pos[2];
   a.check_expr = pos[3];
   if (a.iters < 1) a.iters = 1;
+  if (a.op != "allreduce" && a.op != "reduce_scatter" && a.op != "all_gather") Usage(argv[0], "unknown --op " + a.op);
   return a;
 }
 
@@ -98,28 +110,29 @@ struct Vars {
   }
 };
 
+// `first` = index of buf[0] in the full buffer (the halves work on one block of it).
 template <typename T>
-void Fill(std::vector<T>* buf, const std::string& expr_text, Vars* v) {
+void Fill(std::vector<T>* buf, const std::string& expr_text, Vars* v, size_t first = 0) {
   ibcomm::Expr expr(expr_text, v->Map());
   for (size_t i = 0; i < buf->size(); ++i) {
-    v->i = static_cast<double>(i);
+    v->i = static_cast<double>(first + i);
     (*buf)[i] = static_cast<T>(expr.Eval());
   }
 }
 
 template <typename T>
-std::vector<std::string> Check(const std::vector<T>& buf, const std::string& expr_text, Vars* v) {
+std::vector<std::string> Check(const std::vector<T>& buf, const std::string& expr_text, Vars* v, size_t first = 0) {
   constexpr double eps = 1e-12;
   std::vector<std::string> msgs;
   ibcomm::Expr expr(expr_text, v->Map());
   for (size_t i = 0; i < buf.size(); ++i) {
-    v->i = static_cast<double>(i);
+    v->i = static_cast<double>(first + i);
     const double want = expr.Eval();
     const double got = static_cast<double>(buf[i]);
     if (!(std::fabs(got - want) <= eps)) {
       if (msgs.size() < 1000) {
         std::ostringstream ss;
-        ss << "Error: Element [" << i << "] must be " << want << " but actually is " << got;
+        ss << "Error: Element [" << first + i << "] must be " << want << " but actually is " << got;
         msgs.push_back(ss.str());
       } else {
         msgs.push_back(std::string());
@@ -143,7 +156,30 @@ void RunHost(ibcomm::Communicator* comm, const std::string& algo, const std::vec
   else IBCOMM_FAIL(INVALID_ARGUMENT, "Algorithm '%s' is not available for host buffers.\n", algo.c_str());
 }
 
+// The halves on host buffers (a ring over the host transport).
+template <typename T>
+void RunHostHalf(ibcomm::Communicator* comm, const Args& a, const std::vector<T>& in, std::vector<T>* out, size_t block) {
+  if (a.algorithm != "ring") IBCOMM_FAIL(INVALID_ARGUMENT, "Host reduce-scatter / all-gather run the ring algorithm.\n");
+  if (a.op == "reduce_scatter") comm->ReduceScatter(in.data(), out->data(), block);
+  else comm->AllGather(in.data(), out->data(), block);
+}
+
 #ifdef USE_CUDA
+template <typename T>
+void RunDeviceHalf(ibcomm::Communicator* comm, const Args& a, const std::vector<T>& in, std::vector<T>* out, size_t block) {
+  T *d_in = nullptr, *d_out = nullptr;
+  CUDACHECK(cudaMalloc(&d_in, std::max<size_t>(in.size() * sizeof(T), 16)));
+  CUDACHECK(cudaMalloc(&d_out, std::max<size_t>(out->size() * sizeof(T), 16)));
+  CUDACHECK(cudaMemcpy(d_in, in.data(), in.size() * sizeof(T), cudaMemcpyHostToDevice));
+  ibcomm::CudaAllreduceOptions o;
+  o.algo = ibcomm::AlgoFromName(a.algorithm);
+  if (a.op == "reduce_scatter") comm->ReduceScatterCuda(DTypeOf<T>(), d_in, d_out, block, o);
+  else comm->AllGatherCuda(DTypeOf<T>(), d_in, d_out, block, o);
+  CUDACHECK(cudaMemcpy(out->data(), d_out, out->size() * sizeof(T), cudaMemcpyDeviceToHost));
+  CUDACHECK(cudaFree(d_in));
+  CUDACHECK(cudaFree(d_out));
+}
+
 template <typename T>
 void RunDevice(ibcomm::Communicator* comm, const std::string& algo, const std::vector<T>& in, std::vector<T>* out) {
   T *d_in = nullptr, *d_out = nullptr;
@@ -172,6 +208,8 @@ int RunRanks(const Args& a) {
   const size_t n = a.nbytes / sizeof(T);
 
 #ifdef USE_CUDA
+  if (a.emulate > 0 && a.op != "allreduce")
+    IBCOMM_FAIL(NOT_SUPPORTED, "--emulate runs allreduce only.\n");
   if (a.emulate > 0) {
     // All ranks in this process, one GPU, one cooperative kernel.
     const int np = a.emulate;
@@ -239,20 +277,30 @@ int RunRanks(const Args& a) {
   v.np = benv.world_size;
   v.n = static_cast<double>(n);
   v.nb = static_cast<double>(a.nbytes);
-  std::vector<T> in(n), out(n);
-  Fill(&in, a.init_expr, &v);
+  // The halves: block `rank` of the full buffer is this rank's.
+  const bool half = a.op != "allreduce";
+  const size_t np = static_cast<size_t>(benv.world_size);
+  if (half && (n == 0 || n % np != 0))
+    IBCOMM_FAIL(INVALID_ARGUMENT, "The buffer of %zu elements does not split into %zu equal blocks.\n", n, np);
+  const size_t block = half ? n / np : n;
+  const size_t mine = half ? block * static_cast<size_t>(benv.rank) : 0;
+  const bool rs = a.op == "reduce_scatter", ag = a.op == "all_gather";
+  std::vector<T> in(ag ? block : n), out(rs ? block : n);
+  Fill(&in, a.init_expr, &v, ag ? mine : 0);
 
   for (int k = 0; k < a.iters; ++k) {
     if (use_cuda) {
 #ifdef USE_CUDA
-      RunDevice(&comm, a.algorithm, in, &out);
+      if (half) RunDeviceHalf(&comm, a, in, &out, block);
+      else RunDevice(&comm, a.algorithm, in, &out);
 #endif
     } else {
-      RunHost(&comm, a.algorithm, in, &out);
+      if (half) RunHostHalf(&comm, a, in, &out, block);
+      else RunHost(&comm, a.algorithm, in, &out);
     }
   }
 
-  std::vector<std::string> msgs = Check(out, a.check_expr, &v);
+  std::vector<std::string> msgs = Check(out, a.check_expr, &v, rs ? mine : 0);
   for (int r = 0; r < benv.world_size; ++r) {
     if (r == benv.rank)
       for (const std::string& m : msgs)

@@ -75,3 +75,16 @@ def test_bad_usage(ranks, bins):
 def test_aging(ranks, bins):
     for algo in (RING, RABEN):
         assert check(ranks, bins, 4, algo, "128M", extra=("--iters", "100")) == 0
+
+
+def test_reduce_scatter_and_all_gather(ranks, bins):
+    # The halves through the tester: the buffer size is the full buffer, `i` the
+    # index in it; the closed-form oracle of the allreduce cases applies as is.
+    for np in (1, 2, 3, 5):
+        assert check(ranks, bins, np, RING, np * 1000 * INT, extra=("--op", "reduce_scatter")) == 0
+        assert check(ranks, bins, np, RING, np * 1000 * INT, init="i*3+1", expect="i*3+1", extra=("--op", "all_gather")) == 0
+    assert check(ranks, bins, 4, RING, "8M", extra=("--op", "reduce_scatter")) == 0   # larger than a transport ring
+    assert check(ranks, bins, 4, RING, "8M", init="i", expect="i", extra=("--op", "all_gather")) == 0
+    assert check(ranks, bins, 3, RING, 3 * 16 * INT, init="i", expect="i+1", extra=("--op", "all_gather")) == 3
+    assert check(ranks, bins, 3, RING, 40, extra=("--op", "reduce_scatter")) == INVALID_ARGUMENT  # 10 ints, 3 ranks
+    assert check(ranks, bins, 2, RABEN, 64, extra=("--op", "reduce_scatter")) == INVALID_ARGUMENT
