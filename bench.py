@@ -63,7 +63,8 @@ def parse_args():
                     help="time reduce-scatter and all-gather (fp32, 1 MiB .. 1 GiB per rank in total) against NCCL")
     ap.add_argument("--no-extras", action="store_true", help="skip per-algorithm and NCCL measurements")
     ap.add_argument("--kernel-case", default=None,
-                    choices=["copy", "exec_ring_emu8", "exec_rabenseifner_emu8", "oneshot_emu8"],
+                    choices=["copy", "exec_ring_emu8", "exec_rabenseifner_emu8", "oneshot_emu8", "direct_emu8",
+                             "reduce_scatter_emu8", "all_gather_emu8"],
                     help="run one small single-GPU case of one kernel (for ncu captures) and print its time")
     return ap.parse_args()
 
@@ -330,9 +331,20 @@ def kernel_case(args, comm, dev, time_steps) -> int:
         y = torch.empty_like(x)
         ms = time_steps(lambda: comm.allreduce(x, y, scale=0.5), args.steps, args.warmup)
         moved = 2 * n * 4
+    elif case in ("reduce_scatter_emu8", "all_gather_emu8"):
+        emu = ar.EmuWorld(8)
+        m = 1 << 20  # elements per block: 32 MiB per rank in the full buffers
+        full = [torch.rand(8 * m, device=dev) for _ in range(8)]
+        shard = [torch.rand(m, device=dev) for _ in range(8)]
+        if case == "reduce_scatter_emu8":
+            ms = time_steps(lambda: emu.reduce_scatter(full, shard, scale=0.125), args.steps, args.warmup)
+        else:
+            ms = time_steps(lambda: emu.all_gather(shard, full), args.steps, args.warmup)
+        moved = None
     else:
         emu = ar.EmuWorld(8)
-        algo = {"exec_ring_emu8": "ring", "exec_rabenseifner_emu8": "rabenseifner", "oneshot_emu8": "oneshot"}[case]
+        algo = {"exec_ring_emu8": "ring", "exec_rabenseifner_emu8": "rabenseifner", "oneshot_emu8": "oneshot",
+                "direct_emu8": "direct"}[case]
         m = (16 << 10) if algo == "oneshot" else (8 << 20)  # elements per rank: 64 KiB or 32 MiB
         ins = [torch.rand(m, device=dev) for _ in range(8)]
         outs = [torch.empty(m, device=dev) for _ in range(8)]
