@@ -79,3 +79,47 @@ def test_resnet50_shapes():
     assert len(resnet50_param_shapes()) == 161
     plan = ar.plan_buckets([100, 200, 50, 1000], 4, 1024)
     assert plan == [[0], [1, 2], [3]]
+
+
+def test_python_api_argument_checks():
+    # A world of one rank needs no peers: the host paths and the argument checks run in-process.
+    import torch
+
+    import allreduce_proto_b200 as ar
+    comm = ar.Communicator(1, 0)
+    x = torch.arange(12, dtype=torch.float32)
+    y = torch.empty(12)
+    comm.allreduce(x, y, scale=0.5)
+    assert torch.equal(y, x * 0.5)
+    comm.reduce_scatter(x, y, scale=2.0)          # one rank: one block
+    assert torch.equal(y, x * 2.0)
+    z = torch.empty(12)
+    comm.all_gather(y, z)
+    assert torch.equal(z, y)
+    with pytest.raises(ar.IbcommError) as e:
+        comm.reduce_scatter(x, torch.empty(5))    # not world_size blocks
+    assert e.value.code == ar.INVALID_ARGUMENT
+    with pytest.raises(ar.IbcommError) as e:
+        comm.all_gather(x, torch.empty(12, dtype=torch.float64))
+    assert e.value.code == ar.INVALID_ARGUMENT
+    with pytest.raises(ar.IbcommError):
+        comm.allreduce(x, torch.empty(11))
+    with pytest.raises(ValueError):
+        comm.register(x)                          # registration is for CUDA tensors
+    comm.close()
+
+
+def test_gradient_buckets_without_a_communicator():
+    import torch
+
+    import allreduce_proto_b200 as ar
+    shapes = [(3, 5), (7,), (2, 2, 2)]
+    b = ar.GradientBuckets(shapes, device="cpu", bucket_bytes=64, shardable=True)
+    assert b.num_buckets >= 2 and [tuple(v.shape) for v in b.views] == shapes
+    b.load([torch.full(s, 2.0) for s in shapes])
+    b.allreduce(average=True)                     # no communicator: a plain scale by 1/1
+    assert all(torch.equal(v, torch.full(s, 2.0)) for v, s in zip(b.views, shapes))
+    assert [s.numel() for s in b.reduce_scatter()] == [f.numel() for f in b.flat]
+    b.all_gather()
+    with pytest.raises(ValueError):
+        ar.GradientBuckets(shapes, device="cpu").shards()
