@@ -59,6 +59,9 @@ def parse_args():
     ap.add_argument("--out", default=None)
     ap.add_argument("--write-tuning", default=None, metavar="PATH",
                     help="with --sweep: write the fastest algorithm per size as an IBCOMM_TUNING_FILE table")
+    ap.add_argument("--buckets", action="store_true",
+                    help="time the ResNet-50 gradient-bucket allreduce (25 MiB buckets, fused 1/N, bf16-wire variant) "
+                         "against NCCL on the same buckets")
     ap.add_argument("--rsag", action="store_true",
                     help="time reduce-scatter and all-gather (fp32, 1 MiB .. 1 GiB per rank in total) against NCCL")
     ap.add_argument("--no-extras", action="store_true", help="skip per-algorithm and NCCL measurements")
@@ -185,6 +188,8 @@ def main() -> int:
         return sweep(args, comm, world, rank, dev, time_steps, barrier)
     if args.rsag:
         return rsag_sweep(args, comm, world, rank, dev, time_steps)
+    if args.buckets:
+        return bucket_bench(args, comm, world, rank, dev, time_steps)
     if args.kernel_case:
         return kernel_case(args, comm, dev, time_steps)
 
@@ -352,6 +357,59 @@ def kernel_case(args, comm, dev, time_steps) -> int:
         moved = None
     print(json.dumps({"kernel_case": case, "ms": ms, "steps": args.steps,
                       "gbs_read_plus_write": (moved / (ms / 1e3) / 1e9) if moved else None}))
+    return 0
+
+
+def bucket_bench(args, comm, world, rank, dev, time_steps) -> int:
+    """The data-parallel gradient workload: ResNet-50's 161 gradient tensors (25.6 M fp32 values, ~N(0, 1e-3))
+    in 25 MiB buckets, summed over the ranks with the 1/N scale fused; fp32 on the wire, bf16 on the wire, the
+    sharded pair (reduce-scatter + all-gather), and NCCL (`all_reduce` of every bucket followed by the scale)."""
+    import torch
+    import torch.distributed as dist
+
+    import allreduce_proto_b200 as ar
+    from allreduce_proto_b200.models import resnet50_param_shapes, synthetic_grads
+
+    shapes = [s for _, s in resnet50_param_shapes()]
+    grads = synthetic_grads(dev, seed=rank)
+    steps, warm = max(5, args.steps), max(3, args.warmup)
+    out = {"workload": "resnet50_gradient_buckets", "n_gpus": world, "tensors": len(shapes), "bucket_bytes": 25 << 20}
+    sym = ar.GradientBuckets(shapes, comm=comm, bucket_bytes=25 << 20, shardable=True)
+    sym.load(grads)
+    out["buckets"] = sym.num_buckets
+    out["bytes"] = sym.nbytes
+    t = time_steps(lambda: sym.allreduce(average=True), steps, warm)
+    out["allreduce_fp32_ms"] = t
+    if world > 1:
+        t = time_steps(lambda: sym.allreduce(average=True, wire=torch.bfloat16), steps, warm)
+        out["allreduce_bf16_wire_ms"] = t
+        t = time_steps(lambda: (sym.reduce_scatter(average=True), sym.all_gather()), steps, warm)
+        out["reduce_scatter_plus_all_gather_ms"] = t
+        plain = ar.GradientBuckets(shapes, comm=comm, bucket_bytes=25 << 20, symmetric=False)
+        plain.load(grads)
+        t = time_steps(lambda: plain.allreduce(average=True), steps, warm)
+        out["allreduce_fp32_ordinary_tensors_ms"] = t
+        rids = [comm.register(b) for b in plain.flat]
+        if min(rids) >= 0:
+            t = time_steps(lambda: plain.allreduce(average=True), steps, warm)
+            out["allreduce_fp32_registered_tensors_ms"] = t
+        for rid in rids:
+            if rid >= 0:
+                comm.deregister(rid)
+
+        def nccl_step():
+            for b in plain.flat:
+                dist.all_reduce(b)
+            torch._foreach_mul_(plain.flat, 1.0 / world)
+        t = time_steps(nccl_step, steps, warm)
+        out["nccl_all_reduce_plus_scale_ms"] = t
+    comm.check()
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
     return 0
 
 
