@@ -1,7 +1,8 @@
 // CPU-thread model of the staged two-shot protocols (nvls_kernel.cu,
-// rsag_kernel.cu) and of the one-shot protocol (oneshot_kernel.cu): one thread
-// per (rank, CTA), the pool windows and push slots as plain arrays, the
-// per-CTA cross-rank barriers and flags as release/acquire atomics.  It uses
+// rsag_kernel.cu), of the one-shot protocol (oneshot_kernel.cu) and of the
+// mailbox protocol of device Send/Recv (p2p_sendrecv.cu): one thread per (rank,
+// CTA), the pool windows, push slots and mailboxes as plain arrays, the per-CTA
+// cross-rank barriers, flags and credits as release/acquire atomics.  It uses
 // the kernels' own split (`WindowPart`) and window sizing
 // (`TwoShotWindowElems`), so a split that lets a CTA run ahead into bytes
 // another CTA still needs shows up here: as a wrong sum, and as a data race
@@ -263,7 +264,71 @@ bool RunOneShot(int ws, const std::vector<std::pair<uint64_t, int>>& calls) {
   return bad.load() == 0;
 }
 
+// ---- device Send/Recv: the sender stores piece k of the pair into slot
+// k % slots of its mailbox at the receiver and publishes the cumulative piece
+// count; the receiver copies the piece out and returns a credit; a slot is
+// reused once the piece that held it before has been consumed.
+struct Mailbox {
+  size_t slots, slot_elems;
+  std::vector<int64_t> data;
+  std::atomic<uint64_t> flag{0}, credit{0};
+  Mailbox(size_t s, size_t e) : slots(s), slot_elems(e), data(s * e) {}
+};
+
+void MailboxSend(Mailbox* mb, const std::vector<int64_t>& msg, uint64_t first_piece) {
+  const uint64_t pieces = (msg.size() + mb->slot_elems - 1) / mb->slot_elems;
+  for (uint64_t j = 0; j < pieces; ++j) {
+    const uint64_t k = first_piece + j, off = j * mb->slot_elems;
+    const uint64_t len = std::min<uint64_t>(mb->slot_elems, msg.size() - off);
+    if (k >= mb->slots)
+      while (mb->credit.load(std::memory_order_acquire) < k - mb->slots + 1) std::this_thread::yield();
+    int64_t* dst = mb->data.data() + (k % mb->slots) * mb->slot_elems;
+    for (uint64_t i = 0; i < len; ++i) dst[i] = msg[off + i];
+    mb->flag.store(k + 1, std::memory_order_release);
+  }
+}
+
+void MailboxRecv(Mailbox* mb, std::vector<int64_t>* msg, uint64_t first_piece) {
+  const uint64_t pieces = (msg->size() + mb->slot_elems - 1) / mb->slot_elems;
+  for (uint64_t j = 0; j < pieces; ++j) {
+    const uint64_t k = first_piece + j, off = j * mb->slot_elems;
+    const uint64_t len = std::min<uint64_t>(mb->slot_elems, msg->size() - off);
+    while (mb->flag.load(std::memory_order_acquire) < k + 1) std::this_thread::yield();
+    const int64_t* src = mb->data.data() + (k % mb->slots) * mb->slot_elems;
+    for (uint64_t i = 0; i < len; ++i) (*msg)[off + i] = src[i];
+    mb->credit.store(k + 1, std::memory_order_release);
+  }
+}
+
 }  // namespace
+
+MINI_TEST(MailboxProtocol) {
+  // Messages of many lengths, one after the other, through a mailbox of two slots.
+  Mailbox mb(2, 64);
+  const std::vector<size_t> lengths = {1, 63, 64, 65, 128, 1000, 5, 4096, 129};
+  std::vector<std::vector<int64_t>> got;
+  for (size_t n : lengths) got.emplace_back(n, -1);
+  std::thread sender([&] {
+    uint64_t piece = 0;
+    for (size_t m = 0; m < lengths.size(); ++m) {
+      std::vector<int64_t> msg(lengths[m]);
+      for (size_t i = 0; i < msg.size(); ++i) msg[i] = Value(static_cast<int>(m), i);
+      MailboxSend(&mb, msg, piece);
+      piece += (lengths[m] + mb.slot_elems - 1) / mb.slot_elems;
+    }
+  });
+  std::thread receiver([&] {
+    uint64_t piece = 0;
+    for (size_t m = 0; m < lengths.size(); ++m) {
+      MailboxRecv(&mb, &got[m], piece);
+      piece += (lengths[m] + mb.slot_elems - 1) / mb.slot_elems;
+    }
+  });
+  sender.join();
+  receiver.join();
+  for (size_t m = 0; m < lengths.size(); ++m)
+    for (size_t i = 0; i < got[m].size(); ++i) CHECK_EQ(got[m][i], Value(static_cast<int>(m), i));
+}
 
 MINI_TEST(OneShotParityProtocol) {
   // Calls of changing length and CTA count back to back, no barrier between them.
