@@ -78,6 +78,16 @@ class Communicator:
         except Exception:
             pass
 
+    def __enter__(self) -> "Communicator":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
+    def __repr__(self) -> str:
+        state = "open" if getattr(self, "_h", None) else "closed"
+        return f"Communicator(world_size={self.world_size}, rank={getattr(self, 'rank', None)}, {state})"
+
     # --------------------------------------------------- connection protocol
     def create_queue_pair(self, dest_rank: int) -> tuple[int, int, int]:
         out = (C.c_uint32 * 3)()
