@@ -72,6 +72,7 @@ def _declare(lib) -> None:
         "ibcomm_barrier": [vp],
         "ibcomm_allreduce_host": [vp, i, i, vp, vp, sz],
         "ibcomm_allreduce_cuda": [vp, i, i, vp, vp, sz, dbl, i, vp, i],
+        "ibcomm_choose_algorithm": [sz, i, i, i, i, C.POINTER(C.c_int), C.POINTER(C.c_int)],
         "ibcomm_reduce_scatter_host": [vp, i, vp, vp, sz],
         "ibcomm_all_gather_host": [vp, i, vp, vp, sz],
         "ibcomm_reduce_scatter_cuda": [vp, i, i, vp, vp, sz, dbl, vp, i],

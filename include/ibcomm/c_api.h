@@ -64,6 +64,11 @@ int ibcomm_reduce_scatter_cuda(ibcomm_comm* c, int algo, int dtype, const void* 
 int ibcomm_all_gather_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
                            void* stream, int flags);
 int ibcomm_check(ibcomm_comm* c);
+/* Which algorithm (codes of ibcomm_allreduce_cuda) and how many channels `auto`
+ * takes for a device allreduce of `bytes`: nvls = multicast available and the
+ * type has a switch reduction; mapped = both buffers mapped by the peers
+ * (symmetric or registered memory).  Needs no GPU. */
+int ibcomm_choose_algorithm(size_t bytes, int world_size, int nvls, int mapped, int max_channels, int* algo, int* channels);
 
 /* Peer-mapped (and, with NVSwitch multicast, switch-reducible) device memory.
  * Collective: every rank calls with the same size in the same order. */

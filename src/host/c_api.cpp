@@ -5,11 +5,11 @@
 #include <vector>
 
 #include "ibcomm/communicator.h"
+#include "ibcomm/device_context.h"
 #include "ibcomm/schedule.h"
 #ifdef USE_CUDA
 #include <cuda_runtime.h>
 
-#include "ibcomm/device_context.h"
 #include "ibcomm/emu_world.h"
 #include "kernels.h"
 #endif
@@ -264,6 +264,17 @@ int ibcomm_all_gather_cuda(ibcomm_comm* c, int algo, int dtype, const void* send
 #else
     (void)c; (void)algo; (void)dtype; (void)sendbuf; (void)recvbuf; (void)block_elements; (void)stream; (void)flags;
 #endif
+  });
+}
+
+int ibcomm_choose_algorithm(size_t bytes, int world_size, int nvls, int mapped, int max_channels, int* algo, int* channels) {
+  return Guard([&] {
+    if (world_size < 1 || world_size > ibcomm::kMaxRanks || algo == nullptr || channels == nullptr)
+      IBCOMM_FAIL(INVALID_ARGUMENT, "ibcomm_choose_algorithm: world size 1..%d and two result pointers.\n", ibcomm::kMaxRanks);
+    const ibcomm::TunerChoice c = ibcomm::ChooseAlgorithm(bytes, world_size, nvls != 0, mapped != 0,
+                                                          max_channels > 0 ? max_channels : ibcomm::kMaxChannels);
+    *algo = static_cast<int>(c.algo);
+    *channels = c.channels;
   });
 }
 

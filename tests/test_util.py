@@ -123,3 +123,26 @@ def test_gradient_buckets_without_a_communicator():
     b.all_gather()
     with pytest.raises(ValueError):
         ar.GradientBuckets(shapes, device="cpu").shards()
+
+
+def test_algorithm_table():
+    # The choices `auto` makes (measured on 2, 4 and 8 B200); needs no GPU.
+    from allreduce_proto_b200.utils import choose_algorithm as ca
+    MiB = 1 << 20
+    assert ca(4096, 8)[0] == "oneshot"
+    assert ca(256 * MiB, 8) == ("nvls", 64)                      # symmetric buffers: reduce in the switch
+    assert ca(256 * MiB, 4)[0] == "nvls"
+    assert ca(256 * MiB, 2)[0] == "direct"                       # two ranks: 1.0 S per direction beats 1.5 S
+    assert ca(256 * MiB, 8, nvls=False)[0] == "direct"           # registered buffers, or no multicast
+    assert ca(256 * MiB, 8, mapped=False)[0] == "rabenseifner"   # ordinary buffers, power-of-two ranks
+    assert ca(256 * MiB, 6, mapped=False)[0] == "ring"
+    assert ca(8 * MiB, 8, mapped=False)[0] == "nvls"             # staged through the pool inside the kernel
+    assert ca(256 << 10, 8, mapped=False)[0] == "oneshot"
+    for ws in range(2, 9):
+        for nb in (4, 4096, MiB, 64 * MiB, 1 << 30):
+            for nvls in (False, True):
+                for mapped in (False, True):
+                    algo, ch = ca(nb, ws, nvls=nvls, mapped=mapped)
+                    assert algo in ("oneshot", "nvls", "direct", "ring", "rabenseifner") and 1 <= ch <= 256
+                    assert nvls or algo != "nvls"
+                    assert ca(nb, ws, nvls=nvls, mapped=mapped, max_channels=8)[1] <= 8
