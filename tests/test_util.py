@@ -146,3 +146,27 @@ def test_algorithm_table():
                     assert algo in ("oneshot", "nvls", "direct", "ring", "rabenseifner") and 1 <= ch <= 256
                     assert nvls or algo != "nvls"
                     assert ca(nb, ws, nvls=nvls, mapped=mapped, max_channels=8)[1] <= 8
+
+
+def test_c_headers_compile_as_c99(tmp_path, bins):
+    # The C API is the surface other languages bind to: plain C, no C++ in the headers,
+    # and the library exports what the header declares.
+    import shutil
+    import subprocess
+    from pathlib import Path
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    root = Path(__file__).resolve().parent.parent
+    src = tmp_path / "t.c"
+    src.write_text('#include "ibcomm/c_api.h"\n#include "ibcomm/no_alloc.h"\n#include <stdio.h>\n'
+                   'int main(void) { int a = 0, c = 0;\n'
+                   '  int rc = ibcomm_choose_algorithm((size_t)256 << 20, 8, 1, 1, 0, &a, &c);\n'
+                   '  printf("%d %d %d\\n", rc, a, c); return rc; }\n')
+    lib_dir = root / "allreduce_proto_b200" / "_lib"
+    exe = tmp_path / "t"
+    b = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", f"-I{root / 'include'}", str(src),
+                        f"-L{lib_dir}", "-libcomm", f"-Wl,-rpath,{lib_dir}", "-o", str(exe)],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert b.returncode == 0, b.stdout
+    p = subprocess.run([str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert p.returncode == 0 and p.stdout.split() == ["0", "3", "64"], p.stdout   # nvls, 64 channels
