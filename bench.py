@@ -240,9 +240,14 @@ def main() -> int:
     value = busbw_gbs(nbytes, ms / 1e3, world)
 
     # End to end: pinned host input -> device, allreduce, 4 KiB of the result back.
-    host_in = torch.empty(n, dtype=torch.float32, pin_memory=True)
+    # The pinned buffers are placed on the GPU's own NUMA node (best effort), so that eight ranks do not
+    # pull their inputs through one socket's memory.
+    from allreduce_proto_b200.utils import device_numa_node
+    with device_numa_node(local_rank) as numa_node:
+        host_in = torch.empty(n, dtype=torch.float32, pin_memory=True)
+        host_out = torch.empty(1024, dtype=torch.float32, pin_memory=True)
+        host_in.zero_()
     host_in.copy_(sendbuf)
-    host_out = torch.empty(1024, dtype=torch.float32, pin_memory=True)
 
     def e2e_step():
         sendbuf.copy_(host_in, non_blocking=True)
@@ -252,7 +257,7 @@ def main() -> int:
     e2e_steps = max(3, min(args.steps, 10))
     e2e_ms = time_steps(e2e_step, e2e_steps, 3)
     e2e = {"value": busbw_gbs(nbytes, e2e_ms / 1e3, world), "unit": "GB/s", "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": 4096, "steps": e2e_steps}
+           "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": 4096, "steps": e2e_steps, "host_numa_node": numa_node}
 
     per_algo = {}
     if not args.no_extras:

@@ -170,3 +170,14 @@ def test_c_headers_compile_as_c99(tmp_path, bins):
     assert b.returncode == 0, b.stdout
     p = subprocess.run([str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     assert p.returncode == 0 and p.stdout.split() == ["0", "3", "64"], p.stdout   # nvls, 64 channels
+
+
+def test_numa_helper_is_a_no_op_without_a_gpu():
+    from allreduce_proto_b200.utils import device_numa_node, numa
+    assert numa._parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert numa._parse_cpulist("") == set()
+    import os
+    before = os.sched_getaffinity(0)
+    with device_numa_node(0) as node:
+        assert node is None or isinstance(node, int)
+    assert os.sched_getaffinity(0) == before
