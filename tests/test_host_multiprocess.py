@@ -112,3 +112,18 @@ def test_trace_file_format(bins, tmp_path):
         lines = Path(f"{prefix}_{r}.dat").read_text().splitlines()
         names = [ln.split(",")[0] for ln in lines]
         assert names == ["received", "reduced", "issue_send", "issue_copy_kernel", "issue_redu_kernel", "issue_recv", "other"]
+
+
+@pytest.mark.parametrize("sharded", [False, True])
+def test_data_parallel_example_on_cpu(sharded):
+    # examples/ddp_gradient_buckets.py under torchrun (gloo only for the rendezvous store): real autograd
+    # gradients in buckets, averaged over the library's host transport; the ranks must end with equal weights.
+    example = str(Path(__file__).resolve().parent.parent / "examples" / "ddp_gradient_buckets.py")
+    port = 29650 + (1 if sharded else 0)
+    cmd = ["timeout", "300s", sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "3",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), example, "--device", "cpu", "--steps", "3"]
+    if sharded:
+        cmd.append("--sharded")
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert p.returncode == 0, p.stdout[-3000:]
+    assert p.stdout.count(": OK") == 3, p.stdout[-3000:]
