@@ -90,6 +90,10 @@ class GradientBuckets:
         for p, v in zip(params, self.views):
             p.grad = v
 
+    def zero_(self) -> None:
+        """Clears every bucket (the `zero_grad` of gradients that live here)."""
+        torch._foreach_zero_(self.flat)
+
     def load(self, grads: Sequence[torch.Tensor]) -> None:
         """Copies gradients in (for callers that do not use :meth:`attach`)."""
         torch._foreach_copy_(list(self.views), list(grads))

@@ -77,8 +77,7 @@ def main() -> int:
     for step in range(args.steps):
         x = torch.randn(32, 64, generator=gen).to(device)
         y = torch.randint(0, 10, (32,), generator=gen).to(device)
-        for b in grads.flat:
-            b.zero_()
+        grads.zero_()
         loss = torch.nn.functional.cross_entropy(model(x), y)
         loss.backward()
         if args.sharded:
