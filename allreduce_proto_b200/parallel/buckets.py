@@ -11,7 +11,12 @@ reduce them without staging.
 For sharded optimizers (each rank updates 1/world_size of every bucket) the
 same storage offers the two halves: :meth:`GradientBuckets.reduce_scatter`
 leaves a rank with the reduced block it owns, :meth:`GradientBuckets.all_gather`
-puts the blocks together again, both in place."""
+puts the blocks together again, both in place.
+
+:meth:`GradientBuckets.overlap_with_backward` starts the allreduce of a bucket
+as soon as autograd has produced all of its gradients, on a side stream, so
+that the collectives of the late layers run while the early layers are still
+in their backward pass; :meth:`GradientBuckets.finish` joins them."""
 from __future__ import annotations
 
 from typing import Iterable, Optional, Sequence
@@ -144,3 +149,84 @@ class GradientBuckets:
             return
         for buf, shard in zip(self.flat, mine):
             self.comm.all_gather(shard, buf, algo=algo, sync=sync)
+
+    # ------------------------------------------------ overlap with backward
+    def overlap_with_backward(self, params: Iterable[torch.nn.Parameter], *, average: bool = True, wire=None,
+                              algo: str = "auto") -> None:
+        """Attaches the gradients (see :meth:`attach`) and hooks every parameter: when the last gradient
+        of a bucket has been accumulated, the bucket's allreduce is enqueued.
+
+        Buckets start in descending order (autograd produces the last layers first) and a bucket waits
+        for its turn, so every rank issues the same sequence of collectives.  On CUDA the collectives run
+        on a stream of their own, behind the compute stream's work so far; :meth:`finish` makes the
+        compute stream wait for them (call it before the optimizer reads the gradients).  For gradient
+        accumulation, ``begin_step(communicate=False)`` before a backward pass that should only add up."""
+        params = list(params)
+        self.attach(params)
+        self._ov = {"average": average, "wire": wire, "algo": algo, "stream": None, "communicate": True}
+        self._bucket_of = {i: b for b, idxs in enumerate(self.plan) for i in idxs}
+        # Gradients a bucket has to see before it may go; a bucket without trainable parameters never goes.
+        self._expected = [sum(1 for i in idxs if params[i].requires_grad) for idxs in self.plan]
+        self.remove_hooks()
+        for i, p in enumerate(params):
+            if p.requires_grad:
+                self._handles.append(p.register_post_accumulate_grad_hook(self._make_hook(i)))
+        self.begin_step()
+
+    def begin_step(self, communicate: bool = True) -> None:
+        """Resets the per-step bookkeeping (done by :meth:`finish` as well)."""
+        self._ready = [0] * len(self.plan)
+        self._next = len(self.plan) - 1
+        self._ov["communicate"] = communicate
+
+    def _make_hook(self, index: int):
+        def hook(_param):
+            if self._ov["communicate"]:
+                self._ready[self._bucket_of[index]] += 1
+                self._advance(force=False)
+        return hook
+
+    def _advance(self, force: bool) -> None:
+        # Start every bucket whose turn has come: descending order, no gaps.
+        while self._next >= 0:
+            b = self._next
+            if self._expected[b] > 0:
+                if not force and self._ready[b] < self._expected[b]:
+                    return
+                self._start_bucket(b)
+            self._next -= 1
+
+    def _start_bucket(self, b: int) -> None:
+        buf = self.flat[b]
+        ws = 1 if self.comm is None else self.comm.world_size
+        scale = 1.0 / ws if self._ov["average"] else 1.0
+        if self.comm is None:
+            if scale != 1.0:
+                buf.mul_(scale)
+            return
+        if buf.is_cuda:
+            if self._ov["stream"] is None:
+                self._ov["stream"] = torch.cuda.Stream(device=buf.device)
+            side = self._ov["stream"]
+            side.wait_stream(torch.cuda.current_stream(buf.device))  # this bucket's gradients are complete
+            self.comm.allreduce(buf, algo=self._ov["algo"], scale=scale,
+                                wire=self._ov["wire"] if buf.dtype == torch.float32 else None, stream=side)
+        else:
+            self.comm.allreduce(buf, algo=self._ov["algo"], scale=scale)
+
+    def finish(self) -> None:
+        """Starts the buckets the hooks did not reach (parameters that took no part in this backward
+        pass) and makes the current stream wait for all collectives of the step."""
+        if not hasattr(self, "_ov"):
+            raise ValueError("call overlap_with_backward first")
+        if self._ov["communicate"]:
+            self._advance(force=True)
+        side = self._ov["stream"]
+        if side is not None:
+            torch.cuda.current_stream(side.device).wait_stream(side)
+        self.begin_step(True)
+
+    def remove_hooks(self) -> None:
+        for h in getattr(self, "_handles", []):
+            h.remove()
+        self._handles = []

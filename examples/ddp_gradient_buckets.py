@@ -8,7 +8,8 @@ a synthetic batch, averages them over the ranks through
 `param.grad` are views, the 1/N scale is fused into the reduction) and takes an
 SGD step.  With `--sharded` the averaging is a reduce-scatter, every rank
 updates only its block of the flat parameters, and an all-gather puts the
-parameters together again (the ZeRO-1 pattern).  At the end the ranks compare
+parameters together again (the ZeRO-1 pattern).  With `--overlap` the allreduce
+of a bucket starts from an autograd hook while backward is still running.  At the end the ranks compare
 a checksum of their parameters: they must agree.
 
     python -m torch.distributed.run --nproc-per-node 8 examples/ddp_gradient_buckets.py
@@ -37,6 +38,8 @@ def main() -> int:
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu", choices=["cpu", "cuda"])
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--sharded", action="store_true", help="reduce-scatter + sharded update + all-gather")
+    ap.add_argument("--overlap", action="store_true",
+                    help="start a bucket's allreduce from an autograd hook as soon as its gradients are complete")
     ap.add_argument("--hidden", type=int, default=256)
     args = ap.parse_args()
 
@@ -63,7 +66,10 @@ def main() -> int:
     # Gradients: views into flat buckets (symmetric memory on GPUs, so the collectives run in place).
     grads = ar.GradientBuckets([p.shape for p in params], device=device, comm=comm, bucket_bytes=256 << 10,
                                symmetric=args.device == "cuda", shardable=args.sharded)
-    grads.attach(params)
+    if args.overlap and not args.sharded:
+        grads.overlap_with_backward(params, average=True)
+    else:
+        grads.attach(params)
     weights = None
     if args.sharded:
         # Parameters in the same flat layout, so that block r of a bucket is rank r's share of the weights.
@@ -86,7 +92,10 @@ def main() -> int:
                 w.add_(g, alpha=-lr)          # this rank's block of the weights only
             weights.all_gather(sync=True)
         else:
-            grads.allreduce(average=True, sync=True)
+            if args.overlap:
+                grads.finish()                # the collectives were started during backward
+            else:
+                grads.allreduce(average=True, sync=True)
             with torch.no_grad():
                 for p in params:
                     p.add_(p.grad, alpha=-lr)

@@ -114,15 +114,17 @@ def test_trace_file_format(bins, tmp_path):
         assert names == ["received", "reduced", "issue_send", "issue_copy_kernel", "issue_redu_kernel", "issue_recv", "other"]
 
 
-@pytest.mark.parametrize("sharded", [False, True])
+@pytest.mark.parametrize("sharded", [False, True, "overlap"])
 def test_data_parallel_example_on_cpu(sharded):
     # examples/ddp_gradient_buckets.py under torchrun (gloo only for the rendezvous store): real autograd
     # gradients in buckets, averaged over the library's host transport; the ranks must end with equal weights.
     example = str(Path(__file__).resolve().parent.parent / "examples" / "ddp_gradient_buckets.py")
-    port = 29650 + (1 if sharded else 0)
+    port = 29650 + [False, True, "overlap"].index(sharded)
     cmd = ["timeout", "300s", sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "3",
            "--master-addr", "127.0.0.1", "--master-port", str(port), example, "--device", "cpu", "--steps", "3"]
-    if sharded:
+    if sharded == "overlap":
+        cmd.append("--overlap")
+    elif sharded:
         cmd.append("--sharded")
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     assert p.returncode == 0, p.stdout[-3000:]
