@@ -181,3 +181,17 @@ def test_numa_helper_is_a_no_op_without_a_gpu():
     with device_numa_node(0) as node:
         assert node is None or isinstance(node, int)
     assert os.sched_getaffinity(0) == before
+
+
+def test_bench_reference_arm_prints_unavailable():
+    # The reference cannot be built on this image (no libibverbs, no MPI): the arm says so in one JSON line, exit 0.
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    bench = str(Path(__file__).resolve().parent.parent / "bench.py")
+    p = subprocess.run([sys.executable, bench, "--impl", "reference", "--gpus", "8", "--steps", "5", "--warmup", "3"],
+                       stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    assert p.returncode == 0, p.stderr
+    line = json.loads(p.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
