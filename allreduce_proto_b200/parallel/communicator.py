@@ -153,12 +153,24 @@ class Communicator:
         return comm
 
     @classmethod
-    def from_env(cls, tag: str = "c0", timeout_s: float = 60.0) -> "Communicator":
+    def from_env(cls, tag: str = "c0", timeout_s: float = 60.0, ranks=None) -> "Communicator":
         """Builds a connected communicator from the launcher's environment
         (``IBCOMM_RANK``/``RANK``, ``IBCOMM_WORLD_SIZE``/``WORLD_SIZE``, ``IBCOMM_BOOTSTRAP_DIR``),
-        exchanging descriptors through files like the C++ ``ConnectAll``."""
+        exchanging descriptors through files like the C++ ``ConnectAll``.
+
+        ``ranks``: build the communicator over this subset of the job's ranks only (every member
+        calls with the same list and a ``tag`` not used before); a rank's number in the new
+        communicator is its position in the list.  This is how the survivors of a failed rank form
+        a smaller world and carry on (the collectives of the old communicator have returned
+        TRANSPORT_ERROR by then)."""
         rank = int(os.environ.get("IBCOMM_RANK", os.environ.get("RANK", "0")))
         ws = int(os.environ.get("IBCOMM_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")))
+        if ranks is not None:
+            ranks = [int(r) for r in ranks]
+            if rank not in ranks or len(set(ranks)) != len(ranks) or any(r < 0 or r >= ws for r in ranks):
+                raise IbcommError(_native.INVALID_ARGUMENT, f"rank {rank} builds a communicator over {ranks}")
+            tag = f"{tag}.sub" + "_".join(str(r) for r in ranks)
+            rank, ws = ranks.index(rank), len(ranks)
         comm = cls(ws, rank)
         if ws == 1:
             return comm

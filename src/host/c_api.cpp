@@ -71,6 +71,11 @@ ibcomm::Algo CheckAlgo(int a) {
   return static_cast<ibcomm::Algo>(a);
 }
 
+// A destroyed (or never created) handle is an argument error, not a crash.
+void NeedHandle(const void* h) {
+  if (h == nullptr) IBCOMM_FAIL(INVALID_ARGUMENT, "The handle is null (already destroyed?).\n");
+}
+
 [[maybe_unused]] void NeedCuda() {
 #ifndef USE_CUDA
   IBCOMM_FAIL(NOT_SUPPORTED, "This build of the library has no CUDA support.\n");
@@ -106,27 +111,46 @@ int ibcomm_create(int world_size, ibcomm_comm** out) {
 }
 
 int ibcomm_destroy(ibcomm_comm* c) {
-  return Guard([&] { delete c; });
+  return Guard([&] {
+    NeedHandle(c);
+    delete c;
+  });
 }
 
 int ibcomm_create_queue_pair(ibcomm_comm* c, int dest_rank, uint32_t info_out[3]) {
-  return Guard([&] { ToWords(c->comm.CreateQueuePair(dest_rank), info_out); });
+  return Guard([&] {
+    NeedHandle(c);
+    ToWords(c->comm.CreateQueuePair(dest_rank), info_out);
+  });
 }
 int ibcomm_register_queue_pair(ibcomm_comm* c, int dest_rank, const uint32_t info[3]) {
-  return Guard([&] { c->comm.RegisterQueuePair(dest_rank, FromWords(info)); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.RegisterQueuePair(dest_rank, FromWords(info));
+  });
 }
 int ibcomm_register_process(ibcomm_comm* c, int dest_rank, const uint32_t info[3], uint32_t info_out[3]) {
-  return Guard([&] { ToWords(c->comm.RegisterProcess(dest_rank, FromWords(info)), info_out); });
+  return Guard([&] {
+    NeedHandle(c);
+    ToWords(c->comm.RegisterProcess(dest_rank, FromWords(info)), info_out);
+  });
 }
 int ibcomm_register_myself(ibcomm_comm* c, int my_rank) {
-  return Guard([&] { c->comm.RegisterMyself(my_rank); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.RegisterMyself(my_rank);
+  });
 }
 int ibcomm_set_timeout_ms(ibcomm_comm* c, int ms) {
-  return Guard([&] { c->comm.SetTimeoutMs(ms); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.SetTimeoutMs(ms);
+  });
 }
 
 int ibcomm_set_max_channels(ibcomm_comm* c, int channels) {
   return Guard([&] {
+    NeedHandle(c);
     NeedCuda();
 #ifdef USE_CUDA
     c->comm.PrepareMemoryPool();
@@ -138,32 +162,57 @@ int ibcomm_set_max_channels(ibcomm_comm* c, int channels) {
 }
 
 int ibcomm_send(ibcomm_comm* c, int dest_rank, const void* buf, size_t len, int blocking) {
-  return Guard([&] { c->comm.Send(dest_rank, buf, len, blocking != 0); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.Send(dest_rank, buf, len, blocking != 0);
+  });
 }
 int ibcomm_recv(ibcomm_comm* c, int src_rank, void* buf, size_t len, int blocking) {
-  return Guard([&] { c->comm.Recv(src_rank, buf, len, blocking != 0); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.Recv(src_rank, buf, len, blocking != 0);
+  });
 }
 int ibcomm_send_poll(ibcomm_comm* c, int dest_rank, int* done) {
-  return Guard([&] { *done = c->comm.SendPoll(dest_rank) ? 1 : 0; });
+  return Guard([&] {
+    NeedHandle(c);
+    *done = c->comm.SendPoll(dest_rank) ? 1 : 0;
+  });
 }
 int ibcomm_recv_poll(ibcomm_comm* c, int src_rank, int* done) {
-  return Guard([&] { *done = c->comm.RecvPoll(src_rank) ? 1 : 0; });
+  return Guard([&] {
+    NeedHandle(c);
+    *done = c->comm.RecvPoll(src_rank) ? 1 : 0;
+  });
 }
 int ibcomm_send_wait(ibcomm_comm* c, int dest_rank) {
-  return Guard([&] { c->comm.SendWait(dest_rank); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.SendWait(dest_rank);
+  });
 }
 int ibcomm_recv_wait(ibcomm_comm* c, int src_rank) {
-  return Guard([&] { c->comm.RecvWait(src_rank); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.RecvWait(src_rank);
+  });
 }
 int ibcomm_bcast(ibcomm_comm* c, void* buf, size_t len, int root) {
-  return Guard([&] { c->comm.Bcast(buf, len, root); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.Bcast(buf, len, root);
+  });
 }
 int ibcomm_barrier(ibcomm_comm* c) {
-  return Guard([&] { c->comm.Barrier(); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.Barrier();
+  });
 }
 
 int ibcomm_allreduce_host(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t n) {
   return Guard([&] {
+    NeedHandle(c);
     const ibcomm::Algo a = CheckAlgo(algo);
     const ibcomm::DType d = CheckDType(dtype);
     if (a != ibcomm::Algo::kRing && a != ibcomm::Algo::kRabenseifner)
@@ -216,6 +265,7 @@ int ibcomm_all_gather_host(ibcomm_comm* c, int dtype, const void* sendbuf, void*
 int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t n, double scale,
                           int wire_dtype, void* stream, int flags) {
   return Guard([&] {
+    NeedHandle(c);
     NeedCuda();
 #ifdef USE_CUDA
     ibcomm::CudaAllreduceOptions o;
@@ -235,6 +285,7 @@ int ibcomm_allreduce_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendb
 int ibcomm_reduce_scatter_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
                                double scale, void* stream, int flags) {
   return Guard([&] {
+    NeedHandle(c);
     NeedCuda();
 #ifdef USE_CUDA
     ibcomm::CudaAllreduceOptions o;
@@ -253,6 +304,7 @@ int ibcomm_reduce_scatter_cuda(ibcomm_comm* c, int algo, int dtype, const void* 
 int ibcomm_all_gather_cuda(ibcomm_comm* c, int algo, int dtype, const void* sendbuf, void* recvbuf, size_t block_elements,
                            void* stream, int flags) {
   return Guard([&] {
+    NeedHandle(c);
     NeedCuda();
 #ifdef USE_CUDA
     ibcomm::CudaAllreduceOptions o;
@@ -280,6 +332,7 @@ int ibcomm_choose_algorithm(size_t bytes, int world_size, int nvls, int mapped, 
 
 int ibcomm_check(ibcomm_comm* c) {
   return Guard([&] {
+    NeedHandle(c);
 #ifdef USE_CUDA
     if (c->comm.device() != nullptr) ibcomm::DeviceContextCheck(c->comm.device());
 #else
@@ -290,6 +343,7 @@ int ibcomm_check(ibcomm_comm* c) {
 
 int ibcomm_symmetric_alloc(ibcomm_comm* c, size_t bytes, void** out) {
   return Guard([&] {
+    NeedHandle(c);
     NeedCuda();
 #ifdef USE_CUDA
     *out = ibcomm::DeviceContextSymmetricAlloc(&c->comm, bytes);
@@ -301,6 +355,7 @@ int ibcomm_symmetric_alloc(ibcomm_comm* c, size_t bytes, void** out) {
 
 int ibcomm_symmetric_free(ibcomm_comm* c, void* ptr) {
   return Guard([&] {
+    NeedHandle(c);
     NeedCuda();
 #ifdef USE_CUDA
     ibcomm::DeviceContextSymmetricFree(&c->comm, ptr);
@@ -312,6 +367,7 @@ int ibcomm_symmetric_free(ibcomm_comm* c, void* ptr) {
 
 int ibcomm_register_buffer(ibcomm_comm* c, void* ptr, size_t bytes, int* id) {
   return Guard([&] {
+    NeedHandle(c);
     NeedCuda();
 #ifdef USE_CUDA
     *id = ibcomm::DeviceContextRegisterBuffer(&c->comm, ptr, bytes);
@@ -323,6 +379,7 @@ int ibcomm_register_buffer(ibcomm_comm* c, void* ptr, size_t bytes, int* id) {
 
 int ibcomm_deregister_buffer(ibcomm_comm* c, int id) {
   return Guard([&] {
+    NeedHandle(c);
     NeedCuda();
 #ifdef USE_CUDA
     ibcomm::DeviceContextDeregisterBuffer(&c->comm, id);
@@ -334,6 +391,7 @@ int ibcomm_deregister_buffer(ibcomm_comm* c, int id) {
 
 int ibcomm_get_device_info(ibcomm_comm* c, int connect, ibcomm_device_info* out) {
   return Guard([&] {
+    NeedHandle(c);
     NeedCuda();
 #ifdef USE_CUDA
     c->comm.PrepareMemoryPool();
@@ -362,10 +420,16 @@ int ibcomm_get_device_info(ibcomm_comm* c, int connect, ibcomm_device_info* out)
 }
 
 int ibcomm_set_timer_base(ibcomm_comm* c) {
-  return Guard([&] { c->comm.SetTimerBase(); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.SetTimerBase();
+  });
 }
 int ibcomm_dump_trace(ibcomm_comm* c) {
-  return Guard([&] { c->comm.DumpTrace(); });
+  return Guard([&] {
+    NeedHandle(c);
+    c->comm.DumpTrace();
+  });
 }
 
 int ibcomm_emu_create(int num_ranks, size_t pool_bytes, size_t work_bytes, ibcomm_emu** out) {
@@ -380,12 +444,16 @@ int ibcomm_emu_create(int num_ranks, size_t pool_bytes, size_t work_bytes, ibcom
 }
 
 int ibcomm_emu_destroy(ibcomm_emu* w) {
-  return Guard([&] { delete w; });
+  return Guard([&] {
+    NeedHandle(w);
+    delete w;
+  });
 }
 
 int ibcomm_emu_allreduce(ibcomm_emu* w, int algo, int dtype, const void* const* sendbufs, void* const* recvbufs, size_t n,
                          double scale, int wire_dtype, int channels, void* stream, int async) {
   return Guard([&] {
+    NeedHandle(w);
     NeedCuda();
 #ifdef USE_CUDA
     const int ws = w->world.num_ranks();
@@ -401,6 +469,7 @@ int ibcomm_emu_allreduce(ibcomm_emu* w, int algo, int dtype, const void* const* 
 int ibcomm_emu_rsag(ibcomm_emu* w, int all_gather, int dtype, const void* const* sendbufs, void* const* recvbufs,
                     size_t block_elements, double scale, int channels, void* stream, int async) {
   return Guard([&] {
+    NeedHandle(w);
     NeedCuda();
 #ifdef USE_CUDA
     const int ws = w->world.num_ranks();
@@ -415,6 +484,7 @@ int ibcomm_emu_rsag(ibcomm_emu* w, int all_gather, int dtype, const void* const*
 
 int ibcomm_emu_set_timeout_ms(ibcomm_emu* w, int ms) {
   return Guard([&] {
+    NeedHandle(w);
 #ifdef USE_CUDA
     w->world.SetTimeoutMs(ms);
 #else
@@ -434,6 +504,7 @@ int ibcomm_emu_last_channels(ibcomm_emu* w) {
 
 int ibcomm_emu_set_bad_program_rank(ibcomm_emu* w, int rank) {
   return Guard([&] {
+    NeedHandle(w);
 #ifdef USE_CUDA
     w->world.SetBadProgramRank(rank);
 #else
@@ -444,6 +515,7 @@ int ibcomm_emu_set_bad_program_rank(ibcomm_emu* w, int rank) {
 
 int ibcomm_emu_set_silent_rank(ibcomm_emu* w, int rank) {
   return Guard([&] {
+    NeedHandle(w);
 #ifdef USE_CUDA
     w->world.SetSilentRank(rank);
 #else
@@ -454,6 +526,7 @@ int ibcomm_emu_set_silent_rank(ibcomm_emu* w, int rank) {
 
 int ibcomm_emu_set_direct_staging(ibcomm_emu* w, int on) {
   return Guard([&] {
+    NeedHandle(w);
 #ifdef USE_CUDA
     w->world.SetDirectStaging(on);
 #else
@@ -464,6 +537,7 @@ int ibcomm_emu_set_direct_staging(ibcomm_emu* w, int on) {
 
 int ibcomm_emu_last_status(ibcomm_emu* w, ibcomm_status_report* out) {
   return Guard([&] {
+    NeedHandle(w);
 #ifdef USE_CUDA
     ibcomm::DeviceStatus st;
     memset(&st, 0, sizeof(st));

@@ -130,6 +130,35 @@ def case_peer_exit(comm):
     return 1
 
 
+def case_shrink(comm):
+    """The last rank leaves between steps; the others see the transport error on their next
+    collective, form a smaller communicator and carry on."""
+    x = torch.full((1 << 12,), float(RANK + 1))
+    comm.allreduce(x, algo="ring")                       # step 1: everybody
+    if not torch.allclose(x, torch.full_like(x, WS * (WS + 1) / 2)):
+        return 1
+    comm.barrier()
+    if RANK == WS - 1:
+        comm.close()
+        return 0                                          # leaves with nothing in flight
+    comm.set_timeout_ms(1500)
+    y = torch.ones(1 << 12)
+    try:
+        comm.allreduce(y, algo="ring")                   # step 2: one rank is missing
+        return 1
+    except ar.IbcommError as e:
+        if e.code != ar.TRANSPORT_ERROR:
+            return 1
+    comm.close()
+    survivors = list(range(WS - 1))
+    small = ar.Communicator.from_env(tag="after_failure", ranks=survivors)
+    z = torch.full((1 << 12,), float(RANK + 1))
+    small.allreduce(z, algo="rabenseifner")
+    ok = small.world_size == WS - 1 and torch.allclose(z, torch.full_like(z, (WS - 1) * WS / 2))
+    small.close()
+    return 0 if ok else 1
+
+
 def case_trace(comm):
     comm.set_timer_base()
     x = torch.ones(1 << 12)
@@ -142,7 +171,7 @@ def main():
     case = sys.argv[1]
     comm = ar.Communicator.from_env()
     rc = globals()[f"case_{case}"](comm)
-    if case != "peer_exit":
+    if case not in ("peer_exit", "shrink"):   # these end with ranks that are gone
         comm.barrier()
     comm.close()
     return rc

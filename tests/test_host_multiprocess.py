@@ -67,6 +67,13 @@ def test_peer_that_exits_is_detected(bins):
     assert time.time() - t0 < 60
 
 
+def test_survivors_form_a_smaller_communicator(bins):
+    # Elastic shrink on the host: a rank leaves between steps, the others get the transport
+    # error, build a communicator over the survivors and finish the work.
+    code, err = run(bins, 4, "shrink", env={"IBCOMM_RUN_GRACE_MS": "30000"})
+    assert code == 0, err
+
+
 def test_rank_that_never_joins(bins, tmp_path):
     """Bootstrap gives up with the transport error code when a rank is missing."""
     env = dict(os.environ, IBCOMM_RANK="0", IBCOMM_WORLD_SIZE="2", IBCOMM_BOOTSTRAP_DIR=str(tmp_path))

@@ -195,3 +195,16 @@ def test_bench_reference_arm_prints_unavailable():
     assert p.returncode == 0, p.stderr
     line = json.loads(p.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
+
+
+def test_closed_communicator_raises_instead_of_crashing():
+    import torch
+
+    import allreduce_proto_b200 as ar
+    comm = ar.Communicator(1, 0)
+    comm.close()
+    comm.close()  # closing twice is fine
+    for call in (comm.barrier, lambda: comm.allreduce(torch.ones(4)), lambda: comm.set_timeout_ms(5)):
+        with pytest.raises(ar.IbcommError) as e:
+            call()
+        assert e.value.code == ar.INVALID_ARGUMENT
