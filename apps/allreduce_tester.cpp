@@ -17,6 +17,9 @@
 //                --emulate N              run N ranks inside this one process
 //                                         on one GPU (single cooperative kernel)
 //                --iters K                repeat the allreduce K times
+//                --ranks a,b,...          only the listed ranks of the job take
+//                                         part (the others exit with status 0);
+//                                         p and np then refer to the subset
 //                --op allreduce|reduce_scatter|all_gather
 //                                         the collective (default allreduce).  For
 //                                         the halves <bytes> is the full buffer
@@ -56,6 +59,7 @@ struct Args {
   int emulate = 0;
   int iters = 1;
   std::string op = "allreduce";
+  std::vector<int> ranks;  // empty = every rank of the job
   std::string algorithm;
   size_t nbytes = 0;
   std::string init_expr, check_expr;
@@ -85,6 +89,11 @@ Args ParseArgs(int argc, char** argv) {
     else if (s == "--emulate") a.emulate = atoi(need("--emulate").c_str());
     else if (s == "--iters") a.iters = atoi(need("--iters").c_str());
     else if (s == "--op") a.op = need("--op");
+    else if (s == "--ranks") {
+      std::stringstream ss(need("--ranks"));
+      std::string item;
+      while (std::getline(ss, item, ',')) a.ranks.push_back(atoi(item.c_str()));
+    }
     else pos.push_back(s);
   }
   if (pos.size() != 4) Usage(argv[0], "four positional arguments expected");
@@ -269,8 +278,13 @@ int RunRanks(const Args& a) {
   if (a.device == "cuda") IBCOMM_FAIL(NOT_SUPPORTED, "This tester was built without CUDA.\n");
 #endif
 
+  std::string tag = "c0";
+  if (!a.ranks.empty()) {
+    if (std::find(a.ranks.begin(), a.ranks.end(), benv.rank) == a.ranks.end()) return 0;  // not a member
+    benv = ibcomm::SubsetEnv(benv, a.ranks, &tag);
+  }
   ibcomm::Communicator comm(benv.world_size);
-  ibcomm::ConnectAll(&comm, benv);
+  ibcomm::ConnectAll(&comm, benv, tag);
 
   Vars v;
   v.p = benv.rank;

@@ -13,6 +13,7 @@
 #pragma once
 
 #include <string>
+#include <vector>
 
 #include "ibcomm/communicator.h"
 
@@ -31,6 +32,15 @@ BootstrapEnv ReadBootstrapEnv();
 // `tag` separates several communicators that share one directory.
 void ConnectAll(Communicator* comm, const BootstrapEnv& env, const std::string& tag = "c0",
                 int timeout_ms = 60000);
+
+// Environment of a communicator over a subset of the job's ranks: a member's
+// rank is its position in `ranks`, the world size is the size of the list, and
+// `*tag` gets a suffix naming the subset so that the rendezvous files do not
+// collide with those of other communicators.  Every member calls with the
+// same list.  This is how the survivors of a failed rank form a smaller world
+// (the old communicator's collectives have returned TRANSPORT_ERROR by then).
+// INVALID_ARGUMENT when this rank is not in the list or the list is malformed.
+BootstrapEnv SubsetEnv(const BootstrapEnv& env, const std::vector<int>& ranks, std::string* tag);
 
 // Sum of one integer over all ranks, through rank 0 (tester exit status).
 long long SumOverRanks(Communicator* comm, long long value);

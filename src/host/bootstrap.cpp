@@ -82,6 +82,24 @@ void ConnectAll(Communicator* comm, const BootstrapEnv& env, const std::string& 
   comm->Barrier();
 }
 
+BootstrapEnv SubsetEnv(const BootstrapEnv& env, const std::vector<int>& ranks, std::string* tag) {
+  BootstrapEnv sub = env;
+  sub.rank = -1;
+  std::string suffix = ".sub";
+  for (size_t i = 0; i < ranks.size(); ++i) {
+    const int r = ranks[i];
+    if (r < 0 || r >= env.world_size) IBCOMM_FAIL(INVALID_ARGUMENT, "SubsetEnv: rank %d is not a rank of this job (%d ranks).\n", r, env.world_size);
+    for (size_t j = 0; j < i; ++j)
+      if (ranks[j] == r) IBCOMM_FAIL(INVALID_ARGUMENT, "SubsetEnv: rank %d is listed twice.\n", r);
+    if (r == env.rank) sub.rank = static_cast<int>(i);
+    suffix += (i == 0 ? "" : "_") + std::to_string(r);
+  }
+  if (sub.rank < 0) IBCOMM_FAIL(INVALID_ARGUMENT, "SubsetEnv: rank %d is not in the list.\n", env.rank);
+  sub.world_size = static_cast<int>(ranks.size());
+  if (tag != nullptr) *tag += suffix;
+  return sub;
+}
+
 long long SumOverRanks(Communicator* comm, long long value) {
   const int ws = static_cast<int>(comm->world_size());
   if (ws == 1) return value;

@@ -88,3 +88,12 @@ def test_reduce_scatter_and_all_gather(ranks, bins):
     assert check(ranks, bins, 3, RING, 3 * 16 * INT, init="i", expect="i+1", extra=("--op", "all_gather")) == 3
     assert check(ranks, bins, 3, RING, 40, extra=("--op", "reduce_scatter")) == INVALID_ARGUMENT  # 10 ints, 3 ranks
     assert check(ranks, bins, 2, RABEN, 64, extra=("--op", "reduce_scatter")) == INVALID_ARGUMENT
+
+
+def test_subset_of_the_ranks(ranks, bins):
+    # A communicator over some of the job's ranks (what survivors of a failed rank build): p and np
+    # refer to the subset, the other ranks do not take part.
+    assert check(ranks, bins, 4, RING, 4000, extra=("--ranks", "0,2,3")) == 0
+    assert check(ranks, bins, 4, RABEN, 4000, init="p+1", expect="3", extra=("--ranks", "3,1")) == 0
+    assert check(ranks, bins, 5, RING, 4000, init="np", expect="np*np", extra=("--ranks", "4,0,1,3")) == 0
+    assert check(ranks, bins, 2, RING, 4000, init="1", expect="1", extra=("--ranks", "0,5")) == INVALID_ARGUMENT
