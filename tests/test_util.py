@@ -208,3 +208,38 @@ def test_closed_communicator_raises_instead_of_crashing():
         with pytest.raises(ar.IbcommError) as e:
             call()
         assert e.value.code == ar.INVALID_ARGUMENT
+
+
+def test_partitioner_properties():
+    # Property test (hypothesis): whatever the length, element size, world size and chunk size, the chunks
+    # tile [0, n) without gaps or overlaps, there are at least as many chunks as ranks want, blocks of
+    # chunk ids are contiguous and cover every chunk once.
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=300, deadline=None)
+    @given(n=st.integers(1, 1 << 22), esize=st.sampled_from([1, 2, 4, 8]), ws=st.integers(1, 8),
+           chunk_elems=st.integers(0, 1 << 16))
+    def check(n, esize, ws, chunk_elems):
+        chunk_bytes = chunk_elems * esize
+        try:
+            r = utils.split_buffer(n, esize, ws, chunk_bytes)
+        except ar.IbcommError as e:
+            assert e.code in (ar.INVALID_ARGUMENT, ar.NOT_SUPPORTED)
+            if n < ws:
+                assert e.code == ar.NOT_SUPPORTED
+            return
+        assert n >= ws
+        assert r[0][0] == 0 and r[-1][1] == n
+        assert all(b < e for b, e in r)
+        assert all(r[i][0] == r[i - 1][1] for i in range(1, len(r)))
+        if chunk_bytes > 0:
+            assert all(e - b <= chunk_elems for b, e in r)
+            assert len(r) >= 2 * ws or ws == 1
+        else:
+            assert len(r) <= 4 * ws
+        owned = [utils.rank_to_chunk(len(r), ws, k) for k in range(ws)]
+        flat = [c for o in owned for c in o]
+        assert flat == list(range(len(r)))
+        assert max(len(o) for o in owned) - min(len(o) for o in owned) <= 1
+
+    check()
