@@ -138,6 +138,27 @@ MINI_TEST(RingOwnershipAfterReduceScatter) {
   }
 }
 
+MINI_TEST(RandomConfigurations) {
+  // Seeded fuzz over world size, length, channels, staging size, in-place and scale: the directed cases
+  // above came from bugs that only some combinations showed.
+  std::mt19937 gen(20240607u);
+  auto pick = [&](size_t lo, size_t hi) { return lo + static_cast<size_t>(gen() % (hi - lo + 1)); };
+  for (int it = 0; it < 250; ++it) {
+    const Algo a = (gen() & 1u) ? Algo::kRing : Algo::kRabenseifner;
+    const int ws = static_cast<int>(pick(2, 8));
+    const size_t n = (gen() % 4 == 0) ? pick(static_cast<size_t>(ws), 64) : pick(static_cast<size_t>(ws), 150000);
+    const int nch = static_cast<int>(pick(1, 6));
+    const size_t stage = pick(40000, size_t(1) << 20);
+    const size_t maxc = std::max<size_t>(128, stage / (static_cast<size_t>(NumRegions(a, ws)) * 4) / 128 * 128);
+    const bool in_place = (gen() & 1u) != 0;
+    bool ok;
+    if (gen() % 3 == 0) ok = RunCase<double>(a, ws, n, 0, stage, nch, in_place, 0.5, maxc);
+    else ok = RunCase<int>(a, ws, n, 0, stage, nch, in_place, 1.0, maxc);
+    if (!ok) fprintf(stderr, "failing configuration: %s ws=%d n=%zu nch=%d stage=%zu in_place=%d\n", AlgoName(a), ws, n, nch, stage, in_place ? 1 : 0);
+    CHECK_TRUE(ok);
+  }
+}
+
 MINI_TEST(ValidateProgramFindsOutOfBoundsOps) {
   // Every program the builders cut passes; an op pushed out of the message,
   // out of its slot or out of the staging area is named.
