@@ -383,4 +383,22 @@ MINI_TEST(StagedReduceScatterAllGatherProtocol) {
         CHECK_TRUE(RunRsAg(ws, ncta, block_units, 64));
 }
 
+MINI_TEST(RandomStagedConfigurations) {
+  // Seeded fuzz over world size, CTAs, message length and window capacity.
+  uint64_t state = 88172645463325252ull;
+  auto next = [&] {
+    state ^= state << 13;
+    state ^= state >> 7;
+    state ^= state << 17;
+    return state;
+  };
+  auto pick = [&](uint64_t lo, uint64_t hi) { return lo + next() % (hi - lo + 1); };
+  for (int it = 0; it < 200; ++it) {
+    const int ws = static_cast<int>(pick(2, 5)), ncta = static_cast<int>(pick(1, 5));
+    const uint64_t cap = pick(4, 40) * 16;  // a whole number of vectors
+    CHECK_TRUE(RunAllreduce(ws, ncta, pick(static_cast<uint64_t>(ws), 6 * cap), cap));
+    CHECK_TRUE(RunRsAg(ws, ncta, pick(1, 6 * cap / kVec), cap / kVec));
+  }
+}
+
 int main(int argc, char** argv) { return mini::RunAll(argc > 1 ? argv[1] : nullptr); }
