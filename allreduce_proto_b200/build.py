@@ -52,6 +52,7 @@ CUDA_SOURCES = [
     "src/cuda/nvls_kernel.cu",
     "src/cuda/oneshot_kernel.cu",
     "src/cuda/rsag_kernel.cu",
+    "src/cuda/hybrid_kernel.cu",
     "src/cuda/copy_kernel.cu",
     "src/cuda/p2p_sendrecv.cu",
     "src/cuda/no_alloc.cu",

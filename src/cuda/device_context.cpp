@@ -6,6 +6,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <deque>
@@ -164,6 +165,7 @@ class DeviceContext {
   uint64_t calls_ = 0;
   uint64_t kernel_launches_ = 0;
   int last_algo_ = 0, last_channels_ = 0;
+  int hybrid_channels_ = 0;  // CTAs of the hybrid two-shot kernel when the last call ran it
   int max_channels_ = env::kDefaultNumCudaStream;
   std::vector<P2pState> p2p_;
   std::vector<std::unique_ptr<SymmetricAlloc>> symm_;
@@ -699,6 +701,37 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   }
   p.window_elems = (zin && zout) ? n : window_elems;
   if (p.window_elems == 0) p.window_elems = 1;
+  // Opt-in experiment: IBCOMM_NVLS_HYBRID = percentage (1..90) of a zero-copy switch allreduce that runs
+  // direct, concurrently, in the same kernel; IBCOMM_NVLS_HYBRID_CTAS = "switch,direct" CTAs (48,96).
+  if (multimem && zin && zout && ws_ > 1) {
+    static const int direct_percent = [] {
+      const char* s = getenv("IBCOMM_NVLS_HYBRID");
+      const int v = s != nullptr ? atoi(s) : 0;
+      return (v >= 1 && v <= 90) ? v : 0;
+    }();
+    if (direct_percent > 0 && bytes >= (8u << 20)) {
+      int nvls_ctas = 48, direct_ctas = 96;
+      if (const char* s = getenv("IBCOMM_NVLS_HYBRID_CTAS")) {
+        int a = 0, b = 0;
+        if (sscanf(s, "%d,%d", &a, &b) == 2 && a >= 1 && b >= 1 && a + b <= 148) {
+          nvls_ctas = a;
+          direct_ctas = b;
+        }
+      }
+      HybridParams h;
+      memset(&h, 0, sizeof(h));
+      h.base = p;
+      h.nvls_ctas = nvls_ctas;
+      const uint64_t nvec = bytes / 16;
+      h.split_vec = nvec * static_cast<uint64_t>(100 - direct_percent) / 100;
+      IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+      CUDACHECK(LaunchHybridKernel(h, nvls_ctas + direct_ctas, stream));
+      ++kernel_launches_;
+      IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+      hybrid_channels_ = nvls_ctas + direct_ctas;
+      return;
+    }
+  }
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
   CUDACHECK(LaunchNvlsKernel(p, nullptr, 1, channels, stream));
   ++kernel_launches_;
@@ -775,7 +808,8 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
   }
   MarkIssued(stream);
   last_algo_ = static_cast<int>(algo);
-  last_channels_ = channels;
+  last_channels_ = hybrid_channels_ > 0 ? hybrid_channels_ : channels;
+  hybrid_channels_ = 0;
   Finish(stream, opts.async);
 }
 

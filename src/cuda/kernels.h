@@ -67,6 +67,17 @@ struct NvlsParams {
 };
 cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
 
+// Hybrid two-shot (hybrid_kernel.cu): zero-copy symmetric buffers; CTAs
+// [0, nvls_ctas) reduce 16-byte vectors [0, split_vec) in the switch, the other
+// CTAs of the grid reduce the rest with peer loads and stores.
+struct HybridParams {
+  NvlsParams base;
+  int32_t nvls_ctas;
+  int32_t pad_;
+  uint64_t split_vec;
+};
+cudaError_t LaunchHybridKernel(const HybridParams& h, int blocks, cudaStream_t stream);
+
 // ---- reduce-scatter / all-gather (the halves of the two-shot allreduce) ----
 enum RsAgMode : int32_t { kRsAgReduceScatter = 1, kRsAgAllGather = 2 };
 struct RsAgParams {

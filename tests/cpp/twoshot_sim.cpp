@@ -128,6 +128,61 @@ bool RunAllreduce(int ws, int ncta, uint64_t n, uint64_t cap_elems) {
   return bad.load() == 0;
 }
 
+// HybridKernel (hybrid_kernel.cu): zero-copy buffers; CTAs [0, na) own vectors [0, split), the other CTAs
+// [split, nvec); rank r reduces shard r of its role's part and writes it to every rank.  (The switch
+// role is modelled as the same sum; what is checked is the split and the barrier placement.)
+void HybridCta(World* w, uint64_t seq, int rank, int block, int na, std::vector<std::vector<int64_t>>* bufs_in,
+               std::vector<std::vector<int64_t>>* bufs_out, uint64_t n, uint64_t split_vec) {
+  const int ws = w->ws, grid = w->ncta;
+  const bool switch_role = block < na;
+  const int cta = switch_role ? block : block - na, ncta = switch_role ? na : grid - na;
+  const uint64_t nvec = n / kVec, tail0 = nvec * kVec, split = std::min(split_vec, nvec);
+  uint64_t sb, se, b, e;
+  SubRange(switch_role ? 0 : split, switch_role ? split : nvec, rank, ws, &sb, &se);
+  SubRange(sb, se, cta, ncta, &b, &e);
+  w->Barrier(rank, block, (seq << 32) | 1);
+  for (uint64_t i = b * kVec; i < e * kVec; ++i) {
+    int64_t acc = 0;
+    for (int q = 0; q < ws; ++q) acc += (*bufs_in)[q][i];
+    for (int q = 0; q < ws; ++q) (*bufs_out)[q][i] = acc;
+  }
+  std::vector<int64_t> tail_acc;
+  const bool has_tail = !switch_role && cta == 0;
+  if (has_tail)
+    for (uint64_t i = tail0; i < n; ++i) {
+      int64_t acc = 0;
+      for (int q = 0; q < ws; ++q) acc += (*bufs_in)[q][i];
+      tail_acc.push_back(acc);
+    }
+  w->Barrier(rank, block, (seq << 32) | 2);
+  if (has_tail)
+    for (uint64_t i = tail0; i < n; ++i) (*bufs_out)[rank][i] = tail_acc[i - tail0];
+}
+
+bool RunHybrid(int ws, int na, int nb, uint64_t n, uint64_t split_vec) {
+  World w(ws, na + nb, kVec);
+  std::vector<std::vector<int64_t>> in(ws, std::vector<int64_t>(n)), out(ws, std::vector<int64_t>(n, -1));
+  for (int r = 0; r < ws; ++r)
+    for (uint64_t i = 0; i < n; ++i) in[r][i] = Value(r, i);
+  std::atomic<int> bad{0};
+  auto rank_body = [&](int r) {
+    for (uint64_t seq = 1; seq <= 2; ++seq) {
+      std::vector<std::thread> ctas;
+      for (int c = 0; c < na + nb; ++c) ctas.emplace_back(HybridCta, &w, seq, r, c, na, &in, &out, n, split_vec);
+      for (auto& t : ctas) t.join();
+      for (uint64_t i = 0; i < n; ++i)
+        if (out[r][i] != Sum(ws, i)) ++bad;
+    }
+  };
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < ws; ++r) ranks.emplace_back(rank_body, r);
+  for (auto& t : ranks) t.join();
+  if (bad.load() != 0)
+    fprintf(stderr, "hybrid ws=%d ctas=%d+%d n=%llu split=%llu: %d wrong elements\n", ws, na, nb, static_cast<unsigned long long>(n),
+            static_cast<unsigned long long>(split_vec), bad.load());
+  return bad.load() == 0;
+}
+
 // RsAgBody, direct variant, remote side staged; units of one vector.
 void RsAgCta(World* w, uint64_t seq, bool all_gather, int rank, int cta, const std::vector<int64_t>& send,
              std::vector<int64_t>* recv, uint64_t block_units, uint64_t win_units, uint64_t sub_stride) {
@@ -381,6 +436,15 @@ MINI_TEST(StagedReduceScatterAllGatherProtocol) {
     for (int ncta : {1, 3, 4})
       for (uint64_t block_units : {uint64_t(1), uint64_t(7), uint64_t(64), uint64_t(150), uint64_t(257)})
         CHECK_TRUE(RunRsAg(ws, ncta, block_units, 64));
+}
+
+MINI_TEST(HybridSplitProtocol) {
+  for (int ws : {2, 3, 4})
+    for (int na : {1, 2})
+      for (int nb : {1, 3})
+        for (uint64_t n : {uint64_t(8), uint64_t(403), uint64_t(1024), uint64_t(2051)})
+          for (uint64_t split : {uint64_t(0), uint64_t(1), n / kVec / 2, n / kVec, n})
+            CHECK_TRUE(RunHybrid(ws, na, nb, n, split));
 }
 
 MINI_TEST(RandomStagedConfigurations) {
