@@ -308,6 +308,28 @@ def main() -> int:
             comm.check()
 
     if rank == 0:
+        # Roofline of the timed kernel: one GPU = read + write of the buffer at the measured HBM copy
+        # bandwidth; several GPUs = the bytes that must cross NVLink per GPU and direction (switch path
+        # S (1 + 1/N), the others 2 S (N-1)/N) at the measured peer-copy bandwidth of this pool.
+        roofline = None
+        try:
+            peaks_path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+            hbm = 6650.0
+            hbm_source = "fallback"
+            if os.path.exists(peaks_path):
+                with open(peaks_path) as f:
+                    hbm = float(json.load(f).get("hbm_gbs", hbm))
+                hbm_source = "measured"
+            if world == 1:
+                ideal_ms = 2 * nbytes / (hbm * 1e9) * 1e3
+                roofline = {"bound": f"HBM copy {hbm:.0f} GB/s ({hbm_source})", "ideal_ms": ideal_ms, "fraction": ideal_ms / ms}
+            else:
+                per_dir = nbytes * (1 + 1 / world) if info["last_algo"] == "nvls" else 2 * nbytes * (world - 1) / world
+                ideal_ms = per_dir / 770e9 * 1e3
+                roofline = {"bound": "NVLink 770 GB/s per direction per GPU (measured peer copy)", "bytes_per_direction": per_dir,
+                            "ideal_ms": ideal_ms, "fraction": ideal_ms / ms}
+        except Exception:
+            roofline = None
         line = {
             "metric": "allreduce_busbw_fp32_256MiB", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -318,7 +340,7 @@ def main() -> int:
                        "nvls": info["nvls"], "l2": "inputs (256 MiB) larger than L2 (126 MB)", "elements": n,
                        "bus_factor": "2(N-1)/N, 1 for N=1"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "correct": ok, "max_abs_err": max_err,
-            "per_algo": per_algo, "impl": "ours",
+            "roofline": roofline, "per_algo": per_algo, "impl": "ours",
         }
         print(json.dumps(line))
     if world > 1:
