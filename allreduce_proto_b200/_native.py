@@ -98,6 +98,8 @@ def _declare(lib) -> None:
         "ibcomm_copy_scale": [vp, vp, sz, i, i, dbl, vp],
         "ibcomm_parse_number": [C.c_char_p, C.POINTER(C.c_int64)],
         "ibcomm_get_exp_of_two": [C.c_uint64],
+        "ibcomm_set_tunable": [C.c_char_p, i],
+        "ibcomm_get_tunable": [C.c_char_p, i, C.POINTER(C.c_int)],
         "ibcomm_split_buffer": [sz, sz, sz, C.c_int64, C.POINTER(C.c_uint64), sz, C.POINTER(sz)],
         "ibcomm_rank_to_chunk": [sz, sz, i, C.POINTER(i), sz, C.POINTER(sz)],
         "ibcomm_describe_program": [i, i, i, sz, sz, C.c_int64, sz, C.c_char_p, sz],

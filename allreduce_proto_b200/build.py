@@ -39,6 +39,7 @@ HOST_SOURCES = [
     "src/host/bootstrap.cpp",
     "src/host/schedule.cpp",
     "src/host/tuner.cpp",
+    "src/host/tunables.cpp",
     "src/host/c_api.cpp",
 ]
 CUDA_SOURCES = [
@@ -53,6 +54,7 @@ CUDA_SOURCES = [
     "src/cuda/oneshot_kernel.cu",
     "src/cuda/rsag_kernel.cu",
     "src/cuda/hybrid_kernel.cu",
+    "src/cuda/staged_kernel.cu",
     "src/cuda/copy_kernel.cu",
     "src/cuda/p2p_sendrecv.cu",
     "src/cuda/no_alloc.cu",

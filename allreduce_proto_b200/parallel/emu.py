@@ -76,7 +76,8 @@ class EmuWorld:
         check(_native.lib().ibcomm_emu_set_bad_program_rank(self._h, rank))
 
     def set_direct_staging(self, mode) -> None:
-        """Direct algorithm: 0/False in place, 1/True staged through the pool windows."""
+        """Direct algorithm: 0/False in place, 1/True staged through the pool windows one phase after the other,
+        2 staged through the pipelined kernel (needs 16-byte aligned buffers of whole 16-byte vectors)."""
         check(_native.lib().ibcomm_emu_set_direct_staging(self._h, int(mode)))
 
     @property

@@ -134,6 +134,11 @@ int ibcomm_copy_scale(const void* in, void* out, size_t len_elements, int dtype_
 
 /* Utilities. */
 int ibcomm_parse_number(const char* text, int64_t* out);
+
+/* Named integer knobs of single kernels (include/ibcomm/tunables.h): a value set here wins over the environment
+ * variable of the same name; value < 0 removes the override.  For tuning runs that sweep settings in one process. */
+int ibcomm_set_tunable(const char* name, int value);
+int ibcomm_get_tunable(const char* name, int dflt, int* out);
 int ibcomm_get_exp_of_two(uint64_t n);
 /* Writes up to `capacity` [begin, end) pairs; returns the count in *count. */
 int ibcomm_split_buffer(size_t len_elements, size_t elem_bytes, size_t world_size, int64_t chunk_bytes, uint64_t* pairs,

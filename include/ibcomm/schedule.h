@@ -68,8 +68,17 @@ Program BuildProgram(const ProgramRequest& req);
 // rounded up to a multiple of 128 bytes so that every chunk starts on a
 // vector boundary, and chunks are cut again (each into the same number of
 // pieces, which keeps block boundaries) until one fits `max_chunk_bytes`.
+// `chunks_per_rank` replaces the reference's 4 (chunks = 4 * world_size) when
+// IBCOMM_CHUNKSIZE is unset: small messages are cut into fewer chunks, so
+// that a ring step moves a useful amount of data (see RingChunksPerRank).
 std::vector<Range> SplitForDevice(size_t len_elements, size_t elem_bytes, size_t world_size,
-                                  int64_t env_chunk_bytes, size_t max_chunk_bytes);
+                                  int64_t env_chunk_bytes, size_t max_chunk_bytes, size_t chunks_per_rank = 4);
+// Chunks per rank of the device ring when IBCOMM_CHUNKSIZE is unset: the
+// reference's 4 (knob IBCOMM_RING_POSITIONS) as long as a chunk then holds at
+// least IBCOMM_RING_MIN_CHUNK bytes (default 16 KiB), fewer (down to one)
+// below that: a 4 KiB message on 8 ranks is one 512-byte chunk per rank and
+// 15 ring steps instead of 32 chunks and 60 steps.
+size_t RingChunksPerRank(size_t len_elements, size_t elem_bytes, size_t world_size);
 
 std::string DescribeOp(const Op& op);
 

@@ -17,6 +17,7 @@
 
 #include "ibcomm/communicator.h"
 #include "kernels.h"
+#include "tma_stage.cuh"
 #include "vec_ops.cuh"
 
 namespace ibcomm {
@@ -35,48 +36,6 @@ constexpr int kCopyWarps = kCopyThreads / 32;
 #endif
 constexpr int kCopyStages = IBCOMM_COPY_STAGES;      // tiles in flight per warp
 constexpr int kCopyTileBytesIn = IBCOMM_COPY_TILE;   // bytes of input per tile
-constexpr uint32_t kMbarSpinLimit = 1u << 22;
-
-__device__ __forceinline__ uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void MbarInit(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void MbarExpectTx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait on a phase; false when the limit ran out.
-__device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kMbarSpinLimit; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(SmemAddr(bar)), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void BulkLoad(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(SmemAddr(smem_dst)),
-               "l"(gmem_src), "r"(bytes), "r"(SmemAddr(bar))
-               : "memory");
-}
-__device__ __forceinline__ void BulkStore(void* gmem_dst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(SmemAddr(smem_src)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void BulkCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void BulkWaitRead() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void BulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void FenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
 // Tiles of `kTileElems` elements, dealt round-robin to the warps of the grid.
 // Requires 16-byte aligned `in` and `out`; the ragged end (less than one
 // 16-byte vector of either type) is finished with plain loads and stores.
@@ -100,7 +59,7 @@ __global__ void __launch_bounds__(kCopyThreads) CopyScaleTmaKernel(const TI* __r
 
   if (lane == 0) {
     for (int s = 0; s < kCopyStages; ++s) MbarInit(&full_bar[warp][s], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    MbarInitFence();
   }
   __syncwarp();
 
@@ -198,11 +157,12 @@ static cudaError_t LaunchCopyTyped(const CopyParams& p, int blocks, cudaStream_t
   }
   constexpr int kTileElems = dev::kCopyTileBytesIn / static_cast<int>(sizeof(TI));
   const size_t smem = static_cast<size_t>(dev::kCopyWarps) * dev::kCopyStages * dev::kCopyTileBytesIn;
-  static thread_local bool configured = false;
-  if (!configured) {
+  // The opt-in to more than 48 KiB of dynamic shared memory is a property of
+  // the (function, device) pair and the call is cheap: made on every launch,
+  // so a thread that moves to another GPU is covered.
+  {
     cudaError_t e = cudaFuncSetAttribute(dev::CopyScaleTmaKernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   if (const char* e = getenv("IBCOMM_COPY_BLOCKS")) {  // experiment knob: CTAs of the copy kernel
     int v = atoi(e);

@@ -16,6 +16,7 @@
 #include "driver_api.h"
 #include "engine.h"
 #include "fd_channel.h"
+#include "ibcomm/tunables.h"
 
 namespace ibcomm {
 
@@ -84,6 +85,16 @@ struct LoopbackSend {
   size_t len;
 };
 
+// Share of a zero-copy switch allreduce that the hybrid kernel runs through
+// the direct algorithm, in percent (0 = plain switch kernel), when
+// IBCOMM_NVLS_HYBRID does not say.  Off until a sweep on the machine shows a
+// gain; see the tuning notes of the hybrid kernel.
+int HybridDefaultPercent(int world_size, size_t bytes) {
+  (void)world_size;
+  (void)bytes;
+  return 0;
+}
+
 }  // namespace
 
 class DeviceContext {
@@ -137,8 +148,14 @@ class DeviceContext {
   void RunProgram(Algo algo, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
                   cudaStream_t stream);
   void RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels, cudaStream_t stream);
-  void RunTwoShot(bool multimem, DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
+  void RunTwoShot(bool multimem, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
                   cudaStream_t stream);
+  // The pipelined kernel for buffers that go through the pool; false when the
+  // call does not meet its requirements (nothing has been launched then).
+  bool RunStaged(bool multimem, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
+                 cudaStream_t stream);
+  // Begins a device trace record of `records` entries per channel (no-op when tracing is off).
+  DeviceTraceRec* BeginDeviceTrace(int channels, int records, int* capacity);
   void ExchangeAllocation(SharedAllocation* mine, std::vector<std::unique_ptr<SharedAllocation>>* imported,
                           unsigned char** peer_ptr, bool try_multicast, std::unique_ptr<MulticastGroup>* mc);
 
@@ -166,6 +183,7 @@ class DeviceContext {
   uint64_t kernel_launches_ = 0;
   int last_algo_ = 0, last_channels_ = 0;
   int hybrid_channels_ = 0;  // CTAs of the hybrid two-shot kernel when the last call ran it
+  int staged_channels_ = 0;  // CTAs of the pipelined staged kernel when the last call ran it
   int max_channels_ = env::kDefaultNumCudaStream;
   std::vector<P2pState> p2p_;
   std::vector<std::unique_ptr<SymmetricAlloc>> symm_;
@@ -411,6 +429,7 @@ void DeviceContext::MarkIssued(cudaStream_t stream) {
 void DeviceContext::Finish(cudaStream_t stream, bool async) {
   if (async) return;
   CUDACHECK(cudaStreamSynchronize(stream));
+  cache_.NoteSynchronized();
   Check();
 }
 
@@ -593,19 +612,9 @@ void DeviceContext::RunCopy(DType dtype, const void* sendbuf, void* recvbuf, siz
 
 void DeviceContext::RunProgram(Algo algo, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale,
                                int channels, cudaStream_t stream) {
-  const CachedProgram& cp = cache_.Get(algo, rank_, ws_, n, dtype, wire, layout_, scale != 1.0);
-  DeviceTraceRec* trace = nullptr;
+  const CachedProgram& cp = cache_.Get(algo, rank_, ws_, n, dtype, wire, layout_, scale != 1.0, stream, IsCapturing(stream));
   int cap = 0;
-  if (d_trace_ != nullptr && channels <= trace_channels_) {
-    trace = d_trace_;
-    cap = trace_capacity_;
-    if (!pending_trace_.empty()) CollectTrace(tracer_);
-    PendingTrace pt;
-    pt.channels = channels;
-    pt.ops = std::min<int>(static_cast<int>(cp.prog.ops.size()), cap);
-    clock_gettime(CLOCK_MONOTONIC_RAW, &pt.host_launch);
-    pending_trace_.push_back(pt);
-  }
+  DeviceTraceRec* trace = BeginDeviceTrace(channels, static_cast<int>(cp.prog.ops.size()), &cap);
   ExecParams p = MakeExecParams(rr_, cp, dtype, wire, sendbuf, recvbuf, n, scale,
                                 static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull, trace, cap);
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
@@ -624,7 +633,73 @@ void DeviceContext::RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, 
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
 }
 
-void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale,
+DeviceTraceRec* DeviceContext::BeginDeviceTrace(int channels, int records, int* capacity) {
+  *capacity = 0;
+  if (d_trace_ == nullptr || channels > trace_channels_) return nullptr;
+  if (!pending_trace_.empty()) CollectTrace(tracer_);
+  CUDACHECK(cudaMemsetAsync(d_trace_, 0, sizeof(DeviceTraceRec) * static_cast<size_t>(trace_capacity_) * static_cast<size_t>(trace_channels_), stream_));
+  CUDACHECK(cudaStreamSynchronize(stream_));
+  PendingTrace pt;
+  pt.channels = channels;
+  pt.ops = std::min<int>(records, trace_capacity_);
+  clock_gettime(CLOCK_MONOTONIC_RAW, &pt.host_launch);
+  pending_trace_.push_back(pt);
+  *capacity = trace_capacity_;
+  return d_trace_;
+}
+
+bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale,
+                              int channels, cudaStream_t stream) {
+  if (Tunable("IBCOMM_STAGED", 1) == 0) return false;
+  const size_t wsize = DTypeSize(wire);
+  if (wsize > DTypeSize(dtype)) return false;
+  if (((reinterpret_cast<uintptr_t>(sendbuf) | reinterpret_cast<uintptr_t>(recvbuf)) & 15u) != 0) return false;
+  if ((n * wsize) % 16 != 0) return false;
+  if (multimem && (mc_ == nullptr || !NvlsSupportsDType(wire))) return false;
+  // Four windows (two in, two out) in the pool and the work region behind it
+  // (the two are adjacent and one collective runs at a time).
+  const uint64_t quarter = (layout_.pool_bytes + layout_.work_bytes) / 4 / 4096 * 4096;
+  if (quarter < 4096) return false;
+  StagedParams p;
+  memset(&p, 0, sizeof(p));
+  p.rank = rank_;
+  p.world_size = ws_;
+  p.dtype = static_cast<int32_t>(dtype);
+  p.wire = static_cast<int32_t>(wire);
+  p.use_multimem = multimem ? 1 : 0;
+  p.use_tma = (wire == dtype && Tunable("IBCOMM_STAGED_TMA", 1) != 0) ? 1 : 0;
+  p.peers = rr_.peers;
+  p.sendbuf = sendbuf;
+  p.recvbuf = recvbuf;
+  p.len_elements = n;
+  p.scale = scale;
+  int ctas = Tunable("IBCOMM_STAGED_CTAS", 0);
+  if (ctas <= 0) ctas = std::max(channels, ChooseChannels(Algo::kDirect, n * wsize, ws_, max_channels_));
+  static const int resident = StagedKernelMaxCoResidentBlocks(device_);
+  if (resident > 0) ctas = std::min(ctas, resident);
+  ctas = std::max(1, std::min(ctas, kMaxChannels));
+  uint64_t cap_bytes = quarter;
+  const int max_window = Tunable("IBCOMM_STAGED_WINDOW_KIB", 0);  // experiment knob: smaller windows
+  if (max_window > 0) cap_bytes = std::min<uint64_t>(cap_bytes, static_cast<uint64_t>(max_window) << 10);
+  p.window_elems = TwoShotWindowElems(n, cap_bytes / wsize, wsize, ws_, ctas);
+  for (int j = 0; j < 2; ++j) {
+    p.in_off[j] = layout_.pool_offset + static_cast<uint64_t>(j) * quarter;
+    p.out_off[j] = layout_.pool_offset + static_cast<uint64_t>(2 + j) * quarter;
+  }
+  p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
+  p.status = rr_.d_status;
+  p.doorbell = rr_.d_doorbell;
+  const uint64_t windows = (n + p.window_elems - 1) / p.window_elems;
+  p.trace = BeginDeviceTrace(ctas, static_cast<int>(std::min<uint64_t>(windows, 1u << 20)), &p.trace_capacity);
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+  CUDACHECK(LaunchStagedKernel(p, nullptr, 1, ctas, stream));
+  ++kernel_launches_;
+  IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
+  staged_channels_ = ctas;
+  return true;
+}
+
+void DeviceContext::RunTwoShot(bool multimem, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale,
                                int channels, cudaStream_t stream) {
   const size_t esize = DTypeSize(dtype);
   const size_t bytes = n * esize;
@@ -661,6 +736,12 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   }
   const bool zin = (rin || (sin != nullptr && (sin->mc || !multimem))) && (reinterpret_cast<uintptr_t>(sendbuf) & 15u) == 0;
   const bool zout = (rout || (sout != nullptr && (sout->mc || !multimem))) && (reinterpret_cast<uintptr_t>(recvbuf) & 15u) == 0;
+  // Nothing zero-copy (or a 16-bit wire, which is staged by definition): the
+  // pipelined kernel, when the buffers meet its alignment rules.
+  if ((wire != dtype || (!zin && !zout)) && RunStaged(multimem, dtype, wire, sendbuf, recvbuf, n, scale, channels, stream)) return;
+  if (wire != dtype)
+    IBCOMM_FAIL(NOT_SUPPORTED, "The %s algorithm sends fp32 as 16-bit values only for 16-byte aligned buffers of a whole number of "
+                "16-byte wire vectors; use the ring algorithm for this buffer.\n", multimem ? "nvls" : "direct");
   unsigned char* const mc_arena = mc_ ? mc_->ptr() : nullptr;
   // Staging windows: first half of the pool for inputs, second half for outputs.
   const uint64_t half = layout_.pool_bytes / 2 / 4096 * 4096;
@@ -701,22 +782,17 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, const void* sendbuf, 
   }
   p.window_elems = (zin && zout) ? n : window_elems;
   if (p.window_elems == 0) p.window_elems = 1;
-  // Opt-in experiment: IBCOMM_NVLS_HYBRID = percentage (1..90) of a zero-copy switch allreduce that runs
-  // direct, concurrently, in the same kernel; IBCOMM_NVLS_HYBRID_CTAS = "switch,direct" CTAs (48,96).
+  // Hybrid: IBCOMM_NVLS_HYBRID = percentage (1..90) of a zero-copy switch allreduce that runs direct,
+  // concurrently, in the same kernel on CTAs of its own (IBCOMM_NVLS_HYBRID_SWITCH_CTAS + IBCOMM_NVLS_HYBRID_DIRECT_CTAS
+  // <= one per SM).  The built-in percentage per world size comes from sweeps on B200 (HybridDefaultPercent).
   if (multimem && zin && zout && ws_ > 1) {
-    static const int direct_percent = [] {
-      const char* s = getenv("IBCOMM_NVLS_HYBRID");
-      const int v = s != nullptr ? atoi(s) : 0;
-      return (v >= 1 && v <= 90) ? v : 0;
-    }();
+    int direct_percent = Tunable("IBCOMM_NVLS_HYBRID", HybridDefaultPercent(ws_, bytes));
+    if (direct_percent < 1 || direct_percent > 90) direct_percent = 0;
     if (direct_percent > 0 && bytes >= (8u << 20)) {
-      int nvls_ctas = 48, direct_ctas = 96;
-      if (const char* s = getenv("IBCOMM_NVLS_HYBRID_CTAS")) {
-        int a = 0, b = 0;
-        if (sscanf(s, "%d,%d", &a, &b) == 2 && a >= 1 && b >= 1 && a + b <= 148) {
-          nvls_ctas = a;
-          direct_ctas = b;
-        }
+      int nvls_ctas = Tunable("IBCOMM_NVLS_HYBRID_SWITCH_CTAS", 48), direct_ctas = Tunable("IBCOMM_NVLS_HYBRID_DIRECT_CTAS", 96);
+      if (nvls_ctas < 1 || direct_ctas < 1 || nvls_ctas + direct_ctas > 148) {
+        nvls_ctas = 48;
+        direct_ctas = 96;
       }
       HybridParams h;
       memset(&h, 0, sizeof(h));
@@ -760,30 +836,38 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
   ConnectPeers();
   Algo algo = opts.algo;
   if (algo == Algo::kAuto) algo = AlgoFromName(env::ReadAlgo());
-  const bool nvls_ok = mc_ != nullptr && NvlsSupportsDType(dtype) && wire == dtype;
+  // A 16-bit wire is carried by the ring / Rabenseifner programs and by the
+  // pipelined staged two-shot (switch or direct), which wants 16-byte aligned
+  // buffers of whole 16-byte wire vectors.
+  const bool compressed = wire != dtype;
+  const bool staged_shape = ((reinterpret_cast<uintptr_t>(sendbuf) | reinterpret_cast<uintptr_t>(recvbuf)) & 15u) == 0 &&
+                            (n * DTypeSize(wire)) % 16 == 0 && Tunable("IBCOMM_STAGED", 1) != 0;
+  const bool nvls_ok = mc_ != nullptr && NvlsSupportsDType(wire) && (!compressed || staged_shape);
   int channels;
   if (algo == Algo::kAuto) {
     const bool symmetric = FindSymmetric(sendbuf, bytes) != nullptr && FindSymmetric(recvbuf, bytes) != nullptr;
     unsigned char* unused[kMaxRanks];
     // Registered buffers are mapped by the peers but not bound to the
-    // multicast object: zero-copy for the direct algorithm only.
-    const bool mapped = symmetric || (FindPeerMapped(sendbuf, bytes, unused) && FindPeerMapped(recvbuf, bytes, unused));
+    // multicast object: zero-copy for the direct algorithm only.  With a
+    // 16-bit wire every buffer goes through the pool (that is where the
+    // 16-bit copy lives), mapped or not.
+    const bool mapped = !compressed && (symmetric || (FindPeerMapped(sendbuf, bytes, unused) && FindPeerMapped(recvbuf, bytes, unused)));
     TunerChoice c = ChooseAlgorithm(bytes, ws_, nvls_ok && (symmetric || !mapped), mapped, max_channels_);
     algo = c.algo;
     channels = c.channels;
-    if ((algo == Algo::kOneShot && (bytes > layout_.oneshot_slot_bytes || wire != dtype)) ||
-        ((algo == Algo::kDirect || algo == Algo::kNvls) && wire != dtype)) {
+    if ((algo == Algo::kOneShot && (bytes > layout_.oneshot_slot_bytes || compressed)) ||
+        ((algo == Algo::kDirect || algo == Algo::kNvls) && compressed && !staged_shape)) {
       algo = Algo::kRing;
       channels = ChooseChannels(algo, bytes, ws_, max_channels_);
     }
   } else {
     if (algo == Algo::kNvls && !nvls_ok)
-      IBCOMM_FAIL(NOT_SUPPORTED, "The NVLS algorithm needs NVSwitch multicast and a float32/float16/bfloat16 buffer without wire compression.\n");
+      IBCOMM_FAIL(NOT_SUPPORTED, "The NVLS algorithm needs NVSwitch multicast and float32/float16/bfloat16 values on the wire "
+                  "(with a 16-bit wire: 16-byte aligned buffers of whole 16-byte wire vectors).\n");
     if (algo == Algo::kOneShot && bytes > layout_.oneshot_slot_bytes)
       IBCOMM_FAIL(INVALID_ARGUMENT, "One-shot allreduce handles at most %llu bytes (got %zu).\n",
                   static_cast<unsigned long long>(layout_.oneshot_slot_bytes), bytes);
-    if (algo == Algo::kOneShot && wire != dtype) IBCOMM_FAIL(NOT_SUPPORTED, "One-shot allreduce has no wire compression.\n");
-    if (algo == Algo::kDirect && wire != dtype) IBCOMM_FAIL(NOT_SUPPORTED, "The direct algorithm has no wire compression.\n");
+    if (algo == Algo::kOneShot && compressed) IBCOMM_FAIL(NOT_SUPPORTED, "One-shot allreduce has no wire compression.\n");
     channels = ChooseChannels(algo, bytes, ws_, max_channels_);
     if (algo == Algo::kNvls && !(FindSymmetric(sendbuf, bytes) != nullptr && FindSymmetric(recvbuf, bytes) != nullptr))
       channels = std::max(channels, ChooseChannels(Algo::kDirect, bytes, ws_, max_channels_));
@@ -798,18 +882,19 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
       RunOneShot(dtype, sendbuf, recvbuf, n, opts.scale, channels, stream);
       break;
     case Algo::kNvls:
-      RunTwoShot(true, dtype, sendbuf, recvbuf, n, opts.scale, channels, stream);
+      RunTwoShot(true, dtype, wire, sendbuf, recvbuf, n, opts.scale, channels, stream);
       break;
     case Algo::kDirect:
-      RunTwoShot(false, dtype, sendbuf, recvbuf, n, opts.scale, channels, stream);
+      RunTwoShot(false, dtype, wire, sendbuf, recvbuf, n, opts.scale, channels, stream);
       break;
     default:
       IBCOMM_FAIL(INVALID_ARGUMENT, "Unknown algorithm.\n");
   }
   MarkIssued(stream);
   last_algo_ = static_cast<int>(algo);
-  last_channels_ = hybrid_channels_ > 0 ? hybrid_channels_ : channels;
+  last_channels_ = hybrid_channels_ > 0 ? hybrid_channels_ : (staged_channels_ > 0 ? staged_channels_ : channels);
   hybrid_channels_ = 0;
+  staged_channels_ = 0;
   Finish(stream, opts.async);
 }
 

@@ -6,6 +6,7 @@
 #include <cstring>
 
 #include "engine.h"
+#include "ibcomm/tunables.h"
 
 namespace ibcomm {
 
@@ -24,7 +25,8 @@ struct EmuWorld::Impl {
   int last_channels = 0;
   int silent_rank = -1;
   int bad_program_rank = -1;
-  int direct_staging = 0;  // 0 in place, 1 staged window by window
+  int direct_staging = 0;  // 0 in place, 1 staged window by window, 2 staged through the pipelined kernel
+  int staged_max_blocks = 0;
   uint32_t last_status = 0;
   DeviceStatus last_report{};
 
@@ -64,6 +66,7 @@ EmuWorld::EmuWorld(int num_ranks, size_t pool_bytes, size_t work_bytes) : ws_(nu
     rr.d_doorbell = m.status[static_cast<size_t>(r)].d_doorbell;
   }
   m.max_blocks = ExecKernelMaxCoResidentBlocks(m.device);
+  m.staged_max_blocks = StagedKernelMaxCoResidentBlocks(m.device);
   CUDACHECK(cudaDeviceSynchronize());
 }
 
@@ -116,7 +119,48 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
   const uint64_t timeout_ns = static_cast<uint64_t>(m.timeout_ms) * 1000000ull;
   const int cap = std::max(1, m.max_blocks / m.ws);
 
-  if (algo == Algo::kDirect) {
+  bool all_aligned = true;
+  for (int q = 0; q < m.ws; ++q)
+    all_aligned = all_aligned && ((reinterpret_cast<uintptr_t>(sendbufs[static_cast<size_t>(q)]) | reinterpret_cast<uintptr_t>(recvbufs[static_cast<size_t>(q)])) & 15u) == 0;
+  const size_t wsize = DTypeSize(wire);
+  if (algo == Algo::kDirect && (wire != dtype || m.direct_staging == 2)) {
+    // The pipelined staged kernel (what ordinary buffers and 16-bit wires get on several GPUs).
+    const uint64_t quarter = (m.layout.pool_bytes + m.layout.work_bytes) / 4 / 4096 * 4096;
+    if (!all_aligned || (n * wsize) % 16 != 0 || quarter < 4096)
+      IBCOMM_FAIL(NOT_SUPPORTED, "The pipelined staged two-shot needs 16-byte aligned buffers of whole 16-byte wire vectors.\n");
+    int ch = channels > 0 ? channels : ChooseChannels(Algo::kDirect, n * wsize, m.ws, kMaxChannels);
+    ch = std::max(1, std::min(ch, std::max(1, m.staged_max_blocks / m.ws)));
+    std::vector<StagedParams> ps(static_cast<size_t>(m.ws));
+    for (int r = 0; r < m.ws; ++r) {
+      StagedParams& p = ps[static_cast<size_t>(r)];
+      memset(&p, 0, sizeof(p));
+      const RankResources& rr = m.ranks[static_cast<size_t>(r)];
+      p.rank = r;
+      p.world_size = m.ws;
+      p.dtype = static_cast<int32_t>(dtype);
+      p.wire = static_cast<int32_t>(wire);
+      p.use_multimem = 0;
+      p.use_tma = (wire == dtype && Tunable("IBCOMM_STAGED_TMA", 1) != 0) ? 1 : 0;
+      p.peers = rr.peers;
+      p.sendbuf = sendbufs[static_cast<size_t>(r)];
+      p.recvbuf = recvbufs[static_cast<size_t>(r)];
+      p.len_elements = n;
+      p.scale = scale;
+      p.window_elems = TwoShotWindowElems(n, quarter / wsize, wsize, m.ws, ch);
+      for (int j = 0; j < 2; ++j) {
+        p.in_off[j] = m.layout.pool_offset + static_cast<uint64_t>(j) * quarter;
+        p.out_off[j] = m.layout.pool_offset + static_cast<uint64_t>(2 + j) * quarter;
+      }
+      p.timeout_ns = timeout_ns;
+      p.status = rr.d_status;
+      p.doorbell = rr.d_doorbell;
+      if (r == m.silent_rank) p.len_elements = 0;  // takes no part: no window, no flag
+    }
+    void* d = m.Params(ps.size() * sizeof(StagedParams));
+    CUDACHECK(cudaMemcpyAsync(d, ps.data(), ps.size() * sizeof(StagedParams), cudaMemcpyHostToDevice, stream));
+    CUDACHECK(LaunchStagedKernel(ps[0], static_cast<const StagedParams*>(d), m.ws, ch, stream));
+    m.last_channels = ch;
+  } else if (algo == Algo::kDirect) {
     // The two-shot kernel with peer loads and stores.  All ranks' buffers live
     // on this GPU, so they can be used in place; with `direct_staging` they
     // go through the pool windows like buffers the peers cannot map.
@@ -184,7 +228,7 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
     // Validation (length, chunk size) happens while the first program is cut.
     std::vector<ExecParams> ps;
     for (int r = 0; r < m.ws; ++r) {
-      const CachedProgram& cp = m.cache.Get(algo, r, m.ws, n, dtype, wire, m.layout, scale != 1.0);
+      const CachedProgram& cp = m.cache.Get(algo, r, m.ws, n, dtype, wire, m.layout, scale != 1.0, stream, false);
       ps.push_back(MakeExecParams(m.ranks[static_cast<size_t>(r)], cp, dtype, wire, sendbufs[static_cast<size_t>(r)],
                                   recvbufs[static_cast<size_t>(r)], n, scale, timeout_ns, nullptr, 0));
       if (r == m.silent_rank) ps.back().num_ops = 0;
@@ -199,6 +243,7 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
   }
   if (async) return;
   CUDACHECK(cudaStreamSynchronize(stream));
+  m.cache.NoteSynchronized();
   for (int r = 0; r < m.ws; ++r) {
     DeviceStatus st;
     uint32_t code = m.status[static_cast<size_t>(r)].Consume(&st, stream);

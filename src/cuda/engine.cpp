@@ -4,6 +4,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include "ibcomm/tunables.h"
+
 namespace ibcomm {
 
 static uint64_t AlignUp(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
@@ -80,14 +82,50 @@ std::string DescribeStatus(const DeviceStatus& st) {
 ProgramCache::~ProgramCache() { Clear(); }
 
 void ProgramCache::Clear() {
-  for (auto& kv : cache_)
-    if (kv.second->d_ops != nullptr) cudaFree(kv.second->d_ops);
   cache_.clear();
+  for (Slab& sl : slabs_) {
+    if (sl.d != nullptr) cudaFree(sl.d);
+    if (sl.h != nullptr) cudaFreeHost(sl.h);
+  }
+  slabs_.clear();
   (void)cudaGetLastError();
 }
 
+Op* ProgramCache::Place(const std::vector<Op>& ops, cudaStream_t stream, int* slab_index) {
+  const size_t n = ops.size();
+  int at = -1;
+  for (size_t i = 0; i < slabs_.size(); ++i)
+    if (slabs_[i].cap - slabs_[i].used >= n) at = static_cast<int>(i);
+  if (at < 0) {
+    Slab sl;
+    sl.cap = std::max<size_t>(n, (1u << 20) / sizeof(Op));
+    CUDACHECK(cudaMalloc(&sl.d, sl.cap * sizeof(Op)));
+    CUDACHECK(cudaHostAlloc(reinterpret_cast<void**>(&sl.h), sl.cap * sizeof(Op), cudaHostAllocPortable));
+    slabs_.push_back(sl);
+    at = static_cast<int>(slabs_.size()) - 1;
+  }
+  Slab& sl = slabs_[static_cast<size_t>(at)];
+  memcpy(sl.h + sl.used, ops.data(), n * sizeof(Op));
+  CUDACHECK(cudaMemcpyAsync(sl.d + sl.used, sl.h + sl.used, n * sizeof(Op), cudaMemcpyHostToDevice, stream));
+  Op* d = sl.d + sl.used;
+  sl.used += n;
+  *slab_index = at;
+  return d;
+}
+
+void ProgramCache::NoteSynchronized() {
+  if (cache_.size() <= bound_) return;
+  for (auto it = cache_.begin(); it != cache_.end();) {
+    if (it->second->pinned) ++it;
+    else it = cache_.erase(it);
+  }
+  // A slab without pinned programs starts over; the others keep their contents.
+  for (Slab& sl : slabs_)
+    if (sl.pinned == 0) sl.used = 0;
+}
+
 const CachedProgram& ProgramCache::Get(Algo algo, int rank, int world_size, size_t len_elements, DType dtype, DType wire,
-                                       const ArenaLayout& layout, bool apply_scale) {
+                                       const ArenaLayout& layout, bool apply_scale, cudaStream_t stream, bool capturing) {
   const size_t esize = DTypeSize(dtype), wsize = DTypeSize(wire);
   // Read at the point of use, like the reference: a bad value fails the call.
   const long long env_chunk = env::ReadChunkSize();
@@ -97,10 +135,22 @@ const CachedProgram& ProgramCache::Get(Algo algo, int rank, int world_size, size
   // it as well (the two are adjacent in the arena).
   const uint64_t stage_off = layout.pool_offset;
   const uint64_t stage_bytes = ring ? layout.pool_bytes : layout.pool_bytes + layout.work_bytes;
+  // Knobs that shape the program are part of the key: the ring's chunks per
+  // rank and the number of pieces Rabenseifner cuts the message into.
+  const size_t ring_cpr = ring ? RingChunksPerRank(len_elements, esize, static_cast<size_t>(world_size)) : 0;
+  int raben_div = Tunable("IBCOMM_RABEN_PIECES", 8);
+  if (raben_div < 1 || raben_div > 1024) raben_div = 8;
   Key key{static_cast<int>(algo), rank, world_size, len_elements, static_cast<int>(dtype), static_cast<int>(wire),
-          env_chunk, apply_scale, stage_off, stage_bytes};
+          env_chunk, apply_scale, stage_off, stage_bytes, ring ? static_cast<int>(ring_cpr) : raben_div};
   auto it = cache_.find(key);
-  if (it != cache_.end()) return *it->second;
+  if (it != cache_.end()) {
+    CachedProgram& hit = *it->second;
+    if (capturing && !hit.pinned) {
+      hit.pinned = true;
+      if (hit.slab >= 0) ++slabs_[static_cast<size_t>(hit.slab)].pinned;
+    }
+    return hit;
+  }
 
   const int regions = NumRegions(algo, world_size);
   ProgramRequest req;
@@ -113,15 +163,16 @@ const CachedProgram& ProgramCache::Get(Algo algo, int rank, int world_size, size
     uint64_t max_chunk_wire = stage_bytes / (static_cast<uint64_t>(regions) * 4) / 128 * 128;
     if (max_chunk_wire < 128) max_chunk_wire = 128;
     const size_t max_chunk_user = static_cast<size_t>(max_chunk_wire / wsize * esize);
-    req.ranges = SplitForDevice(len_elements, esize, static_cast<size_t>(world_size), env_chunk, max_chunk_user);
+    req.ranges = SplitForDevice(len_elements, esize, static_cast<size_t>(world_size), env_chunk, max_chunk_user, ring_cpr);
   } else {
     // Chunks only fix the block boundaries here; what travels are pieces:
     // IBCOMM_CHUNKSIZE when set, otherwise an eighth of the message (four
-    // pieces in the largest step), as far as two slots per partner fit.
+    // pieces in the largest step; knob IBCOMM_RABEN_PIECES), as far as two
+    // slots per partner fit.
     req.ranges = SplitForDevice(len_elements, esize, static_cast<size_t>(world_size), env_chunk, 0);
     size_t cap = static_cast<size_t>(stage_bytes / (static_cast<uint64_t>(regions) * 2) / wsize) / 32 * 32;
     if (cap < 32) cap = 32;
-    size_t piece = env_chunk > 0 ? static_cast<size_t>(env_chunk) / esize : std::max<size_t>(util::ceilDiv(len_elements, size_t(8)), 16384);
+    size_t piece = env_chunk > 0 ? static_cast<size_t>(env_chunk) / esize : std::max<size_t>(util::ceilDiv(len_elements, static_cast<size_t>(raben_div)), 16384);
     if (piece > cap) {
       static bool warned = false;
       if (!warned && rank == 0) {
@@ -147,14 +198,12 @@ const CachedProgram& ProgramCache::Get(Algo algo, int rank, int world_size, size
                                   ring ? "ring" : "Rabenseifner", len_elements, world_size, bad.c_str());
   }
   if (!cp->prog.ops.empty()) {
-    const size_t bytes = cp->prog.ops.size() * sizeof(Op);
-    CUDACHECK(cudaMalloc(&cp->d_ops, bytes));
-    CUDACHECK(cudaMemcpy(cp->d_ops, cp->prog.ops.data(), bytes, cudaMemcpyHostToDevice));
+    cp->d_ops = Place(cp->prog.ops, stream, &cp->slab);
+    if (capturing) {
+      cp->pinned = true;
+      ++slabs_[static_cast<size_t>(cp->slab)].pinned;
+    }
   }
-  // Programs are small (tens of KiB); they are kept, because a captured CUDA
-  // graph holds the device pointer of the program it was recorded with.  The
-  // bound only stops a pathological stream of distinct lengths.
-  if (cache_.size() > 4096) Clear();
   const CachedProgram& ref = *cp;
   cache_[key] = std::move(cp);
   return ref;

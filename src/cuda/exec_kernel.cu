@@ -7,6 +7,14 @@
 //         -> recvbuf and/or the next peer's staging slot over NVLink,
 // then publishes the data flag to the receiver and returns the credit to the
 // sender.  No host round trip and no separate reduce, cast or scale kernel.
+//
+// The CTA is warp-specialised so that the synchronisation of one op overlaps
+// the data of its neighbours: one thread (the "waiter") runs ahead through
+// the program and waits for the flags of the coming ops; the data warps
+// stream op after op without a CTA-wide barrier; another thread (the
+// "poster") follows behind, and once every data warp has issued an op's
+// stores it fences them and publishes the op's flags.  The three parties
+// hand over through two counters in shared memory (ops ready, warp-ops done).
 // Counterpart of the reference's host event loop around _reduce_inplace_cuda
 // (ibcomm/allreduce_cuda_impl.h:24-33, 103-299, 470-707).
 //
@@ -19,6 +27,7 @@
 
 #include "flags.cuh"
 #include "ibcomm/communicator.h"
+#include "ibcomm/tunables.h"
 #include "kernels.h"
 #include "vec_ops.cuh"
 
@@ -39,7 +48,8 @@ struct ExecTraits {
 // are predicates on registers, not divergence.
 template <typename T, typename W>
 __device__ __forceinline__ void VecLoop(const uint4* __restrict__ a_base, bool a_is_stage, const uint4* __restrict__ b_base,
-                                        uint4* l_base, uint4* r_base, uint64_t npacks, bool do_scale, double scale, bool round_wire) {
+                                        uint4* l_base, uint4* r_base, uint64_t npacks, bool do_scale, double scale, bool round_wire,
+                                        unsigned tid, unsigned nthr) {
   using Tr = ExecTraits<T, W>;
   using A = typename Tr::A;
   constexpr int P = Tr::P;
@@ -47,8 +57,8 @@ __device__ __forceinline__ void VecLoop(const uint4* __restrict__ a_base, bool a
   constexpr int VT = P / VecIO<T>::kN;  // 16-byte vectors per pack in the user type
   constexpr int VW = P / VecIO<W>::kN;  // ... in the wire type
   const int va = a_is_stage ? VW : VT;
-  const uint64_t stride = blockDim.x;
-  for (uint64_t i = threadIdx.x; i < npacks; i += stride * U) {
+  const uint64_t stride = nthr;
+  for (uint64_t i = tid; i < npacks; i += stride * U) {
     uint4 qa[U][VT];
     uint4 qb[U][VT];
 #pragma unroll
@@ -115,9 +125,9 @@ __device__ __forceinline__ void VecLoop(const uint4* __restrict__ a_base, bool a
 // and for the few elements after the last whole pack.
 template <typename T, typename W>
 __device__ void ScalarLoop(const Op& op, const T* sendbuf, T* recvbuf, const W* stage_in, W* stage_out, uint64_t lo,
-                           uint64_t hi, double scale) {
+                           uint64_t hi, double scale, unsigned tid, unsigned nthr) {
   using A = typename Acc<T>::type;
-  for (uint64_t k = lo + threadIdx.x; k < hi; k += blockDim.x) {
+  for (uint64_t k = lo + tid; k < hi; k += nthr) {
     const uint64_t g = op.cell_begin + k;
     A v;
     if (op.src_a == kSrcStage) v = ToAcc<A, W>(LdScalarStrong<W>(stage_in + k));
@@ -133,7 +143,7 @@ __device__ void ScalarLoop(const Op& op, const T* sendbuf, T* recvbuf, const W* 
 }
 
 template <typename T, typename W>
-__device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch) {
+__device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch, unsigned tid, unsigned nthr) {
   using Tr = ExecTraits<T, W>;
   uint64_t lo, hi;
   ChannelSlice(op.elem_begin - op.cell_begin, op.elem_count, p.stage.slot_bytes / sizeof(W), nch, ch, &lo, &hi);
@@ -155,8 +165,13 @@ __device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch) {
   bool aligned = true;
   if (uses_send) aligned &= (reinterpret_cast<uintptr_t>(sendbuf + g0) & 15u) == 0;
   if (uses_recv) aligned &= (reinterpret_cast<uintptr_t>(recvbuf + g0) & 15u) == 0;
+  // The place inside a staging slot follows the cell, not the user buffer: a
+  // range that starts in the middle of a cell (Rabenseifner pieces, 16-bit
+  // wire) can be 16-byte aligned on the user side and not in the slot.
+  if (stage_in != nullptr) aligned &= (reinterpret_cast<uintptr_t>(stage_in + lo) & 15u) == 0;
+  if (stage_out != nullptr) aligned &= (reinterpret_cast<uintptr_t>(stage_out + lo) & 15u) == 0;
   if (!aligned) {
-    ScalarLoop<T, W>(op, sendbuf, recvbuf, stage_in, stage_out, lo, hi, p.scale);
+    ScalarLoop<T, W>(op, sendbuf, recvbuf, stage_in, stage_out, lo, hi, p.scale, tid, nthr);
     return;
   }
   const uint64_t npacks = (hi - lo) / Tr::P;
@@ -171,10 +186,10 @@ __device__ void RunOpData(const Op& op, const ExecParams& p, int ch, int nch) {
     uint4* l_base = (op.flags & kOpStoreLocal) ? reinterpret_cast<uint4*>(recvbuf + g0) : nullptr;
     uint4* r_base = (op.flags & kOpStoreRemote) ? reinterpret_cast<uint4*>(stage_out + lo) : nullptr;
     VecLoop<T, W>(a_base, a_is_stage, b_base, l_base, r_base, npacks, (op.flags & kOpScale) != 0, p.scale,
-                  (op.flags & kOpRoundWire) != 0);
+                  (op.flags & kOpRoundWire) != 0, tid, nthr);
   }
   const uint64_t done = lo + npacks * Tr::P;
-  if (done < hi) ScalarLoop<T, W>(op, sendbuf, recvbuf, stage_in, stage_out, done, hi, p.scale);
+  if (done < hi) ScalarLoop<T, W>(op, sendbuf, recvbuf, stage_in, stage_out, done, hi, p.scale, tid, nthr);
 }
 
 // Body of the executor for one CTA; returns when the program is done or a wait gave up.
@@ -200,8 +215,45 @@ __device__ __forceinline__ bool OpInBounds(const Op& op, const ExecParams& p) {
   return true;
 }
 
+// Hand-over counters between the waiter, the data warps and the poster.
+struct ExecSync {
+  unsigned ready;  // ops whose flags have arrived (written by the waiter)
+  unsigned done;   // (data warp, op) pairs whose stores have been issued
+  int stop;        // a wait gave up or the program is bad: everybody leaves
+};
+
+__device__ __forceinline__ unsigned SmemU32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ unsigned LdAcquireShared(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(SmemU32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void StReleaseShared(unsigned* p, unsigned v) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(SmemU32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void AddReleaseShared(unsigned* p, unsigned v) {
+  asm volatile("red.release.cta.shared.add.u32 [%0], %1;" ::"r"(SmemU32(p)), "r"(v) : "memory");
+}
+
+// Spins until *counter >= target.  False when the call was stopped, or after
+// twice the wait limit (a safety net: the waiter's own limit fires first).
+__device__ __forceinline__ bool SpinShared(const unsigned* counter, unsigned target, ExecSync* sync, uint64_t timeout_ns) {
+  if (LdAcquireShared(counter) >= target) return true;
+  const uint64_t t0 = GlobalTimerNs();
+  for (uint32_t spin = 1;; ++spin) {
+    if (LdAcquireShared(counter) >= target) return true;
+    if (*reinterpret_cast<volatile int*>(&sync->stop) != 0) return false;
+    if ((spin & 1023u) == 0u && GlobalTimerNs() - t0 > 2 * timeout_ns) {
+      *reinterpret_cast<volatile int*>(&sync->stop) = 1;
+      return false;
+    }
+  }
+}
+
+// Body of the executor for one CTA: warps [0, data_warps) move data, lane 0 of
+// the next warp is the waiter, lane 0 of the last warp the poster.
 template <typename T, typename W>
-__device__ void ExecBody(const ExecParams& p, uint64_t seq, int* s_stop) {
+__device__ void ExecBody(const ExecParams& p, uint64_t seq, ExecSync* sync) {
   const int ch = blockIdx.x, nch = gridDim.x;
   WaitCtx w;
   w.peers = &p.peers;
@@ -214,43 +266,77 @@ __device__ void ExecBody(const ExecParams& p, uint64_t seq, int* s_stop) {
   w.channel = ch;
   const uint64_t base = seq << 32;
   ControlPage* const me = Ctl(p.peers, p.rank);
+  volatile int* const stop = &sync->stop;
 
   // Entry barrier per channel: every peer's channel `ch` has started this
   // call, hence finished the previous one, so staging slots are free.
   if (threadIdx.x < p.world_size && threadIdx.x != p.rank) {
     StReleaseSys(&Ctl(p.peers, threadIdx.x)->bar[ch][p.rank], base | 1u);
-    if (!WaitGE(&me->bar[ch][threadIdx.x], base | 1u, w, kWaitBarrier, threadIdx.x, -1)) *s_stop = 1;
+    if (!WaitGE(&me->bar[ch][threadIdx.x], base | 1u, w, kWaitBarrier, threadIdx.x, -1)) *stop = 1;
   }
   __syncthreads();
-  if (*s_stop) return;
+  if (*stop) return;
 
   DeviceTraceRec* trace = (p.trace != nullptr && p.trace_capacity > 0) ? p.trace + static_cast<size_t>(ch) * p.trace_capacity : nullptr;
+  const int warps = static_cast<int>(blockDim.x) / 32;
+  const int data_warps = warps - 2;
+  const int warp = static_cast<int>(threadIdx.x) / 32, lane = static_cast<int>(threadIdx.x) % 32;
 
-  for (int oi = 0; oi < p.num_ops; ++oi) {
-    const Op op = p.ops[oi];
-    if (threadIdx.x == 0) {
-      bool ok = OpInBounds<W>(op, p);
-      if (!ok) {
-        ReportFailure(w, kStatusBadProgram, 0, -1, oi, op.elem_begin, op.elem_count);
-        BroadcastAbort(w);
-      }
-      if (ok && op.wait_in != 0) ok = WaitGE(&me->inflag[ch][op.peer_in], base | op.wait_in, w, kWaitData, op.peer_in, oi);
-      if (ok && op.wait_credit != 0)
-        ok = WaitGE(&me->credit[ch][op.peer_out], base | op.wait_credit, w, kWaitCredit, op.peer_out, oi);
-      if (!ok) *s_stop = 1;
-      if (trace != nullptr && oi < p.trace_capacity) trace[oi].t_wait_done = GlobalTimerNs();
+  if (warp < data_warps) {
+    const unsigned nthr = static_cast<unsigned>(data_warps) * 32u;
+    for (int oi = 0; oi < p.num_ops; ++oi) {
+      int go = 1;
+      if (lane == 0) go = SpinShared(&sync->ready, static_cast<unsigned>(oi) + 1u, sync, p.timeout_ns) ? 1 : 0;
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (!go) break;
+      const Op op = p.ops[oi];
+      // No barrier separates consecutive ops, and an element need not map to
+      // the same thread in two ops that cover different ranges.  An op that
+      // reads recvbuf (Rabenseifner's running partial sums, written by earlier
+      // ops) therefore first waits until every data warp has finished the ops
+      // before it.  Overwrites need no such barrier: a range is overwritten
+      // only by data that a peer derived from this rank's own transfer of the
+      // range, which the poster published after all data warps had read it.
+      if (op.src_a == kSrcRecv || op.src_b == kSrcRecv) asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
+      RunOpData<T, W>(op, p, ch, nch, threadIdx.x, nthr);
+      __syncwarp();
+      if (lane == 0) AddReleaseShared(&sync->done, 1u);
     }
-    __syncthreads();
-    if (*s_stop) return;
-    RunOpData<T, W>(op, p, ch, nch);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      if (op.post_out != 0) {
-        FenceSys();
-        StRelaxedSys(&Ctl(p.peers, op.peer_out)->inflag[ch][p.rank], base | op.post_out);
+  } else if (warp == data_warps) {
+    if (lane == 0) {
+      // Waiter: bounds check, then the op's data flag and slot credit.
+      for (int oi = 0; oi < p.num_ops && *stop == 0; ++oi) {
+        const Op op = p.ops[oi];
+        bool ok = OpInBounds<W>(op, p);
+        if (!ok) {
+          ReportFailure(w, kStatusBadProgram, 0, -1, oi, op.elem_begin, op.elem_count);
+          BroadcastAbort(w);
+        }
+        if (ok && op.wait_in != 0) ok = WaitGE(&me->inflag[ch][op.peer_in], base | op.wait_in, w, kWaitData, op.peer_in, oi);
+        if (ok && op.wait_credit != 0)
+          ok = WaitGE(&me->credit[ch][op.peer_out], base | op.wait_credit, w, kWaitCredit, op.peer_out, oi);
+        if (!ok) {
+          *stop = 1;
+          break;
+        }
+        if (trace != nullptr && oi < p.trace_capacity) trace[oi].t_wait_done = GlobalTimerNs();
+        StReleaseShared(&sync->ready, static_cast<unsigned>(oi) + 1u);
       }
-      if (op.post_credit != 0) StRelaxedSys(&Ctl(p.peers, op.peer_in)->credit[ch][p.rank], base | op.post_credit);
-      if (trace != nullptr && oi < p.trace_capacity) trace[oi].t_done = GlobalTimerNs();
+    }
+  } else {
+    if (lane == 0) {
+      // Poster: when all data warps have issued the op's stores, make them
+      // visible system-wide and publish the op's flags.
+      for (int oi = 0; oi < p.num_ops; ++oi) {
+        if (!SpinShared(&sync->done, static_cast<unsigned>(data_warps) * (static_cast<unsigned>(oi) + 1u), sync, p.timeout_ns)) break;
+        const Op op = p.ops[oi];
+        if (op.post_out != 0) {
+          FenceSys();
+          StRelaxedSys(&Ctl(p.peers, op.peer_out)->inflag[ch][p.rank], base | op.post_out);
+        }
+        if (op.post_credit != 0) StRelaxedSys(&Ctl(p.peers, op.peer_in)->credit[ch][p.rank], base | op.post_credit);
+        if (trace != nullptr && oi < p.trace_capacity) trace[oi].t_done = GlobalTimerNs();
+      }
     }
   }
 }
@@ -259,31 +345,31 @@ template <typename T, typename W>
 __global__ void __launch_bounds__(kExecThreads, 1)
 ExecKernel(const __grid_constant__ ExecParams p0, const ExecParams* __restrict__ emu) {
   __shared__ ExecParams p;
-  __shared__ int s_stop;
+  __shared__ ExecSync s_sync;
   __shared__ uint64_t s_seq;
   {
     const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y)
                                            : reinterpret_cast<const uint32_t*>(&p0);
     for (unsigned i = threadIdx.x; i < sizeof(ExecParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
-    if (threadIdx.x == 0) s_stop = 0;
+    if (threadIdx.x == 0) {
+      s_sync.ready = 0;
+      s_sync.done = 0;
+      s_sync.stop = 0;
+    }
   }
   __syncthreads();
   if (p.world_size <= 1) return;
   const uint64_t seq = BeginCollective(p.peers, p.rank, &s_seq);
   // num_ops <= 0: this rank sits the call out (test hook), but still counts it.
-  if (p.num_ops > 0) ExecBody<T, W>(p, seq, &s_stop);
+  if (p.num_ops > 0) ExecBody<T, W>(p, seq, &s_sync);
   EndCollective(p.peers, p.rank, seq, gridDim.x);
 }
 
 }  // namespace dev
 
 static int ExecThreads() {
-  static int threads = [] {
-    const char* s = getenv("IBCOMM_EXEC_THREADS");
-    int v = s ? atoi(s) : 0;
-    return (v >= 64 && v <= kExecThreads && v % 32 == 0) ? v : kExecThreads;
-  }();
-  return threads;
+  const int v = Tunable("IBCOMM_EXEC_THREADS", 0);
+  return (v >= 64 && v <= kExecThreads && v % 32 == 0) ? v : kExecThreads;
 }
 
 template <typename T, typename W>

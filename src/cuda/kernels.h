@@ -78,6 +78,37 @@ struct HybridParams {
 };
 cudaError_t LaunchHybridKernel(const HybridParams& h, int blocks, cudaStream_t stream);
 
+// ---- pipelined staged two-shot (staged_kernel.cu) ----
+// For buffers the peers cannot map, and for fp32 buffers that travel as
+// bf16/fp16: the message moves through the pool in windows, and inside one
+// CTA three warp groups work on three different windows at the same time
+// (copy in / reduce over NVLink / copy out), double-buffered.
+struct StagedParams {
+  int32_t rank;
+  int32_t world_size;
+  int32_t dtype;         // element type of the user buffers
+  int32_t wire;          // element type in the pool and on the wire (== dtype, or 16-bit for fp32 buffers)
+  int32_t use_multimem;  // 1: multimem.ld_reduce / multimem.st; 0: peer loads + peer stores
+  int32_t use_tma;       // 1: the local copies are bulk asynchronous copies (needs wire == dtype)
+  PeerTable peers;
+  const void* sendbuf;   // 16-byte aligned
+  void* recvbuf;         // 16-byte aligned
+  uint64_t len_elements; // a whole number of 16-byte wire vectors
+  double scale;
+  uint64_t window_elems; // elements per window (a whole number of vectors per rank and CTA)
+  uint64_t in_off[2];    // byte offsets of the two input windows inside every arena
+  uint64_t out_off[2];   // ... and of the two output windows
+  uint64_t timeout_ns;
+  DeviceStatus* status;
+  uint32_t* doorbell;
+  DeviceTraceRec* trace;   // [CTA][trace_capacity]: per window, when the reduce could start and when it was done
+  int32_t trace_capacity;  // 0 = tracing off
+  int32_t pad_;
+};
+cudaError_t LaunchStagedKernel(const StagedParams& p, const StagedParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
+// Largest grid of the staged kernel that is co-resident on `device` (0 on error).
+int StagedKernelMaxCoResidentBlocks(int device);
+
 // ---- reduce-scatter / all-gather (the halves of the two-shot allreduce) ----
 enum RsAgMode : int32_t { kRsAgReduceScatter = 1, kRsAgAllGather = 2 };
 struct RsAgParams {

@@ -25,6 +25,7 @@
 
 #include "flags.cuh"
 #include "ibcomm/communicator.h"
+#include "ibcomm/tunables.h"
 #include "kernels.h"
 #include "twoshot_common.cuh"
 #include "vec_ops.cuh"
@@ -184,11 +185,6 @@ __global__ void __launch_bounds__(kNvlsThreads, 1) NvlsKernel(const __grid_const
 
 }  // namespace dev
 
-static int EnvInt(const char* name, int dflt) {
-  const char* s = getenv(name);
-  return s ? atoi(s) : dflt;
-}
-
 template <typename T, int U, bool kMultimem, int kR>
 static cudaError_t LaunchNvlsU(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, int threads, cudaStream_t stream) {
   dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(emu != nullptr ? emu_ranks : 1));
@@ -203,8 +199,8 @@ static cudaError_t LaunchNvlsU(const NvlsParams& p, const NvlsParams* emu, int e
 template <typename T>
 static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
   // Tuning knobs for experiments: loads in flight per thread and CTA size.
-  static const int unroll = EnvInt("IBCOMM_NVLS_UNROLL", 4);
-  static const int threads_env = EnvInt("IBCOMM_NVLS_THREADS", dev::kNvlsThreads);
+  const int unroll = Tunable("IBCOMM_NVLS_UNROLL", 4);
+  const int threads_env = Tunable("IBCOMM_NVLS_THREADS", dev::kNvlsThreads);
   const int threads = (threads_env >= 64 && threads_env <= dev::kNvlsThreads && threads_env % 32 == 0) ? threads_env : dev::kNvlsThreads;
   if (!p.use_multimem) {
     // Direct variant: compiled per world-size class (loads in flight per rank).

@@ -82,21 +82,21 @@ __device__ __forceinline__ void CopyVectors(uint4* dst, const uint4* src, uint64
 // loads in registers).
 template <typename T, int kU, int kR, typename Store>
 __device__ __forceinline__ void PeerReduceUnits(unsigned char* const* peer, int ws, uint64_t off, uint64_t b, uint64_t e,
-                                                bool do_scale, double scale, Store store) {
+                                                bool do_scale, double scale, Store store, unsigned tid, unsigned nthr) {
   using A = typename Acc<T>::type;
   constexpr int kVecElems = 16 / static_cast<int>(sizeof(T));
-  for (uint64_t i = b + threadIdx.x; i < e; i += static_cast<uint64_t>(blockDim.x) * kU) {
+  for (uint64_t i = b + tid; i < e; i += static_cast<uint64_t>(nthr) * kU) {
     uint4 v[kU][kR];
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
-      const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+      const uint64_t idx = i + static_cast<uint64_t>(u) * nthr;
 #pragma unroll
       for (int q = 0; q < kR; ++q)
         if (q < ws && idx < e) v[u][q] = Ld16Strong(peer[q] + off + idx * 16);
     }
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
-      const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+      const uint64_t idx = i + static_cast<uint64_t>(u) * nthr;
       if (idx < e) {
         A acc[kVecElems];
         VecIO<T>::Load(v[u][0], acc);
@@ -115,10 +115,17 @@ __device__ __forceinline__ void PeerReduceUnits(unsigned char* const* peer, int 
 
 // The kernels are compiled per world-size class kR (2, 4 or 8 ranks at most)
 // with 8 / kR vectors in flight per rank: 2 ranks x 4 vectors, 4 x 2, 8 x 1.
+// The whole CTA takes part ...
 template <typename T, int kR, typename Store>
 __device__ __forceinline__ void PeerReduce(unsigned char* const* peer, int ws, uint64_t off, uint64_t b, uint64_t e,
                                            bool do_scale, double scale, Store store) {
-  PeerReduceUnits<T, kMaxRanks / kR, kR>(peer, ws, off, b, e, do_scale, scale, store);
+  PeerReduceUnits<T, kMaxRanks / kR, kR>(peer, ws, off, b, e, do_scale, scale, store, threadIdx.x, blockDim.x);
+}
+// ... or a group of `nthr` threads of it, numbered `tid` = 0 .. nthr - 1.
+template <typename T, int kR, typename Store>
+__device__ __forceinline__ void PeerReduceGroup(unsigned char* const* peer, int ws, uint64_t off, uint64_t b, uint64_t e,
+                                                bool do_scale, double scale, Store store, unsigned tid, unsigned nthr) {
+  PeerReduceUnits<T, kMaxRanks / kR, kR>(peer, ws, off, b, e, do_scale, scale, store, tid, nthr);
 }
 inline int RankClass(int world_size) { return world_size <= 2 ? 2 : (world_size <= 4 ? 4 : kMaxRanks); }
 

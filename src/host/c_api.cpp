@@ -7,6 +7,7 @@
 #include "ibcomm/communicator.h"
 #include "ibcomm/device_context.h"
 #include "ibcomm/schedule.h"
+#include "ibcomm/tunables.h"
 #ifdef USE_CUDA
 #include <cuda_runtime.h>
 
@@ -575,6 +576,20 @@ int ibcomm_parse_number(const char* text, int64_t* out) {
 }
 
 int ibcomm_get_exp_of_two(uint64_t n) { return util::GetExpOfTwo(n); }
+
+int ibcomm_set_tunable(const char* name, int value) {
+  return Guard([&] {
+    if (name == nullptr || name[0] == '\0') IBCOMM_FAIL(INVALID_ARGUMENT, "ibcomm_set_tunable: empty name.\n");
+    ibcomm::SetTunable(name, value);
+  });
+}
+
+int ibcomm_get_tunable(const char* name, int dflt, int* out) {
+  return Guard([&] {
+    if (name == nullptr || out == nullptr) IBCOMM_FAIL(INVALID_ARGUMENT, "ibcomm_get_tunable: null argument.\n");
+    *out = ibcomm::Tunable(name, dflt);
+  });
+}
 
 int ibcomm_split_buffer(size_t len_elements, size_t elem_bytes, size_t world_size, int64_t chunk_bytes, uint64_t* pairs,
                         size_t capacity, size_t* count) {

@@ -3,6 +3,8 @@
 #include <algorithm>
 #include <cstdio>
 
+#include "ibcomm/tunables.h"
+
 namespace ibcomm {
 
 namespace {
@@ -142,19 +144,35 @@ void BuildRing(Builder* bld) {
     const std::vector<int>& b = blocks[static_cast<size_t>(blk)];
     return i < b.size() ? b[b.size() - 1 - i] : -1;
   };
-  for (size_t i = 0; i < positions; ++i) {
-    int c = at(r, i);
-    if (c >= 0) bld->Send(bld->ChunkRange(c), kSrcSend, to);
+  // Chunks at the same position of their blocks form a chain: every op of a
+  // chain waits for the op the upstream rank ran one step earlier.  Chains
+  // are independent of each other, so a group of them is walked step by step
+  // (all chains' step k before any chain's step k + 1): while one chain's
+  // flag travels, the CTA moves the others' data.  A group of g chains keeps
+  // up to g transfers ahead of the downstream rank's receives, so it needs
+  // g + 1 staging slots (with g slots every rank would wait for a credit that
+  // its neighbour can only return after the same wait).
+  const size_t group = std::max<size_t>(1, std::min<size_t>(positions, bld->slots > 1 ? bld->slots - 1 : 1));
+  for (size_t i0 = 0; i0 < positions; i0 += group) {
+    const size_t i1 = std::min(positions, i0 + group);
+    for (size_t i = i0; i < i1; ++i) {
+      const int c = at(r, i);
+      if (c >= 0) bld->Send(bld->ChunkRange(c), kSrcSend, to);
+    }
     for (int k = 0; k <= ws - 2; ++k) {  // reduce-scatter
-      c = at(Mod(r - 1 - k, ws), i);
-      if (c < 0) continue;
       const bool final_step = (k == ws - 2);
-      bld->Recv(bld->ChunkRange(c), from, kSrcSend, /*store_local=*/final_step, /*scale=*/final_step, to);
+      for (size_t i = i0; i < i1; ++i) {
+        const int c = at(Mod(r - 1 - k, ws), i);
+        if (c < 0) continue;
+        bld->Recv(bld->ChunkRange(c), from, kSrcSend, /*store_local=*/final_step, /*scale=*/final_step, to);
+      }
     }
     for (int k = 0; k <= ws - 2; ++k) {  // all-gather
-      c = at(Mod(r - k, ws), i);
-      if (c < 0) continue;
-      bld->Recv(bld->ChunkRange(c), from, kSrcNone, true, false, k != ws - 2 ? to : -1);
+      for (size_t i = i0; i < i1; ++i) {
+        const int c = at(Mod(r - k, ws), i);
+        if (c < 0) continue;
+        bld->Recv(bld->ChunkRange(c), from, kSrcNone, true, false, k != ws - 2 ? to : -1);
+      }
     }
   }
 }
@@ -306,13 +324,15 @@ Program BuildProgram(const ProgramRequest& req) {
 }
 
 std::vector<Range> SplitForDevice(size_t len_elements, size_t elem_bytes, size_t world_size,
-                                  int64_t env_chunk_bytes, size_t max_chunk_bytes) {
+                                  int64_t env_chunk_bytes, size_t max_chunk_bytes, size_t chunks_per_rank) {
   std::vector<Range> base = SplitBuffer(len_elements, elem_bytes, world_size, env_chunk_bytes);
   const size_t vec_elems = 128 / elem_bytes;
   if (env_chunk_bytes <= 0) {
-    size_t per = util::ceilDiv(len_elements, 4 * world_size);
-    if (per >= 4 * vec_elems && per % vec_elems != 0) {
-      per = util::ceilDiv(per, vec_elems) * vec_elems;
+    if (chunks_per_rank < 1) chunks_per_rank = 1;
+    size_t per = util::ceilDiv(len_elements, chunks_per_rank * world_size);
+    const bool round = per >= 4 * vec_elems && per % vec_elems != 0;
+    if (round) per = util::ceilDiv(per, vec_elems) * vec_elems;
+    if (round || chunks_per_rank != 4) {
       base.clear();
       for (size_t b = 0; b < len_elements; b += per) base.emplace_back(b, std::min(len_elements, b + per));
     }
@@ -334,6 +354,16 @@ std::vector<Range> SplitForDevice(size_t len_elements, size_t elem_bytes, size_t
     }
   }
   return out;
+}
+
+size_t RingChunksPerRank(size_t len_elements, size_t elem_bytes, size_t world_size) {
+  const int positions = Tunable("IBCOMM_RING_POSITIONS", 4);
+  size_t cpr = positions >= 1 && positions <= 64 ? static_cast<size_t>(positions) : 4;
+  const int min_env = Tunable("IBCOMM_RING_MIN_CHUNK", 16384);
+  const size_t min_chunk = min_env > 0 ? static_cast<size_t>(min_env) : 1;
+  const size_t bytes = len_elements * elem_bytes;
+  while (cpr > 1 && bytes / (cpr * world_size) < min_chunk) --cpr;
+  return cpr;
 }
 
 uint64_t TwoShotWindowElems(uint64_t n, uint64_t cap_elems, size_t esize, int world_size, int channels) {

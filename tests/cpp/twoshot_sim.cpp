@@ -1,5 +1,5 @@
 // CPU-thread model of the staged two-shot protocols (nvls_kernel.cu,
-// rsag_kernel.cu), of the one-shot protocol (oneshot_kernel.cu) and of the
+// rsag_kernel.cu, and the pipelined staged_kernel.cu with its three roles per CTA), of the one-shot protocol (oneshot_kernel.cu) and of the
 // mailbox protocol of device Send/Recv (p2p_sendrecv.cu): one thread per (rank,
 // CTA), the pool windows, push slots and mailboxes as plain arrays, the per-CTA
 // cross-rank barriers, flags and credits as release/acquire atomics.  It uses
@@ -125,6 +125,105 @@ bool RunAllreduce(int ws, int ncta, uint64_t n, uint64_t cap_elems) {
   if (bad.load() != 0)
     fprintf(stderr, "allreduce ws=%d ncta=%d n=%llu window=%llu: %d wrong elements\n", ws, ncta, static_cast<unsigned long long>(n),
             static_cast<unsigned long long>(window), bad.load());
+  return bad.load() == 0;
+}
+
+// ---- pipelined staged two-shot (staged_kernel.cu) ----
+// One thread per (rank, CTA, role): loader, reducer, storer.  Two input and
+// two output windows per rank; three flag rows per (rank, CTA, source).  The
+// waits and posts are the kernel's: loader k waits reduced >= k-1, reducer k
+// waits in_ready >= k+1 and out_free >= k-1, storer k waits reduced >= k+1.
+struct PipeWorld {
+  int ws, ncta;
+  std::vector<std::vector<int64_t>> in[2], out[2];
+  std::vector<std::atomic<uint64_t>> row[3];  // 0 in_ready, 1 reduced, 2 out_free
+  PipeWorld(int ws_, int ncta_, size_t window) : ws(ws_), ncta(ncta_) {
+    for (int j = 0; j < 2; ++j) {
+      in[j].assign(ws_, std::vector<int64_t>(window, -7));
+      out[j].assign(ws_, std::vector<int64_t>(window, -7));
+    }
+    for (auto& r : row) {
+      r = std::vector<std::atomic<uint64_t>>(static_cast<size_t>(ws_) * ncta_ * ws_);
+      for (auto& f : r) f.store(0);
+    }
+  }
+  std::atomic<uint64_t>& Flag(int which, int rank, int cta, int src) { return row[which][(static_cast<size_t>(rank) * ncta + cta) * ws + src]; }
+  void WaitAll(int which, int rank, int cta, uint64_t v) {
+    for (int q = 0; q < ws; ++q)
+      while (Flag(which, rank, cta, q).load(std::memory_order_acquire) < v) std::this_thread::yield();
+  }
+  void PostAll(int which, int rank, int cta, uint64_t v) {
+    for (int q = 0; q < ws; ++q) Flag(which, q, cta, rank).store(v, std::memory_order_release);
+  }
+};
+
+void PipeRole(PipeWorld* w, int role, uint64_t seq, int rank, int cta, const std::vector<int64_t>& send, std::vector<int64_t>* recv,
+              uint64_t total_nv, uint64_t full_nv) {
+  const int ws = w->ws, ncta = w->ncta;
+  const uint64_t base = seq << 32;
+  const uint64_t windows = (total_nv + full_nv - 1) / full_nv;
+  for (uint64_t k = 0; k < windows; ++k) {
+    const int j = static_cast<int>(k & 1);
+    const uint64_t v0 = k * full_nv, nv = std::min(full_nv, total_nv - v0);
+    if (role == 0) {
+      if (k >= 2) w->WaitAll(1, rank, cta, base | (k - 1));
+      for (int s = 0; s < ws; ++s) {
+        uint64_t b, e;
+        WindowPart(full_nv, nv, s, ws, cta, ncta, &b, &e);
+        for (uint64_t i = b * kVec; i < e * kVec; ++i) w->in[j][rank][i] = send[v0 * kVec + i];
+      }
+      w->PostAll(0, rank, cta, base | (k + 1));
+    } else if (role == 1) {
+      w->WaitAll(0, rank, cta, base | (k + 1));
+      if (k >= 2) w->WaitAll(2, rank, cta, base | (k - 1));
+      uint64_t b, e;
+      WindowPart(full_nv, nv, rank, ws, cta, ncta, &b, &e);
+      for (uint64_t i = b * kVec; i < e * kVec; ++i) {
+        int64_t acc = 0;
+        for (int q = 0; q < ws; ++q) acc += w->in[j][q][i];
+        for (int q = 0; q < ws; ++q) w->out[j][q][i] = acc;
+      }
+      w->PostAll(1, rank, cta, base | (k + 1));
+    } else {
+      w->WaitAll(1, rank, cta, base | (k + 1));
+      for (int s = 0; s < ws; ++s) {
+        uint64_t b, e;
+        WindowPart(full_nv, nv, s, ws, cta, ncta, &b, &e);
+        for (uint64_t i = b * kVec; i < e * kVec; ++i) (*recv)[v0 * kVec + i] = w->out[j][rank][i];
+      }
+      w->PostAll(2, rank, cta, base | (k + 1));
+    }
+  }
+}
+
+bool RunPipelined(int ws, int ncta, uint64_t n_vec, uint64_t cap_elems) {
+  const uint64_t n = n_vec * kVec;
+  const uint64_t window = TwoShotWindowElems(n, cap_elems, 16 / kVec, ws, ncta);
+  const uint64_t full_nv = window / kVec;
+  if (full_nv == 0) return true;
+  PipeWorld w(ws, ncta, window);
+  std::vector<std::vector<int64_t>> send(ws, std::vector<int64_t>(n)), recv(ws, std::vector<int64_t>(n, -1));
+  for (int r = 0; r < ws; ++r)
+    for (uint64_t i = 0; i < n; ++i) send[r][i] = Value(r, i);
+  std::atomic<int> bad{0};
+  auto rank_body = [&](int r) {
+    // Three calls back to back; the ranks are not synchronised in between.
+    for (uint64_t seq = 1; seq <= 3; ++seq) {
+      std::fill(recv[r].begin(), recv[r].end(), -1);
+      std::vector<std::thread> t;
+      for (int c = 0; c < ncta; ++c)
+        for (int role = 0; role < 3; ++role) t.emplace_back(PipeRole, &w, role, seq, r, c, std::cref(send[r]), &recv[r], n_vec, full_nv);
+      for (auto& x : t) x.join();
+      for (uint64_t i = 0; i < n; ++i)
+        if (recv[r][i] != Sum(ws, i)) ++bad;
+    }
+  };
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < ws; ++r) ranks.emplace_back(rank_body, r);
+  for (auto& t : ranks) t.join();
+  if (bad.load() != 0)
+    fprintf(stderr, "pipelined ws=%d ncta=%d nvec=%llu window=%llu: %d wrong elements\n", ws, ncta,
+            static_cast<unsigned long long>(n_vec), static_cast<unsigned long long>(window), bad.load());
   return bad.load() == 0;
 }
 
@@ -438,6 +537,14 @@ MINI_TEST(StagedReduceScatterAllGatherProtocol) {
         CHECK_TRUE(RunRsAg(ws, ncta, block_units, 64));
 }
 
+MINI_TEST(PipelinedStagedProtocol) {
+  // Windows of 256 elements (64 vectors): messages of one to nine windows, the last one short.
+  for (int ws : {2, 3, 4})
+    for (int ncta : {1, 2, 3})
+      for (uint64_t nvec : {uint64_t(1), uint64_t(9), uint64_t(64), uint64_t(65), uint64_t(200), uint64_t(513)})
+        CHECK_TRUE(RunPipelined(ws, ncta, nvec, 256));
+}
+
 MINI_TEST(HybridSplitProtocol) {
   for (int ws : {2, 3, 4})
     for (int na : {1, 2})
@@ -462,6 +569,7 @@ MINI_TEST(RandomStagedConfigurations) {
     const uint64_t cap = pick(4, 40) * 16;  // a whole number of vectors
     CHECK_TRUE(RunAllreduce(ws, ncta, pick(static_cast<uint64_t>(ws), 6 * cap), cap));
     CHECK_TRUE(RunRsAg(ws, ncta, pick(1, 6 * cap / kVec), cap / kVec));
+    if (it % 4 == 0) CHECK_TRUE(RunPipelined(std::min(ws, 4), std::min(ncta, 3), pick(1, 6 * cap / kVec), cap));
   }
 }
 

@@ -149,6 +149,77 @@ def test_direct_two_shot(ws):
     w.set_direct_staging(0)
 
 
+@pytest.mark.parametrize("ws", [2, 3, 4, 8])
+def test_pipelined_staged_two_shot(ws):
+    # The pipelined kernel for buffers that go through the pool (loader, reducer and storer warps of a CTA on
+    # three windows at once).  2 MiB of staging = four windows of 512 KiB, so the larger messages take many
+    # windows (the last one short); copies by the bulk copy engine and, with the knob off, in registers.
+    w = world(ws, 1 << 20, 1 << 20)
+    w.set_direct_staging(2)
+    try:
+        for tma in (1, 0):
+            ar.utils.set_tunable("IBCOMM_STAGED_TMA", tma)
+            for dtype in (torch.float32, torch.bfloat16, torch.int32, torch.float64):
+                for n in (8 * ws, 4096, 65536 + 8, 300000, 1 << 20, (1 << 20) + 12344):
+                    ins = make_inputs(ws, n, dtype, seed=n + ws)
+                    scale = 0.5 if dtype != torch.int32 else 1.0
+                    want = reference(ins, scale, dtype)
+                    outs = [torch.zeros(n, device="cuda", dtype=dtype) for _ in range(ws)]
+                    for channels in ((0,) if n < (1 << 20) else (0, 1, 3)):
+                        w.allreduce(ins, outs, algo="direct", scale=scale, channels=channels)
+                        check(outs, want, dtype, ws)
+            # in place, several calls back to back without a host synchronisation in between
+            bufs = make_inputs(ws, 500000, torch.float32, seed=3)
+            want = reference(bufs, 1.0, torch.float32)
+            w.allreduce(bufs, None, algo="direct")
+            check(bufs, want, torch.float32, ws)
+            ins = make_inputs(ws, 700000, torch.float32, seed=4)
+            outs = [torch.zeros(700000, device="cuda") for _ in range(ws)]
+            for _ in range(5):
+                w.allreduce(ins, outs, algo="direct", sync=False)
+            torch.cuda.synchronize()
+            check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+    finally:
+        ar.utils.set_tunable("IBCOMM_STAGED_TMA", -1)
+        w.set_direct_staging(0)
+
+
+@pytest.mark.parametrize("wire", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("ws", [2, 4, 8])
+def test_two_shot_with_16_bit_wire(ws, wire):
+    # fp32 buffers, 16-bit values in the pool and on the wire, fp32 sums: the direct two-shot through the
+    # pipelined kernel.  Every rank must end up with the same bits.
+    w = world(ws, 1 << 20, 1 << 20)
+    for n in (8 * ws, 65536, 300000, (1 << 20) + 8):
+        ins = make_inputs(ws, n, torch.float32, seed=n)
+        outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+        w.allreduce(ins, outs, algo="direct", wire=wire, scale=1.0 / ws)
+        check(outs, reference(ins, 1.0 / ws, torch.float32), torch.float32, ws, wire=wire)
+        for o in outs[1:]:
+            assert torch.equal(o, outs[0])
+
+
+def test_pipelined_staged_wait_runs_out():
+    # A rank that takes no part: the others' loaders, reducers and storers give up after the limit, the kernel
+    # returns, the status names the wait, and the world stays usable.
+    ws = 4
+    w = ar.EmuWorld(ws, 1 << 20, 1 << 20)
+    w.set_direct_staging(2)
+    w.set_timeout_ms(200)
+    n = 1 << 16
+    ins = make_inputs(ws, n, torch.float32)
+    outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+    w.set_silent_rank(1)
+    with pytest.raises(ar.IbcommError) as e:
+        w.allreduce(ins, outs, algo="direct")
+    assert e.value.code == ar.TRANSPORT_ERROR
+    assert w.last_status()["code"] in (1, 2)
+    w.set_silent_rank(-1)
+    w.set_timeout_ms(5000)
+    w.allreduce(ins, outs, algo="direct")
+    check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+
+
 def test_unaligned_buffers_take_the_scalar_path():
     ws = 3
     w = world(ws)

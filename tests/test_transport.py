@@ -28,7 +28,7 @@ def test_schedule_simulator_under_thread_sanitizer(tmp_path):
         pytest.skip("no g++")
     exe = tmp_path / "schedule_sim_tsan"
     srcs = ["tests/cpp/schedule_sim.cpp"] + [f"src/host/{n}.cpp" for n in
-            ("error", "env", "partition", "schedule", "shm_transport", "trace", "communicator")]
+            ("error", "env", "partition", "schedule", "tunables", "shm_transport", "trace", "communicator")]
     cmd = ["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", "-w", f"-I{root / 'include'}", f"-I{root / 'tests' / 'cpp'}",
            *[str(root / s) for s in srcs], "-o", str(exe), "-pthread", "-lrt"]
     b = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
@@ -59,7 +59,7 @@ def test_two_shot_window_protocol_under_thread_sanitizer(tmp_path):
         pytest.skip("no g++")
     exe = tmp_path / "twoshot_sim_tsan"
     srcs = ["tests/cpp/twoshot_sim.cpp"] + [f"src/host/{n}.cpp" for n in
-            ("error", "env", "partition", "schedule", "shm_transport", "trace", "communicator")]
+            ("error", "env", "partition", "schedule", "tunables", "shm_transport", "trace", "communicator")]
     cmd = ["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", "-w", f"-I{root / 'include'}", f"-I{root / 'tests' / 'cpp'}",
            *[str(root / s) for s in srcs], "-o", str(exe), "-pthread", "-lrt"]
     b = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
