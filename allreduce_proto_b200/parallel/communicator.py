@@ -126,15 +126,25 @@ class Communicator:
         self.barrier()
 
     @classmethod
-    def from_torch_distributed(cls, group=None, tag: str = "c0") -> "Communicator":
+    def from_torch_distributed(cls, group=None, tag: str = "c0", ranks=None) -> "Communicator":
         """Builds a connected communicator from an initialised ``torch.distributed`` job.
 
         The descriptors travel through the job's key-value store (host only; no
-        collective of the backend is used)."""
+        collective of the backend is used).
+
+        ``ranks``: build the communicator over this subset of the job's ranks only (every member
+        calls with the same list; the other ranks do not call); a rank's number in the new
+        communicator is its position in the list."""
         import torch.distributed as dist
         if not dist.is_initialized():
             raise IbcommError(_native.INVALID_ARGUMENT, "torch.distributed is not initialised")
         rank, ws = dist.get_rank(group), dist.get_world_size(group)
+        if ranks is not None:
+            ranks = [int(r) for r in ranks]
+            if rank not in ranks or len(set(ranks)) != len(ranks) or any(r < 0 or r >= ws for r in ranks):
+                raise IbcommError(_native.INVALID_ARGUMENT, f"rank {rank} builds a communicator over {ranks}")
+            tag = f"{tag}.sub" + "_".join(str(r) for r in ranks)
+            rank, ws = ranks.index(rank), len(ranks)
         comm = cls(ws, rank)
         if ws == 1:
             return comm

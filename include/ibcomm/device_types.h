@@ -25,6 +25,8 @@ namespace ibcomm {
 constexpr int kMaxRanks = 8;       // one NVSwitch box
 constexpr int kMaxChannels = 256;  // CTAs per rank a collective may use
 constexpr int kExecThreads = 512;  // threads per channel CTA
+constexpr int kP2pCtas = 32;       // CTAs of a device Send / Recv kernel (each owns a fixed part of every mailbox slot)
+constexpr int kP2pMaxSlots = 8;    // upper bound of mailbox slots per source rank
 
 // ---- control page at the start of every rank's arena (peer-writable) ----
 // All words are 64-bit, written by exactly one remote rank and polled locally.
@@ -36,9 +38,13 @@ struct ControlPage {
   uint64_t inflag[kMaxChannels][kMaxRanks];
   // credit[c][d]: number of my transfers rank d has consumed.
   uint64_t credit[kMaxChannels][kMaxRanks];
-  // Point-to-point mailbox counters, one per source / destination rank.
-  uint64_t p2p_flag[kMaxRanks];
-  uint64_t p2p_credit[kMaxRanks];
+  // Point-to-point mailbox counters per CTA of the Send / Recv kernels and
+  // per source / destination rank: cumulative piece numbers of the ordered
+  // pair.  p2p_len[s][slot]: byte length of the message from rank s whose
+  // first piece sits in `slot` (written before that piece's flag).
+  uint64_t p2p_flag[kP2pCtas][kMaxRanks];
+  uint64_t p2p_credit[kP2pCtas][kMaxRanks];
+  uint64_t p2p_len[kMaxRanks][kP2pMaxSlots];
   // Set (to the call sequence) by any rank that gave up; polled by waiters.
   uint64_t abort_seq;
   // Written only by this rank's own kernels: the number of collectives it has
@@ -62,6 +68,7 @@ enum DeviceStatusCode : uint32_t {
   kStatusWaitTimeout = 1,   // a flag did not arrive within the limit
   kStatusPeerAbort = 2,     // a peer (or another CTA) reported failure
   kStatusBadProgram = 3,    // self-check of an op failed (index out of range)
+  kStatusLengthMismatch = 4,  // a device Recv met a message of another length than it was posted for
 };
 enum DeviceWaitKind : uint32_t { kWaitBarrier = 1, kWaitData = 2, kWaitCredit = 3, kWaitP2p = 4, kWaitOneShot = 5 };
 

@@ -85,6 +85,16 @@ struct LoopbackSend {
   size_t len;
 };
 
+// Identity of one device message for the abort protocol: the same on the
+// sending and the receiving side, different for every message of every ordered
+// pair, and outside the range of the collectives' call numbers.  (A constant
+// per rank would make one timed-out message poison every later one: the abort
+// word keeps the last value written to it.)
+uint64_t P2pSeq(int src, int dst, uint64_t first_piece) {
+  return 0xFF00000000000000ull | (static_cast<uint64_t>(src) << 52) | (static_cast<uint64_t>(dst) << 48) |
+         (first_piece & 0xFFFFFFFFFFFFull);
+}
+
 // Share of a zero-copy switch allreduce that the hybrid kernel runs through
 // the direct algorithm, in percent (0 = plain switch kernel), when
 // IBCOMM_NVLS_HYBRID does not say.  Off until a sweep on the machine shows a
@@ -154,6 +164,10 @@ class DeviceContext {
   // call does not meet its requirements (nothing has been launched then).
   bool RunStaged(bool multimem, DType dtype, DType wire, const void* sendbuf, void* recvbuf, size_t n, double scale, int channels,
                  cudaStream_t stream);
+  // Caps a collective's CTAs at what the GPU holds at once (CTA b of this rank
+  // waits for CTA b of the peers) and at IBCOMM_MAX_CTAS when set (a program
+  // that overlaps collectives with compute leaves SMs to the compute).
+  int ClampChannels(Algo algo, int channels);
   // Begins a device trace record of `records` entries per channel (no-op when tracing is off).
   DeviceTraceRec* BeginDeviceTrace(int channels, int records, int* capacity);
   void ExchangeAllocation(SharedAllocation* mine, std::vector<std::unique_ptr<SharedAllocation>>* imported,
@@ -184,6 +198,8 @@ class DeviceContext {
   int last_algo_ = 0, last_channels_ = 0;
   int hybrid_channels_ = 0;  // CTAs of the hybrid two-shot kernel when the last call ran it
   int staged_channels_ = 0;  // CTAs of the pipelined staged kernel when the last call ran it
+  std::map<int, int> exec_resident_;  // executor CTA size -> co-resident CTAs on this device
+  int twoshot_resident_ = -1;
   int max_channels_ = env::kDefaultNumCudaStream;
   std::vector<P2pState> p2p_;
   std::vector<std::unique_ptr<SymmetricAlloc>> symm_;
@@ -633,6 +649,23 @@ void DeviceContext::RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, 
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
 }
 
+int DeviceContext::ClampChannels(Algo algo, int channels) {
+  int limit;
+  if (algo == Algo::kRing || algo == Algo::kRabenseifner) {
+    const int threads = ExecKernelThreadsFor(channels);
+    auto it = exec_resident_.find(threads);
+    if (it == exec_resident_.end()) it = exec_resident_.emplace(threads, ExecKernelMaxCoResidentBlocks(device_, threads)).first;
+    limit = it->second;
+  } else {
+    if (twoshot_resident_ < 0) twoshot_resident_ = TwoShotKernelMaxCoResidentBlocks(device_);
+    limit = twoshot_resident_;
+  }
+  if (limit > 0) channels = std::min(channels, limit);
+  const int cap = Tunable("IBCOMM_MAX_CTAS", 0);
+  if (cap > 0) channels = std::min(channels, cap);
+  return std::max(1, channels);
+}
+
 DeviceTraceRec* DeviceContext::BeginDeviceTrace(int channels, int records, int* capacity) {
   *capacity = 0;
   if (d_trace_ == nullptr || channels > trace_channels_) return nullptr;
@@ -677,6 +710,7 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   if (ctas <= 0) ctas = std::max(channels, ChooseChannels(Algo::kDirect, n * wsize, ws_, max_channels_));
   static const int resident = StagedKernelMaxCoResidentBlocks(device_);
   if (resident > 0) ctas = std::min(ctas, resident);
+  if (Tunable("IBCOMM_MAX_CTAS", 0) > 0) ctas = std::min(ctas, Tunable("IBCOMM_MAX_CTAS", 0));
   ctas = std::max(1, std::min(ctas, kMaxChannels));
   uint64_t cap_bytes = quarter;
   const int max_window = Tunable("IBCOMM_STAGED_WINDOW_KIB", 0);  // experiment knob: smaller windows
@@ -872,6 +906,15 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
     if (algo == Algo::kNvls && !(FindSymmetric(sendbuf, bytes) != nullptr && FindSymmetric(recvbuf, bytes) != nullptr))
       channels = std::max(channels, ChooseChannels(Algo::kDirect, bytes, ws_, max_channels_));
   }
+  {
+    // Experiment knobs: a fixed CTA count for the op executor / the two-shot kernels.
+    const char* knob = (algo == Algo::kRing || algo == Algo::kRabenseifner) ? "IBCOMM_EXEC_CHANNELS"
+                       : (algo == Algo::kNvls || algo == Algo::kDirect)    ? "IBCOMM_TWOSHOT_CHANNELS"
+                                                                            : nullptr;
+    const int forced = knob != nullptr ? Tunable(knob, 0) : 0;
+    if (forced > 0) channels = std::min(forced, kMaxChannels);
+  }
+  channels = ClampChannels(algo, channels);
   OrderAfterPrevious(stream);
   switch (algo) {
     case Algo::kRing:
@@ -980,7 +1023,7 @@ void DeviceContext::ReduceScatterOrAllGather(int mode, DType dtype, const void* 
     p.sub_stride_bytes = sub;
     p.window_elems = std::min<uint64_t>(block_elems, sub / esize);
   }
-  int channels = ChooseChannels(p.use_multimem && zero_copy ? Algo::kNvls : Algo::kDirect, remote_bytes, ws_, max_channels_);
+  int channels = ClampChannels(Algo::kDirect, ChooseChannels(p.use_multimem && zero_copy ? Algo::kNvls : Algo::kDirect, remote_bytes, ws_, max_channels_));
   if (p.staged) {
     // Equal windows, each a whole number of units per channel.
     const uint64_t cap = p.sub_stride_bytes / esize;
@@ -1029,11 +1072,11 @@ void DeviceContext::Send(int dest, const void* buf, size_t len) {
   p.slot_bytes = layout_.mailbox_slot_bytes;
   p.slots = layout_.mailbox_slots;
   p.first_piece = s.pieces_sent;
-  p.seq = 0xFFFFFFFF00000000ull | static_cast<uint64_t>(rank_);
+  p.seq = P2pSeq(rank_, dest, s.pieces_sent);
   p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
   p.status = rr_.d_status;
   p.doorbell = rr_.d_doorbell;
-  s.pieces_sent += (len + p.slot_bytes - 1) / p.slot_bytes;
+  s.pieces_sent += len == 0 ? 1 : (len + p.slot_bytes - 1) / p.slot_bytes;
   IBCOMM_TRACE(*tracer_, kTraceIssueSend);
   CUDACHECK(LaunchP2pKernel(p, send_stream_));
   ++kernel_launches_;
@@ -1076,11 +1119,11 @@ void DeviceContext::Recv(int src, void* buf, size_t len) {
   p.slot_bytes = layout_.mailbox_slot_bytes;
   p.slots = layout_.mailbox_slots;
   p.first_piece = s.pieces_received;
-  p.seq = 0xFFFFFFFF00000000ull | static_cast<uint64_t>(rank_);
+  p.seq = P2pSeq(src, rank_, s.pieces_received);
   p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
   p.status = rr_.d_status;
   p.doorbell = rr_.d_doorbell;
-  s.pieces_received += (len + p.slot_bytes - 1) / p.slot_bytes;
+  s.pieces_received += len == 0 ? 1 : (len + p.slot_bytes - 1) / p.slot_bytes;
   IBCOMM_TRACE(*tracer_, kTraceIssueRecv);
   CUDACHECK(LaunchP2pKernel(p, recv_stream_));
   ++kernel_launches_;

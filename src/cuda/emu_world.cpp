@@ -65,7 +65,7 @@ EmuWorld::EmuWorld(int num_ranks, size_t pool_bytes, size_t work_bytes) : ws_(nu
     rr.h_doorbell = m.status[static_cast<size_t>(r)].h_doorbell;
     rr.d_doorbell = m.status[static_cast<size_t>(r)].d_doorbell;
   }
-  m.max_blocks = ExecKernelMaxCoResidentBlocks(m.device);
+  m.max_blocks = ExecKernelMaxCoResidentBlocks(m.device, 0);
   m.staged_max_blocks = StagedKernelMaxCoResidentBlocks(m.device);
   CUDACHECK(cudaDeviceSynchronize());
 }

@@ -19,8 +19,18 @@ ArenaLayout MakeArenaLayout(size_t pool_bytes, size_t work_bytes) {
   l.oneshot_slot_bytes = 512u << 10;
   off += 2ull * kMaxRanks * l.oneshot_slot_bytes;
   l.mailbox_offset = off;
-  l.mailbox_slot_bytes = 256u << 10;
-  l.mailbox_slots = 2;
+  // Device Send/Recv mailboxes: per source rank a ring of slots.  2 MiB slots
+  // give each of the kP2pCtas CTAs of a message 64 KiB per piece, four slots
+  // keep the sender ahead of the receiver (knobs for experiments:
+  // IBCOMM_P2P_SLOT_KIB, IBCOMM_P2P_SLOTS; all ranks must agree).
+  {
+    int kib = Tunable("IBCOMM_P2P_SLOT_KIB", 2048);
+    if (kib < 16 || kib > (64 << 10)) kib = 2048;
+    int slots = Tunable("IBCOMM_P2P_SLOTS", 4);
+    if (slots < 2 || slots > kP2pMaxSlots) slots = 4;
+    l.mailbox_slot_bytes = static_cast<uint64_t>(kib) << 10;
+    l.mailbox_slots = static_cast<uint32_t>(slots);
+  }
   off += static_cast<uint64_t>(kMaxRanks) * l.mailbox_slots * l.mailbox_slot_bytes;
   l.pool_offset = off;
   l.pool_bytes = AlignUp(pool_bytes < 4096 ? 4096 : pool_bytes, 4096);
@@ -66,13 +76,13 @@ uint32_t StatusBlock::Consume(DeviceStatus* out, cudaStream_t stream) {
 }
 
 std::string DescribeStatus(const DeviceStatus& st) {
-  static const char* const codes[] = {"ok", "wait timed out", "aborted by a peer", "bad program"};
+  static const char* const codes[] = {"ok", "wait timed out", "aborted by a peer", "bad program", "message length mismatch"};
   static const char* const kinds[] = {"?", "barrier", "data flag", "slot credit", "mailbox", "one-shot flag"};
   char buf[320];
   snprintf(buf, sizeof(buf),
            "device collective failed: %s while waiting for a %s from rank %d (rank %d, channel %d, op %d, call %llu, "
            "expected %llu, saw %llu)",
-           codes[st.code < 4 ? st.code : 0], kinds[st.kind < 6 ? st.kind : 0], st.peer, st.rank, st.channel, st.op_index,
+           codes[st.code < 5 ? st.code : 0], kinds[st.kind < 6 ? st.kind : 0], st.peer, st.rank, st.channel, st.op_index,
            static_cast<unsigned long long>(st.seq), static_cast<unsigned long long>(st.expected & 0xffffffffull),
            static_cast<unsigned long long>(st.seen & 0xffffffffull));
   return buf;

@@ -30,6 +30,7 @@
 #include "ibcomm/tunables.h"
 #include "kernels.h"
 #include "vec_ops.cuh"
+#include "warp_roles.cuh"
 
 namespace ibcomm {
 namespace dev {
@@ -215,45 +216,10 @@ __device__ __forceinline__ bool OpInBounds(const Op& op, const ExecParams& p) {
   return true;
 }
 
-// Hand-over counters between the waiter, the data warps and the poster.
-struct ExecSync {
-  unsigned ready;  // ops whose flags have arrived (written by the waiter)
-  unsigned done;   // (data warp, op) pairs whose stores have been issued
-  int stop;        // a wait gave up or the program is bad: everybody leaves
-};
-
-__device__ __forceinline__ unsigned SmemU32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ unsigned LdAcquireShared(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(SmemU32(p)) : "memory");
-  return v;
-}
-__device__ __forceinline__ void StReleaseShared(unsigned* p, unsigned v) {
-  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(SmemU32(p)), "r"(v) : "memory");
-}
-__device__ __forceinline__ void AddReleaseShared(unsigned* p, unsigned v) {
-  asm volatile("red.release.cta.shared.add.u32 [%0], %1;" ::"r"(SmemU32(p)), "r"(v) : "memory");
-}
-
-// Spins until *counter >= target.  False when the call was stopped, or after
-// twice the wait limit (a safety net: the waiter's own limit fires first).
-__device__ __forceinline__ bool SpinShared(const unsigned* counter, unsigned target, ExecSync* sync, uint64_t timeout_ns) {
-  if (LdAcquireShared(counter) >= target) return true;
-  const uint64_t t0 = GlobalTimerNs();
-  for (uint32_t spin = 1;; ++spin) {
-    if (LdAcquireShared(counter) >= target) return true;
-    if (*reinterpret_cast<volatile int*>(&sync->stop) != 0) return false;
-    if ((spin & 1023u) == 0u && GlobalTimerNs() - t0 > 2 * timeout_ns) {
-      *reinterpret_cast<volatile int*>(&sync->stop) = 1;
-      return false;
-    }
-  }
-}
-
 // Body of the executor for one CTA: warps [0, data_warps) move data, lane 0 of
 // the next warp is the waiter, lane 0 of the last warp the poster.
 template <typename T, typename W>
-__device__ void ExecBody(const ExecParams& p, uint64_t seq, ExecSync* sync) {
+__device__ void ExecBody(const ExecParams& p, uint64_t seq, RoleSync* sync) {
   const int ch = blockIdx.x, nch = gridDim.x;
   WaitCtx w;
   w.peers = &p.peers;
@@ -345,7 +311,7 @@ template <typename T, typename W>
 __global__ void __launch_bounds__(kExecThreads, 1)
 ExecKernel(const __grid_constant__ ExecParams p0, const ExecParams* __restrict__ emu) {
   __shared__ ExecParams p;
-  __shared__ ExecSync s_sync;
+  __shared__ RoleSync s_sync;
   __shared__ uint64_t s_seq;
   {
     const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y)
@@ -377,7 +343,7 @@ static cudaError_t Launch(const ExecParams& p, const ExecParams* emu, int emu_ra
   dim3 grid(static_cast<unsigned>(channels), static_cast<unsigned>(emu != nullptr ? emu_ranks : 1));
   // Beyond one CTA per SM, two smaller CTAs share an SM: while one waits for a
   // flag, the other streams.
-  const int kThreads = (channels > 148 && ExecThreads() > 256) ? 256 : ExecThreads();
+  const int kThreads = ExecKernelThreadsFor(channels);
   if (emu != nullptr) {
     // Ranks sharing one GPU wait on each other inside this launch: it must be
     // cooperative so the runtime refuses a grid that cannot be co-resident.
@@ -401,9 +367,12 @@ cudaError_t LaunchExecKernel(const ExecParams& p, const ExecParams* emu, int emu
   return cudaErrorInvalidValue;
 }
 
-int ExecKernelMaxCoResidentBlocks(int device) {
+int ExecKernelThreadsFor(int channels) { return (channels > 148 && ExecThreads() > 256) ? 256 : ExecThreads(); }
+
+int ExecKernelMaxCoResidentBlocks(int device, int threads) {
   int per_sm = 0, sms = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dev::ExecKernel<float, float>, kExecThreads, 0) != cudaSuccess) return 0;
+  if (threads <= 0) threads = kExecThreads;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dev::ExecKernel<float, float>, threads, 0) != cudaSuccess) return 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
   return per_sm * sms;
 }

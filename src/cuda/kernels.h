@@ -12,7 +12,12 @@ namespace ibcomm {
 // `emu` == nullptr: one rank, grid = channels.  Otherwise `emu` points to
 // `emu_ranks` parameter blocks in device memory and the launch is cooperative.
 cudaError_t LaunchExecKernel(const ExecParams& p, const ExecParams* emu, int emu_ranks, int channels, cudaStream_t stream);
-int ExecKernelMaxCoResidentBlocks(int device);
+// CTA size the executor uses for a grid of `channels` CTAs, and the largest
+// grid of CTAs of `threads` threads (0 = the full-size CTA) that is co-resident
+// on `device` (0 on error).  CTA b of a rank waits for CTA b of the other
+// ranks, so a collective never launches more CTAs than fit at once.
+int ExecKernelThreadsFor(int channels);
+int ExecKernelMaxCoResidentBlocks(int device, int threads = 0);
 
 // ---- world_size == 1, and local staging: out = cast(in * scale) ----
 // Uses bulk asynchronous copies (TMA, non-tensor form) through shared memory.
@@ -66,6 +71,8 @@ struct NvlsParams {
   uint32_t* doorbell;
 };
 cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
+// Largest co-resident grid of the two-shot kernels (they share CTA size and register budget).
+int TwoShotKernelMaxCoResidentBlocks(int device);
 
 // Hybrid two-shot (hybrid_kernel.cu): zero-copy symmetric buffers; CTAs
 // [0, nvls_ctas) reduce 16-byte vectors [0, split_vec) in the switch, the other

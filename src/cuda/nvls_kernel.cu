@@ -219,6 +219,13 @@ static cudaError_t LaunchNvlsTyped(const NvlsParams& p, const NvlsParams* emu, i
   }
 }
 
+int TwoShotKernelMaxCoResidentBlocks(int device) {
+  int per_sm = 0, sms = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dev::NvlsKernel<float, 4, false, kMaxRanks>, dev::kNvlsThreads, 0) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+  return per_sm * sms;
+}
+
 cudaError_t LaunchNvlsKernel(const NvlsParams& p, const NvlsParams* emu, int emu_ranks, int blocks, cudaStream_t stream) {
   const DType t = static_cast<DType>(p.dtype);
   if (p.use_multimem && !(t == DType::kFloat32 || t == DType::kFloat16 || t == DType::kBFloat16)) return cudaErrorInvalidValue;
