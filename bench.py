@@ -388,6 +388,292 @@ def strided_error(out, n: int, world: int, scale: float, dev, stride: int = 61) 
     return float((out[idx].double() - want).abs().max().item())
 
 
+def nccl_registered_pair(n: int, dev):
+    """Two fp32 tensors of `n` elements in memory that NCCL itself allocated and registered
+    (`ncclMemAlloc` through torch's MemPool, then `register_mem_pool`), so that NCCL's zero-copy
+    (user-buffer registration, in-switch) paths apply to it: the counterpart of `symmetric_empty`.
+    Returns (in, out, note); (None, None, reason) when this torch / NCCL cannot do it."""
+    import torch
+    import torch.distributed as dist
+    try:
+        backend = dist.group.WORLD._get_backend(dev)
+        pool = torch.cuda.MemPool(backend.mem_allocator)
+        with torch.cuda.use_mem_pool(pool):
+            a = torch.empty(n, dtype=torch.float32, device=dev)
+            b = torch.empty(n, dtype=torch.float32, device=dev)
+        backend.register_mem_pool(pool)
+        return a, b, "ncclMemAlloc pool registered with the communicator"
+    except Exception as e:  # noqa: BLE001 - reported, not fatal
+        return None, None, f"unavailable: {type(e).__name__}: {e}"
+
+
+def tune(args, comm, world, rank, dev, time_steps) -> int:
+    """Sweeps the knobs of the kernels inside one process launch (a launch of N ranks costs far more than a
+    timed configuration).  One JSON line per configuration in --out; rank 0 prints a summary line."""
+    import torch
+    import torch.distributed as dist
+
+    from allreduce_proto_b200.utils import busbw_gbs, set_tunable
+
+    if world < 2:
+        if rank == 0:
+            print(json.dumps({"tune": None, "reason": "needs at least two GPUs"}))
+        return 0
+    sections = [x for x in args.tune.split(",") if x] or ["hybrid", "staged", "wire", "exec", "small", "nccl"]
+    out_path = args.out or f"bench_out/tune_{world}gpu.jsonl"
+    n = args.elements
+    nbytes = n * 4
+    scale = 1.0 / world
+    info = comm.device_info(connect=True)
+    sym_in = comm.symmetric_empty(n, torch.float32)
+    sym_out = comm.symmetric_empty(n, torch.float32)
+    plain_in = seeded_input(n, rank, dev)
+    plain_out = torch.empty_like(plain_in)
+    sym_in.copy_(plain_in)
+    steps, warm = max(5, args.steps // 2), max(3, args.warmup)
+    rows = []
+
+    def run(section, name, fn, knobs=None, check=None, size=nbytes, k=steps, w=warm):
+        knobs = knobs or {}
+        for key, v in knobs.items():
+            set_tunable(key, v)
+        row = {"section": section, "name": name, "knobs": knobs, "bytes": size, "n_gpus": world}
+        try:
+            t = time_steps(fn, k, w)
+            comm.check()
+            row.update({"ms": t, "busbw_gbs": busbw_gbs(size, t / 1e3, world), "algo": comm.device_info()["last_algo"],
+                        "channels": comm.device_info()["last_channels"]})
+            if check is not None:
+                row["max_abs_err"] = strided_error(check, size // 4, world, scale, dev)
+        except Exception as e:  # noqa: BLE001 - a configuration may be unsupported
+            row["error"] = str(e)
+        finally:
+            for key in knobs:
+                set_tunable(key, -1)
+        rows.append(row)
+        return row
+
+    def allreduce(a, b, algo, wire=None):
+        return lambda: comm.allreduce(a, b, algo=algo, scale=scale, wire=wire)
+
+    if "nccl" in sections:
+        buf = plain_in.clone()
+        run("nccl", "nccl_plain", lambda: dist.all_reduce(buf))
+        ra, rb, note = nccl_registered_pair(n, dev)
+        if ra is not None:
+            ra.copy_(plain_in)
+            r = run("nccl", "nccl_registered", lambda: dist.all_reduce(ra))
+            r["note"] = note
+        else:
+            rows.append({"section": "nccl", "name": "nccl_registered", "error": note})
+        del buf
+    if "hybrid" in sections and info["nvls"]:
+        run("hybrid", "nvls_zero_copy", allreduce(sym_in, sym_out, "nvls"), {"IBCOMM_NVLS_HYBRID": 0}, check=sym_out)
+        run("hybrid", "direct_zero_copy", allreduce(sym_in, sym_out, "direct"), check=sym_out)
+        splits = ((32, 96), (48, 96), (64, 84), (48, 64), (24, 120)) if world > 2 else ((48, 96), (32, 112))
+        for pct in (10, 15, 20, 25, 30, 35, 40, 50):
+            for a, b in splits:
+                run("hybrid", f"hybrid_{pct}_{a}_{b}", allreduce(sym_in, sym_out, "nvls"),
+                    {"IBCOMM_NVLS_HYBRID": pct, "IBCOMM_NVLS_HYBRID_SWITCH_CTAS": a, "IBCOMM_NVLS_HYBRID_DIRECT_CTAS": b},
+                    check=sym_out if (a, b) == splits[0] else None)
+        for ch in (32, 64, 96, 128):
+            run("hybrid", f"direct_zero_copy_ch{ch}", allreduce(sym_in, sym_out, "direct"), {"IBCOMM_TWOSHOT_CHANNELS": ch})
+    if "staged" in sections:
+        algos = ["direct"] + (["nvls"] if info["nvls"] else [])
+        for algo in algos:
+            run("staged", f"{algo}_sequential", allreduce(plain_in, plain_out, algo), {"IBCOMM_STAGED": 0}, check=plain_out)
+            for ctas in (64, 96, 128, 148):
+                for tma in (1, 0):
+                    run("staged", f"{algo}_pipelined_ctas{ctas}_tma{tma}", allreduce(plain_in, plain_out, algo),
+                        {"IBCOMM_STAGED_CTAS": ctas, "IBCOMM_STAGED_TMA": tma}, check=plain_out if ctas == 128 else None)
+            for kib in (4096, 8192, 16384):
+                run("staged", f"{algo}_pipelined_window{kib}KiB", allreduce(plain_in, plain_out, algo),
+                    {"IBCOMM_STAGED_WINDOW_KIB": kib})
+        for size in (1 << 20, 4 << 20, 16 << 20, 64 << 20):
+            m = size // 4
+            for algo in algos + ["auto", "ring", "rabenseifner"]:
+                run("staged", f"{algo}_plain_{size >> 20}MiB", allreduce(plain_in[:m], plain_out[:m], algo), size=size, k=30, w=5)
+            nb = plain_in[:m].clone()
+            run("staged", f"nccl_{size >> 20}MiB", lambda: dist.all_reduce(nb), size=size, k=30, w=5)
+    if "wire" in sections:
+        for algo in ["ring", "rabenseifner", "direct"] + (["nvls"] if info["nvls"] else []):
+            for wire in (torch.bfloat16, torch.float16):
+                r = run("wire", f"{algo}_{str(wire).split('.')[-1]}_wire", allreduce(plain_in, plain_out, algo, wire=wire))
+                if "error" not in r:
+                    r["max_abs_err"] = strided_error(plain_out, n, world, scale, dev)
+        if info["nvls"]:
+            for ctas in (64, 96, 148):
+                run("wire", f"nvls_bfloat16_wire_ctas{ctas}", allreduce(plain_in, plain_out, "nvls", wire=torch.bfloat16),
+                    {"IBCOMM_STAGED_CTAS": ctas})
+    if "exec" in sections:
+        for algo in ("ring", "rabenseifner"):
+            for threads in (512, 256):
+                for ch in (64, 128, 148, 256):
+                    run("exec", f"{algo}_t{threads}_ch{ch}", allreduce(plain_in, plain_out, algo),
+                        {"IBCOMM_EXEC_THREADS": threads, "IBCOMM_EXEC_CHANNELS": ch}, check=plain_out if ch == 256 else None)
+        for pos in (2, 8):
+            run("exec", f"ring_positions{pos}", allreduce(plain_in, plain_out, "ring"), {"IBCOMM_RING_POSITIONS": pos}, check=plain_out)
+        for pieces in (2, 4, 16):
+            run("exec", f"rabenseifner_pieces{pieces}", allreduce(plain_in, plain_out, "rabenseifner"),
+                {"IBCOMM_RABEN_PIECES": pieces}, check=plain_out)
+    if "small" in sections:
+        for size in (4 << 10, 64 << 10, 1 << 20):
+            m = size // 4
+            for algo in ("ring", "rabenseifner", "oneshot", "auto"):
+                if algo == "oneshot" and size > (512 << 10):
+                    continue
+                run("small", f"{algo}_{size >> 10}KiB", allreduce(plain_in[:m], plain_out[:m], algo), size=size, k=200, w=20)
+            nb = plain_in[:m].clone()
+            run("small", f"nccl_{size >> 10}KiB", lambda: dist.all_reduce(nb), size=size, k=200, w=20)
+    if rank == 0:
+        os.makedirs(os.path.dirname(out_path) or ".", exist_ok=True)
+        with open(out_path, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+        best = {}
+        for r in rows:
+            if "ms" in r and r["bytes"] == nbytes and (r["section"] not in best or r["ms"] < best[r["section"]]["ms"]):
+                best[r["section"]] = r
+        print(json.dumps({"tune": out_path, "rows": len(rows), "n_gpus": world,
+                          "best": {k: {"name": v["name"], "ms": v["ms"], "busbw_gbs": v["busbw_gbs"]} for k, v in best.items()}}))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    return 0
+
+
+def p2p_bench(args, comm, world, rank, dev, time_steps) -> int:
+    """Device Send/Recv between ranks 0 and 1: one direction, and both directions at once, 1 MiB .. 1 GiB,
+    against NCCL's send/recv on the same tensors.  Device time (CUDA events on the default stream, which the
+    library's blocking send and receive streams synchronise with), max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    if world < 2:
+        if rank == 0:
+            print(json.dumps({"p2p": None, "reason": "needs at least two GPUs"}))
+        return 0
+    out_path = args.out or f"bench_out/p2p_{world}gpu.jsonl"
+    nmax = min(args.sweep_max_bytes, 1 << 30)
+    src = torch.empty(nmax, dtype=torch.uint8, device=dev)
+    dst = torch.empty(nmax, dtype=torch.uint8, device=dev)
+    src.copy_(torch.arange(nmax, device=dev, dtype=torch.int64).remainder(251).to(torch.uint8) + rank)
+    comm.device_info(connect=True)
+    rows = []
+    size = 1 << 20
+    while size <= nmax:
+        a, b = src[:size], dst[:size]
+        steps, warm = (50, 5) if size <= (64 << 20) else (10, 3)
+
+        def one_way():
+            if rank == 0:
+                comm.send(1, a, blocking=False)
+                comm.send_wait(1)
+            elif rank == 1:
+                comm.recv(0, b, blocking=True)
+
+        def both_ways():
+            if rank < 2:
+                comm.send(1 - rank, a, blocking=False)
+                comm.recv(1 - rank, b, blocking=True)
+                comm.send_wait(1 - rank)
+
+        def nccl_one_way():
+            if rank == 0:
+                dist.send(a, 1)
+            elif rank == 1:
+                dist.recv(b, 0)
+
+        for name, fn, dirs in (("ours_one_way", one_way, 1), ("ours_both_ways", both_ways, 1), ("nccl_one_way", nccl_one_way, 1)):
+            t = time_steps(fn, steps, warm)
+            comm.check()
+            rows.append({"bytes": size, "name": name, "us": t * 1e3, "gbs_per_direction": size * dirs / (t / 1e3) / 1e9})
+        if rank == 1:
+            want = (torch.arange(size, device=dev, dtype=torch.int64).remainder(251).to(torch.uint8))
+            if not torch.equal(b, want):
+                rows.append({"bytes": size, "name": "payload_mismatch"})
+        size *= 4
+    if rank == 0:
+        os.makedirs(os.path.dirname(out_path) or ".", exist_ok=True)
+        with open(out_path, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+        print(json.dumps({"p2p": out_path, "rows": len(rows),
+                          "at_largest": {r["name"]: round(r["gbs_per_direction"], 1) for r in rows if r["bytes"] == size // 4 and "us" in r}}))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    return 0
+
+
+def world_size_bench(args, comm, world, rank, dev, barrier, max_over_ranks) -> int:
+    """Ring, Rabenseifner, auto and NCCL at 64 MiB of fp32 (normal(0, 1) values seeded by rank) on every world
+    size 2..N of this launch, the non-powers of two included: a communicator over the first w ranks each
+    (the other ranks wait at a barrier of the whole job).  Checked against the fp64 sum."""
+    import torch
+    import torch.distributed as dist
+
+    import allreduce_proto_b200 as ar
+    from allreduce_proto_b200.utils import busbw_gbs
+
+    out_path = args.out or f"bench_out/world_sizes_{world}gpu.jsonl"
+    n = (64 << 20) // 4
+    g = torch.Generator(device=dev)
+    g.manual_seed(rank)
+    x = torch.randn(n, device=dev, generator=g)
+    y = torch.empty_like(x)
+    rows = []
+    for w in range(2, world + 1):
+        members = list(range(w))
+        group = dist.new_group(members)  # every rank of the job takes part in creating it
+        if rank < w:
+            sub = comm if w == world else ar.Communicator.from_torch_distributed(tag=f"ws{w}", ranks=members)
+            want = torch.zeros(n, dtype=torch.float64, device=dev)
+            for r in range(w):
+                gr = torch.Generator(device=dev)
+                gr.manual_seed(r)
+                want += torch.randn(n, device=dev, generator=gr).double()
+            for algo in ("ring", "rabenseifner", "auto", "nccl"):
+                def step():
+                    if algo == "nccl":
+                        dist.all_reduce(y, group=group)  # in place, on the previous result: timing only
+                    else:
+                        sub.allreduce(x, y, algo=algo)
+                for _ in range(5):
+                    step()
+                torch.cuda.synchronize()
+                dist.barrier(group=group)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                steps = 20
+                e0.record()
+                for _ in range(steps):
+                    step()
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+                ms = float(t.item())
+                if algo != "nccl":
+                    sub.check()
+                err = float((y.double() - want).abs().max().item()) if algo != "nccl" else None
+                rows.append({"world_size": w, "algo": algo, "bytes": n * 4, "ms": ms, "busbw_gbs": busbw_gbs(n * 4, ms / 1e3, w),
+                             "max_abs_err": err, "chosen": sub.device_info()["last_algo"] if algo != "nccl" else "nccl"})
+            if sub is not comm:
+                sub.barrier()
+                sub.close()
+        barrier()
+    if rank == 0:
+        os.makedirs(os.path.dirname(out_path) or ".", exist_ok=True)
+        with open(out_path, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+        print(json.dumps({"world_sizes": out_path, "rows": len(rows)}))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    return 0
+
+
 def kernel_case(args, comm, dev, time_steps) -> int:
     """One kernel, one GPU, small inputs (still larger than L2): the workload of the ncu captures in profiles/."""
     import torch

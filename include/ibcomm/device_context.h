@@ -17,18 +17,21 @@ namespace ibcomm {
 // Byte layout of one rank's arena.  Every rank uses the same layout.
 struct ArenaLayout {
   uint64_t control_offset = 0;   // ControlPage
-  uint64_t oneshot_offset = 0;   // [2 parities][kMaxRanks] slots of oneshot_slot_bytes
-  uint64_t oneshot_slot_bytes = 0;
+  uint64_t oneshot_offset = 0;   // [2 parities][world_size sources] slots of oneshot_slot_bytes
+  uint64_t oneshot_slot_bytes = 0;  // the one-shot area (kOneShotAreaBytes) divided by 2 * world_size
   uint64_t mailbox_offset = 0;   // [kMaxRanks sources][mailbox_slots] of mailbox_slot_bytes
   uint64_t mailbox_slot_bytes = 0;
   uint32_t mailbox_slots = 0;
+  uint64_t bcast_ring_offset = 0;  // one more ring of mailbox_slots slots: device broadcasts through the switch
   uint64_t pool_offset = 0;      // IBCOMM_MEMORY_POOL_PRE_ALLOC bytes
   uint64_t pool_bytes = 0;
   uint64_t work_offset = 0;      // IBCOMM_WORK_GPU_MEMORY_SIZE bytes
   uint64_t work_bytes = 0;
   uint64_t total_bytes = 0;
 };
-ArenaLayout MakeArenaLayout(size_t pool_bytes, size_t work_bytes);
+// Bytes of the one-shot area: 16 MiB slots for two ranks, 4 MiB for eight.
+constexpr uint64_t kOneShotAreaBytes = 64ull << 20;
+ArenaLayout MakeArenaLayout(size_t pool_bytes, size_t work_bytes, int world_size);
 
 // Algorithm and channel choice for a message (src/host/tuner.cpp).
 struct TunerChoice {
@@ -47,6 +50,10 @@ bool DeviceContextSendPoll(DeviceContext* d, int dest);
 bool DeviceContextRecvPoll(DeviceContext* d, int src);
 void DeviceContextSendWait(DeviceContext* d, int dest);
 void DeviceContextRecvWait(DeviceContext* d, int src);
+// Broadcast of a device buffer through NVSwitch multicast; false (nothing done)
+// when the box has no multicast or the length is not a multiple of 16 (the
+// same on every rank): the caller then falls back to sends.
+bool DeviceContextBcast(DeviceContext* d, void* buf, size_t len, int root);
 void DeviceContextCollectTrace(DeviceContext* d, Tracer* tracer);
 
 // Introspection for bindings and tests.

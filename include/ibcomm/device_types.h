@@ -25,7 +25,7 @@ namespace ibcomm {
 constexpr int kMaxRanks = 8;       // one NVSwitch box
 constexpr int kMaxChannels = 256;  // CTAs per rank a collective may use
 constexpr int kExecThreads = 512;  // threads per channel CTA
-constexpr int kP2pCtas = 32;       // CTAs of a device Send / Recv kernel (each owns a fixed part of every mailbox slot)
+constexpr int kP2pCtas = 128;      // most CTAs a device Send / Recv / Bcast kernel may use (each owns a fixed part of every mailbox slot)
 constexpr int kP2pMaxSlots = 8;    // upper bound of mailbox slots per source rank
 
 // ---- control page at the start of every rank's arena (peer-writable) ----
@@ -45,6 +45,13 @@ struct ControlPage {
   uint64_t p2p_flag[kP2pCtas][kMaxRanks];
   uint64_t p2p_credit[kP2pCtas][kMaxRanks];
   uint64_t p2p_len[kMaxRanks][kP2pMaxSlots];
+  // Device broadcast through the switch: the root multicasts pieces into the
+  // broadcast ring of every rank's mailbox area and then bcast_flag (the
+  // cumulative piece number over all broadcasts of the communicator);
+  // receiver q returns bcast_credit[c][q] to every rank, so that whoever is
+  // the root of a later broadcast knows which slots are free.
+  uint64_t bcast_flag[kP2pCtas];
+  uint64_t bcast_credit[kP2pCtas][kMaxRanks];
   // Set (to the call sequence) by any rank that gave up; polled by waiters.
   uint64_t abort_seq;
   // Written only by this rank's own kernels: the number of collectives it has

@@ -26,8 +26,20 @@
  * (torch's included); the caller passes the inputs and the outputs.
  *
  * First call on a device: the address of the scratch array is looked up once
- * per device (with that device current) and remembered.  Make that first call
- * outside any stream capture.
+ * per device (with that device current) and remembered.  With CUDA's lazy
+ * module loading (the default) the driver may also set the array up only at
+ * that moment, which is work on the driver's side that can take time or fail:
+ * make one warm-up call per device at start-up (or run with
+ * CUDA_MODULE_LOADING=EAGER); the no-allocation guarantee holds from the
+ * second call on.
+ *
+ * Stream capture: none of the calls may be made while `stream` is being
+ * captured.  Every call ends by copying the kernel's error word to the host
+ * and synchronising the stream, neither of which a capture allows.
+ *
+ * Threads: one process-wide lock is held for the whole call, the wait for the
+ * kernel included, so calls from several threads run one after the other,
+ * also when they target different GPUs.
  *
  * Sharing: every call on a device uses the same scratch array, which keeps
  * what the previous call left in it.  The flags are call counters that only

@@ -120,6 +120,7 @@ class DeviceContext {
   void Check();
   uint32_t Peek(DeviceStatus* out);
 
+  bool Bcast(void* buf, size_t len, int root);
   void Send(int dest, const void* buf, size_t len);
   void Recv(int src, void* buf, size_t len);
   bool SendPoll(int dest);
@@ -202,6 +203,8 @@ class DeviceContext {
   int twoshot_resident_ = -1;
   int max_channels_ = env::kDefaultNumCudaStream;
   std::vector<P2pState> p2p_;
+  int p2p_ctas_ = 96;          // CTAs of every Send / Recv / Bcast kernel of this communicator (knob IBCOMM_P2P_CTAS)
+  uint64_t bcast_pieces_ = 0;  // pieces of all device broadcasts so far (equal on every rank)
   std::vector<std::unique_ptr<SymmetricAlloc>> symm_;
   std::vector<RegisteredBuffer> registered_;
   std::vector<ImportedIpc> ipc_imports_;
@@ -227,7 +230,9 @@ DeviceContext::DeviceContext(Communicator* comm) : comm_(comm) {
   ws_ = static_cast<int>(comm->world_size());
   if (ws_ > kMaxRanks) IBCOMM_FAIL(NOT_SUPPORTED, "Device collectives support up to %d ranks (got %d).\n", kMaxRanks, ws_);
   max_channels_ = std::min(env::ReadNumCudaStream(), kMaxChannels);
-  layout_ = MakeArenaLayout(env::ReadPreAllocSize(), env::ReadWorkGpuMemorySize());
+  p2p_ctas_ = Tunable("IBCOMM_P2P_CTAS", 96);
+  if (p2p_ctas_ < 1 || p2p_ctas_ > kP2pCtas) p2p_ctas_ = 96;
+  layout_ = MakeArenaLayout(env::ReadPreAllocSize(), env::ReadWorkGpuMemorySize(), ws_);
   // A blocking stream: work the caller queued on the legacy default stream is
   // ordered before the collectives issued here, and vice versa.
   CUDACHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamDefault));
@@ -689,9 +694,9 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   if (((reinterpret_cast<uintptr_t>(sendbuf) | reinterpret_cast<uintptr_t>(recvbuf)) & 15u) != 0) return false;
   if ((n * wsize) % 16 != 0) return false;
   if (multimem && (mc_ == nullptr || !NvlsSupportsDType(wire))) return false;
-  // Four windows (two in, two out) in the pool and the work region behind it
-  // (the two are adjacent and one collective runs at a time).
-  const uint64_t quarter = (layout_.pool_bytes + layout_.work_bytes) / 4 / 4096 * 4096;
+  // Six windows (three in, three out) in the pool and the work region behind
+  // it (the two are adjacent and one collective runs at a time).
+  const uint64_t quarter = (layout_.pool_bytes + layout_.work_bytes) / 6 / 4096 * 4096;
   if (quarter < 4096) return false;
   StagedParams p;
   memset(&p, 0, sizeof(p));
@@ -711,14 +716,14 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   static const int resident = StagedKernelMaxCoResidentBlocks(device_);
   if (resident > 0) ctas = std::min(ctas, resident);
   if (Tunable("IBCOMM_MAX_CTAS", 0) > 0) ctas = std::min(ctas, Tunable("IBCOMM_MAX_CTAS", 0));
-  ctas = std::max(1, std::min(ctas, kMaxChannels));
+  ctas = std::max(1, std::min(ctas, 128));  // the kernel keeps a second row of flags at CTA index + 128
   uint64_t cap_bytes = quarter;
   const int max_window = Tunable("IBCOMM_STAGED_WINDOW_KIB", 0);  // experiment knob: smaller windows
   if (max_window > 0) cap_bytes = std::min<uint64_t>(cap_bytes, static_cast<uint64_t>(max_window) << 10);
   p.window_elems = TwoShotWindowElems(n, cap_bytes / wsize, wsize, ws_, ctas);
-  for (int j = 0; j < 2; ++j) {
+  for (int j = 0; j < 3; ++j) {
     p.in_off[j] = layout_.pool_offset + static_cast<uint64_t>(j) * quarter;
-    p.out_off[j] = layout_.pool_offset + static_cast<uint64_t>(2 + j) * quarter;
+    p.out_off[j] = layout_.pool_offset + static_cast<uint64_t>(3 + j) * quarter;
   }
   p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
   p.status = rr_.d_status;
@@ -1078,7 +1083,7 @@ void DeviceContext::Send(int dest, const void* buf, size_t len) {
   p.doorbell = rr_.d_doorbell;
   s.pieces_sent += len == 0 ? 1 : (len + p.slot_bytes - 1) / p.slot_bytes;
   IBCOMM_TRACE(*tracer_, kTraceIssueSend);
-  CUDACHECK(LaunchP2pKernel(p, send_stream_));
+  CUDACHECK(LaunchP2pKernel(p, p2p_ctas_, send_stream_));
   ++kernel_launches_;
   IBCOMM_TRACE(*tracer_, kTraceIssueSend);
   CUDACHECK(cudaEventRecord(s.send_done, send_stream_));
@@ -1125,10 +1130,43 @@ void DeviceContext::Recv(int src, void* buf, size_t len) {
   p.doorbell = rr_.d_doorbell;
   s.pieces_received += len == 0 ? 1 : (len + p.slot_bytes - 1) / p.slot_bytes;
   IBCOMM_TRACE(*tracer_, kTraceIssueRecv);
-  CUDACHECK(LaunchP2pKernel(p, recv_stream_));
+  CUDACHECK(LaunchP2pKernel(p, p2p_ctas_, recv_stream_));
   ++kernel_launches_;
   IBCOMM_TRACE(*tracer_, kTraceIssueRecv);
   CUDACHECK(cudaEventRecord(s.recv_done, recv_stream_));
+}
+
+bool DeviceContext::Bcast(void* buf, size_t len, int root) {
+  NvtxRange nvtx("ibcomm::Bcast(device)");
+  ConnectPeers();
+  if (mc_ == nullptr || len == 0 || len % 16 != 0) return false;  // the same on every rank
+  if (Tunable("IBCOMM_BCAST_MULTICAST", 1) == 0) return false;
+  OrderAfterPrevious(stream_);
+  BcastParams p;
+  memset(&p, 0, sizeof(p));
+  p.rank = rank_;
+  p.root = root;
+  p.world_size = ws_;
+  p.peers = rr_.peers;
+  p.buf = buf;
+  p.bytes = len;
+  p.ring_offset = layout_.bcast_ring_offset;
+  p.slot_bytes = layout_.mailbox_slot_bytes;
+  p.slots = layout_.mailbox_slots;
+  p.first_piece = bcast_pieces_;
+  p.seq = 0xFE00000000000000ull | (bcast_pieces_ & 0xFFFFFFFFFFFFull);
+  p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
+  p.status = rr_.d_status;
+  p.doorbell = rr_.d_doorbell;
+  bcast_pieces_ += (len + p.slot_bytes - 1) / p.slot_bytes;
+  IBCOMM_TRACE(*tracer_, kTraceIssueSend);
+  CUDACHECK(LaunchBcastKernel(p, p2p_ctas_, stream_));
+  ++kernel_launches_;
+  IBCOMM_TRACE(*tracer_, kTraceIssueSend);
+  MarkIssued(stream_);
+  CUDACHECK(cudaStreamSynchronize(stream_));
+  Check();
+  return true;
 }
 
 bool DeviceContext::SendPoll(int dest) {
@@ -1254,6 +1292,7 @@ bool DeviceContextSendPoll(DeviceContext* d, int dest) { return d->SendPoll(dest
 bool DeviceContextRecvPoll(DeviceContext* d, int src) { return d->RecvPoll(src); }
 void DeviceContextSendWait(DeviceContext* d, int dest) { d->SendWait(dest); }
 void DeviceContextRecvWait(DeviceContext* d, int src) { d->RecvWait(src); }
+bool DeviceContextBcast(DeviceContext* d, void* buf, size_t len, int root) { return d->Bcast(buf, len, root); }
 void DeviceContextCollectTrace(DeviceContext* d, Tracer* tracer) { d->CollectTrace(tracer); }
 DeviceInfo DeviceContextInfo(DeviceContext* d) { return d->Info(); }
 void DeviceContextSetMaxChannels(DeviceContext* d, int channels) { d->SetMaxChannels(channels); }

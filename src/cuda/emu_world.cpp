@@ -47,7 +47,7 @@ EmuWorld::EmuWorld(int num_ranks, size_t pool_bytes, size_t work_bytes) : ws_(nu
   m.ws = num_ranks;
   CUDACHECK(cudaGetDevice(&m.device));
   m.timeout_ms = env::ReadTimeoutMs();
-  m.layout = MakeArenaLayout(pool_bytes ? pool_bytes : env::ReadPreAllocSize(), work_bytes ? work_bytes : env::ReadWorkGpuMemorySize());
+  m.layout = MakeArenaLayout(pool_bytes ? pool_bytes : env::ReadPreAllocSize(), work_bytes ? work_bytes : env::ReadWorkGpuMemorySize(), num_ranks);
   const size_t total = static_cast<size_t>(m.layout.total_bytes) * static_cast<size_t>(num_ranks);
   CUDACHECK(cudaMalloc(&m.arenas, total));
   CUDACHECK(cudaMemset(m.arenas, 0, total));
@@ -125,11 +125,11 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
   const size_t wsize = DTypeSize(wire);
   if (algo == Algo::kDirect && (wire != dtype || m.direct_staging == 2)) {
     // The pipelined staged kernel (what ordinary buffers and 16-bit wires get on several GPUs).
-    const uint64_t quarter = (m.layout.pool_bytes + m.layout.work_bytes) / 4 / 4096 * 4096;
+    const uint64_t quarter = (m.layout.pool_bytes + m.layout.work_bytes) / 6 / 4096 * 4096;
     if (!all_aligned || (n * wsize) % 16 != 0 || quarter < 4096)
       IBCOMM_FAIL(NOT_SUPPORTED, "The pipelined staged two-shot needs 16-byte aligned buffers of whole 16-byte wire vectors.\n");
     int ch = channels > 0 ? channels : ChooseChannels(Algo::kDirect, n * wsize, m.ws, kMaxChannels);
-    ch = std::max(1, std::min(ch, std::max(1, m.staged_max_blocks / m.ws)));
+    ch = std::max(1, std::min(std::min(ch, 128), std::max(1, m.staged_max_blocks / m.ws)));
     std::vector<StagedParams> ps(static_cast<size_t>(m.ws));
     for (int r = 0; r < m.ws; ++r) {
       StagedParams& p = ps[static_cast<size_t>(r)];
@@ -147,9 +147,9 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
       p.len_elements = n;
       p.scale = scale;
       p.window_elems = TwoShotWindowElems(n, quarter / wsize, wsize, m.ws, ch);
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < 3; ++j) {
         p.in_off[j] = m.layout.pool_offset + static_cast<uint64_t>(j) * quarter;
-        p.out_off[j] = m.layout.pool_offset + static_cast<uint64_t>(2 + j) * quarter;
+        p.out_off[j] = m.layout.pool_offset + static_cast<uint64_t>(3 + j) * quarter;
       }
       p.timeout_ns = timeout_ns;
       p.status = rr.d_status;

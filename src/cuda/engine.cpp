@@ -10,28 +10,36 @@ namespace ibcomm {
 
 static uint64_t AlignUp(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
-ArenaLayout MakeArenaLayout(size_t pool_bytes, size_t work_bytes) {
+ArenaLayout MakeArenaLayout(size_t pool_bytes, size_t work_bytes, int world_size) {
   ArenaLayout l;
   uint64_t off = 0;
   l.control_offset = off;
   off += AlignUp(sizeof(ControlPage), 65536);
   l.oneshot_offset = off;
-  l.oneshot_slot_bytes = 512u << 10;
-  off += 2ull * kMaxRanks * l.oneshot_slot_bytes;
+  // A one-shot call pushes the whole message to every peer, so it needs one
+  // slot per (parity, source rank): few ranks get large slots.
+  const uint64_t ws = static_cast<uint64_t>(world_size < 2 ? 2 : (world_size > kMaxRanks ? kMaxRanks : world_size));
+  l.oneshot_slot_bytes = kOneShotAreaBytes / (2 * ws) / 4096 * 4096;
+  off += kOneShotAreaBytes;
   l.mailbox_offset = off;
-  // Device Send/Recv mailboxes: per source rank a ring of slots.  2 MiB slots
-  // give each of the kP2pCtas CTAs of a message 64 KiB per piece, four slots
-  // keep the sender ahead of the receiver (knobs for experiments:
-  // IBCOMM_P2P_SLOT_KIB, IBCOMM_P2P_SLOTS; all ranks must agree).
+  // Device Send/Recv mailboxes: per source rank a ring of slots.  A slot is
+  // the unit of hand-over: before a piece's flag may be raised the sending
+  // CTA waits until its stores are acknowledged over NVLink (about 6 us under
+  // load, measured on B200), so a piece has to be worth several microseconds
+  // of link time: 4 MiB slots, four of them (two in flight from the sender's
+  // two warp groups, two being emptied by the receiver).  Knobs for experiments: IBCOMM_P2P_SLOT_KIB,
+  // IBCOMM_P2P_SLOTS; all ranks must agree.
   {
-    int kib = Tunable("IBCOMM_P2P_SLOT_KIB", 2048);
-    if (kib < 16 || kib > (64 << 10)) kib = 2048;
+    int kib = Tunable("IBCOMM_P2P_SLOT_KIB", 4096);
+    if (kib < 16 || kib > (64 << 10)) kib = 4096;
     int slots = Tunable("IBCOMM_P2P_SLOTS", 4);
     if (slots < 2 || slots > kP2pMaxSlots) slots = 4;
     l.mailbox_slot_bytes = static_cast<uint64_t>(kib) << 10;
     l.mailbox_slots = static_cast<uint32_t>(slots);
   }
-  off += static_cast<uint64_t>(kMaxRanks) * l.mailbox_slots * l.mailbox_slot_bytes;
+  // One ring per source rank, plus the ring device broadcasts are multicast into.
+  l.bcast_ring_offset = off + static_cast<uint64_t>(kMaxRanks) * l.mailbox_slots * l.mailbox_slot_bytes;
+  off += static_cast<uint64_t>(kMaxRanks + 1) * l.mailbox_slots * l.mailbox_slot_bytes;
   l.pool_offset = off;
   l.pool_bytes = AlignUp(pool_bytes < 4096 ? 4096 : pool_bytes, 4096);
   off += l.pool_bytes;

@@ -11,10 +11,11 @@
 // The CTA is warp-specialised so that the synchronisation of one op overlaps
 // the data of its neighbours: one thread (the "waiter") runs ahead through
 // the program and waits for the flags of the coming ops; the data warps
-// stream op after op without a CTA-wide barrier; another thread (the
-// "poster") follows behind, and once every data warp has issued an op's
-// stores it fences them and publishes the op's flags.  The three parties
-// hand over through two counters in shared memory (ops ready, warp-ops done).
+// stream op after op without a CTA-wide barrier, in two groups that take the
+// ops in turn; another thread (the "poster") follows behind, and once the
+// warps of an op's group have had their stores acknowledged it publishes the
+// op's flags.  The parties hand over through counters in shared memory (ops
+// ready; per data warp, ops done).
 // Counterpart of the reference's host event loop around _reduce_inplace_cuda
 // (ibcomm/allreduce_cuda_impl.h:24-33, 103-299, 470-707).
 //
@@ -249,24 +250,41 @@ __device__ void ExecBody(const ExecParams& p, uint64_t seq, RoleSync* sync) {
   const int warp = static_cast<int>(threadIdx.x) / 32, lane = static_cast<int>(threadIdx.x) % 32;
 
   if (warp < data_warps) {
-    const unsigned nthr = static_cast<unsigned>(data_warps) * 32u;
+    // Two groups of data warps (even and odd warps) take the ops in turn.
+    // After its stores a group waits until they are acknowledged over NVLink
+    // (the release below) before the poster may publish the op; meanwhile the
+    // other group loads and stores the next op, so the link does not idle
+    // during the hand-over.  Consecutive ops are independent of each other
+    // (different chains of the ring, different pieces of a halving step) with
+    // one exception, handled by the barrier below.
+    const int group = warp & 1;
+    const unsigned all_threads = static_cast<unsigned>(data_warps) * 32u;
+    const unsigned nthr = static_cast<unsigned>((data_warps + 1 - group) / 2) * 32u;
+    const unsigned gtid = static_cast<unsigned>(warp >> 1) * 32u + static_cast<unsigned>(lane);
+    bool alive = true;
     for (int oi = 0; oi < p.num_ops; ++oi) {
-      int go = 1;
-      if (lane == 0) go = SpinShared(&sync->ready, static_cast<unsigned>(oi) + 1u, sync, p.timeout_ns) ? 1 : 0;
-      go = __shfl_sync(0xffffffffu, go, 0);
-      if (!go) break;
       const Op op = p.ops[oi];
       // No barrier separates consecutive ops, and an element need not map to
       // the same thread in two ops that cover different ranges.  An op that
       // reads recvbuf (Rabenseifner's running partial sums, written by earlier
-      // ops) therefore first waits until every data warp has finished the ops
-      // before it.  Overwrites need no such barrier: a range is overwritten
-      // only by data that a peer derived from this rank's own transfer of the
-      // range, which the poster published after all data warps had read it.
-      if (op.src_a == kSrcRecv || op.src_b == kSrcRecv) asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
-      RunOpData<T, W>(op, p, ch, nch, threadIdx.x, nthr);
+      // ops) therefore first waits until every data warp, of both groups, has
+      // finished the ops before it.  Every data warp walks the whole program
+      // and meets these barriers, also after the call was stopped.
+      // Overwrites need no such barrier: a range is overwritten only by data
+      // that a peer derived from this rank's own transfer of the range, which
+      // the poster published after all warps of the op's group had read it.
+      if (op.src_a == kSrcRecv || op.src_b == kSrcRecv) asm volatile("bar.sync 1, %0;" ::"r"(all_threads) : "memory");
+      if ((oi & 1) != group || !alive) continue;
+      int go = 1;
+      if (lane == 0) go = SpinShared(&sync->ready, static_cast<unsigned>(oi) + 1u, sync, p.timeout_ns) ? 1 : 0;
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (!go) {
+        alive = false;
+        continue;
+      }
+      RunOpData<T, W>(op, p, ch, nch, gtid, nthr);
       __syncwarp();
-      if (lane == 0) AddReleaseShared(&sync->done, 1u);
+      if (lane == 0) StReleaseShared(&sync->done[warp], static_cast<unsigned>(oi) + 1u);
     }
   } else if (warp == data_warps) {
     if (lane == 0) {
@@ -294,7 +312,11 @@ __device__ void ExecBody(const ExecParams& p, uint64_t seq, RoleSync* sync) {
       // Poster: when all data warps have issued the op's stores, make them
       // visible system-wide and publish the op's flags.
       for (int oi = 0; oi < p.num_ops; ++oi) {
-        if (!SpinShared(&sync->done, static_cast<unsigned>(data_warps) * (static_cast<unsigned>(oi) + 1u), sync, p.timeout_ns)) break;
+        // The warps of the group that ran op oi.
+        bool all = true;
+        for (int wi = oi & 1; wi < data_warps && all; wi += 2)
+          all = SpinShared(&sync->done[wi], static_cast<unsigned>(oi) + 1u, sync, p.timeout_ns);
+        if (!all) break;
         const Op op = p.ops[oi];
         if (op.post_out != 0) {
           FenceSys();
@@ -317,11 +339,7 @@ ExecKernel(const __grid_constant__ ExecParams p0, const ExecParams* __restrict__
     const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y)
                                            : reinterpret_cast<const uint32_t*>(&p0);
     for (unsigned i = threadIdx.x; i < sizeof(ExecParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
-    if (threadIdx.x == 0) {
-      s_sync.ready = 0;
-      s_sync.done = 0;
-      s_sync.stop = 0;
-    }
+    if (threadIdx.x == 0) RoleSyncInit(&s_sync);
   }
   __syncthreads();
   if (p.world_size <= 1) return;

@@ -88,8 +88,9 @@ cudaError_t LaunchHybridKernel(const HybridParams& h, int blocks, cudaStream_t s
 // ---- pipelined staged two-shot (staged_kernel.cu) ----
 // For buffers the peers cannot map, and for fp32 buffers that travel as
 // bf16/fp16: the message moves through the pool in windows, and inside one
-// CTA three warp groups work on three different windows at the same time
-// (copy in / reduce over NVLink / copy out), double-buffered.
+// CTA four warp groups work on up to four windows at the same time (copy in /
+// two reducers over NVLink / copy out), three buffers of each kind.  At most
+// 128 CTAs.
 struct StagedParams {
   int32_t rank;
   int32_t world_size;
@@ -103,8 +104,8 @@ struct StagedParams {
   uint64_t len_elements; // a whole number of 16-byte wire vectors
   double scale;
   uint64_t window_elems; // elements per window (a whole number of vectors per rank and CTA)
-  uint64_t in_off[2];    // byte offsets of the two input windows inside every arena
-  uint64_t out_off[2];   // ... and of the two output windows
+  uint64_t in_off[3];    // byte offsets of the three input windows inside every arena
+  uint64_t out_off[3];   // ... and of the three output windows
   uint64_t timeout_ns;
   DeviceStatus* status;
   uint32_t* doorbell;
@@ -184,6 +185,35 @@ struct P2pParams {
   DeviceStatus* status;
   uint32_t* doorbell;
 };
-cudaError_t LaunchP2pKernel(const P2pParams& p, cudaStream_t stream);
+// `ctas` (1..kP2pCtas) must be the same for every message of a communicator
+// and on both sides: a CTA's flags count the pieces of its own part.  One SM
+// sustains roughly 10 GB/s of stores to a peer, so bandwidth needs many CTAs.
+cudaError_t LaunchP2pKernel(const P2pParams& p, int ctas, cudaStream_t stream);
+
+// ---- device broadcast through NVSwitch multicast ----
+// The root writes every piece ONCE (`multimem.st` into the broadcast ring of
+// all ranks' mailbox areas at the same time, then the flag the same way); the
+// others copy it out and return credits.  Needs the multicast alias of the
+// arenas and a length that is a multiple of 16 (conditions every rank decides
+// alike; a buffer that is only byte-aligned is moved byte by byte).
+struct BcastParams {
+  int32_t rank;
+  int32_t root;
+  int32_t world_size;
+  int32_t pad_;
+  PeerTable peers;
+  void* buf;                // root: source, others: destination
+  uint64_t bytes;
+  uint64_t ring_offset;     // byte offset of the broadcast ring in the arena
+  uint64_t slot_bytes;
+  uint32_t slots;
+  uint32_t pad2_;
+  uint64_t first_piece;     // cumulative piece number of the communicator's broadcasts at call start
+  uint64_t seq;
+  uint64_t timeout_ns;
+  DeviceStatus* status;
+  uint32_t* doorbell;
+};
+cudaError_t LaunchBcastKernel(const BcastParams& p, int ctas, cudaStream_t stream);
 
 }  // namespace ibcomm

@@ -159,9 +159,10 @@ extern "C" int ibcomm_emu_oneshot_allreduce_f32_noalloc(const float* const* send
     Describe(errbuf, errbuf_len, "num_ranks = %d is outside 1..%d", num_ranks, kMaxRanks);
     return 1;
   }
-  if (len_elements * sizeof(float) > kSlotBytes) {
+  // Compared in elements: `len_elements * sizeof(float)` wraps for absurd lengths.
+  if (len_elements > kSlotBytes / sizeof(float)) {
     Describe(errbuf, errbuf_len, "%zu elements = %zu bytes per buffer exceed the limit of %zu bytes of the no-allocation entry point",
-             len_elements, len_elements * sizeof(float), kSlotBytes);
+             len_elements, len_elements <= (~size_t(0)) / sizeof(float) ? len_elements * sizeof(float) : ~size_t(0), kSlotBytes);
     return 1;
   }
   for (int r = 0; r < num_ranks; ++r) {

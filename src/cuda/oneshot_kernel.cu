@@ -57,7 +57,7 @@ __device__ void OneShotBody(const OneShotParams& p, uint64_t seq, int& s_stop) {
   }
   auto slot = [&](int owner_rank, int src_rank) -> T* {
     return reinterpret_cast<T*>(p.peers.arena[owner_rank] + p.slot_offset +
-                                (static_cast<uint64_t>(parity) * kMaxRanks + static_cast<uint64_t>(src_rank)) * p.slot_bytes);
+                                (static_cast<uint64_t>(parity) * static_cast<uint64_t>(ws) + static_cast<uint64_t>(src_rank)) * p.slot_bytes);
   };
   const bool aligned = ((reinterpret_cast<uintptr_t>(sendbuf) | reinterpret_cast<uintptr_t>(recvbuf)) & 15u) == 0;
   const uint64_t nfull = aligned ? (hi - lo) / kVecElems : 0;  // whole vectors handled by the vector path
@@ -66,8 +66,20 @@ __device__ void OneShotBody(const OneShotParams& p, uint64_t seq, int& s_stop) {
   for (int k = 1; k < ws; ++k) {
     const int q = (me + k) % ws;  // start with a different peer on every rank
     T* dst = slot(q, me);
-    for (uint64_t i = threadIdx.x; i < nfull; i += blockDim.x)
-      St16(reinterpret_cast<uint4*>(dst + lo) + i, Ld16(reinterpret_cast<const uint4*>(sendbuf + lo) + i));
+    constexpr int kU = 4;  // vectors in flight per thread
+    for (uint64_t i = threadIdx.x; i < nfull; i += static_cast<uint64_t>(blockDim.x) * kU) {
+      uint4 v[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+        if (idx < nfull) v[u] = Ld16(reinterpret_cast<const uint4*>(sendbuf + lo) + idx);
+      }
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const uint64_t idx = i + static_cast<uint64_t>(u) * blockDim.x;
+        if (idx < nfull) St16(reinterpret_cast<uint4*>(dst + lo) + idx, v[u]);
+      }
+    }
     for (uint64_t i = lo + nfull * kVecElems + threadIdx.x; i < hi; i += blockDim.x) dst[i] = sendbuf[i];
   }
   __syncthreads();

@@ -8,31 +8,38 @@
 // reads (its own shard of it, from every rank: `multimem.ld_reduce` in the
 // NVSwitch, or peer loads summed in rank order), and the output window, which
 // every rank writes (`multimem.st` / peer stores of its reduced, scaled
-// shard) and which this rank copies to `recvbuf`.  Both are double-buffered,
-// and the 16 warps of a CTA are three groups that work on three different
+// shard) and which this rank copies to `recvbuf`.  There are three buffers of
+// each kind, and the 16 warps of a CTA are four groups that work on up to four
 // windows at the same time:
 //
-//   loader   (warps 0-3)   sendbuf -> input window k+1       local HBM traffic
-//   reducer  (warps 8-15)  input windows k -> output windows k   NVLink traffic
-//   storer   (warps 4-7)   output window k-1 -> recvbuf      local HBM traffic
+//   loader     sendbuf -> input window k+2                    local HBM traffic
+//   reducer A  input windows k   -> output windows k   (even k)   NVLink traffic
+//   reducer B  input windows k+1 -> output windows k+1 (odd k)    NVLink traffic
+//   storer     output window k-1 -> recvbuf                   local HBM traffic
 //
 // so the links stay busy while the copies run, where the sequential kernel
-// (nvls_kernel.cu) leaves them idle during its copy phases.  When the wire
-// type equals the buffer type the copies are bulk asynchronous copies (TMA,
-// `cp.async.bulk`, global -> shared -> global, no multicast, this GPU's memory
-// only) driven by one thread per group through a three-deep ring of 16 KiB
-// shared-memory stages; with a 16-bit wire the loader and the storer convert
-// in registers instead (fp32 accumulation in the reducer either way).
+// (nvls_kernel.cu) leaves them idle during its copy phases.  Two reducer
+// groups because a window can only be published once its stores have been
+// acknowledged over NVLink, which takes microseconds: while one group waits
+// for that, the other streams the next window.  When the wire type equals the
+// buffer type the copies are bulk asynchronous copies (TMA, `cp.async.bulk`,
+// global -> shared -> global, no multicast, this GPU's memory only) driven by
+// one thread of the loader warp and one of the storer warp through six-deep
+// rings of 16 KiB shared-memory stages (the other 14 warps reduce); with a
+// 16-bit wire the loader and the storer (three warps each) convert in
+// registers instead (fp32 accumulation in the reducers either way).
 //
-// Synchronisation is per CTA index across ranks, with three rows of the
-// control page (values (call << 32) | window + 1, growing only):
-//   inflag[b][q]  rank q's CTA b has filled its input window k
-//   bar[b][q]     rank q's CTA b has reduced its part of window k
-//   credit[b][q]  rank q's CTA b has copied output window k out
-// loader k waits for bar >= k-1 (input buffer free again), reducer k for
-// inflag >= k+1 and credit >= k-1, storer k for bar >= k+1.  CTA b touches
-// the same bytes of a window on every rank (part b of every shard), so no
-// CTA-to-CTA synchronisation is needed.  Every wait is bounded.
+// Synchronisation is per CTA index across ranks, with rows of the control
+// page (values (call << 32) | window + 1, growing only):
+//   inflag[b][q]              rank q's CTA b has filled its input window k
+//   bar[b][q], bar[b+128][q]  rank q's CTA b has reduced its part of window k
+//                             (even k / odd k: the two reducer groups finish
+//                             their windows independently of each other)
+//   credit[b][q]              rank q's CTA b has copied output window k out
+// loader k waits for "reduced" >= k-2 (input buffer free again), reducer k for
+// inflag >= k+1 and credit >= k-2, storer k for "reduced" >= k+1.  CTA b
+// touches the same bytes of a window on every rank (part b of every shard),
+// so no CTA-to-CTA synchronisation is needed.  Every wait is bounded.
 //
 // Requirements (the host falls back to the sequential kernel otherwise):
 // 16-byte aligned buffers and a length that is a whole number of 16-byte
@@ -53,23 +60,29 @@ namespace ibcomm {
 namespace dev {
 
 constexpr int kStagedThreads = 512;
-constexpr int kLoadThreads = 128;    // warps 0-3
-constexpr int kStoreThreads = 128;   // warps 4-7
-constexpr int kReduceThreads = 256;  // warps 8-15
-constexpr int kBarLoad = 1, kBarStore = 2, kBarReduce = 3;  // named barriers of the groups (0 is __syncthreads)
+// Warps per group.  With bulk copies one thread drives each copy group, so
+// the loader and the storer are one warp each and 14 warps reduce; with
+// copies in registers (16-bit wire) the split is 3 / 3 / 10.
+constexpr int kLoadWarpsBulk = 1, kStoreWarpsBulk = 1;
+constexpr int kLoadWarpsRegs = 3, kStoreWarpsRegs = 3;
+constexpr int kBarLoad = 1, kBarStore = 2, kBarReduce = 3;  // named barriers of the groups (0 is __syncthreads); reducer B uses kBarReduce + 1
+constexpr int kStagedBuffers = 3;     // input windows, and output windows, in the pool
+constexpr int kStagedMaxCtas = 128;   // the odd windows' "reduced" flags live in bar[cta + 128]
 constexpr uint32_t kBulkChunk = 16384;  // bytes per bulk copy
-constexpr int kBulkDepth = 3;           // stages per copy group
+constexpr int kBulkDepth = 6;           // stages per copy group
 constexpr size_t kStagedSmemBytes = 2ull * kBulkDepth * kBulkChunk;
 
-enum StagedRole : int { kRoleLoad = 0, kRoleStore = 1, kRoleReduce = 2 };
+enum StagedRole : int { kRoleLoad = 0, kRoleStore = 1, kRoleReduce = 2 /* and 3 for reducer B */ };
 enum StagedRow : int { kRowInReady = 0, kRowReduced = 1, kRowOutFree = 2 };
 
 __device__ __forceinline__ void GroupSync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-__device__ __forceinline__ uint64_t* FlagRow(ControlPage* page, int row, int cta) {
-  return row == kRowInReady ? page->inflag[cta] : (row == kRowReduced ? page->bar[cta] : page->credit[cta]);
+// `window` selects the row of the "reduced" flags (even or odd windows).
+__device__ __forceinline__ uint64_t* FlagRow(ControlPage* page, int row, int cta, uint64_t window) {
+  return row == kRowInReady ? page->inflag[cta]
+                            : (row == kRowReduced ? page->bar[cta + ((window & 1) != 0 ? kStagedMaxCtas : 0)] : page->credit[cta]);
 }
 
 // State every thread of a warp group shares.
@@ -88,8 +101,8 @@ struct RoleCtx {
 // Waits until every rank's word in `row` has reached `value`.  All `nthr`
 // threads of the group call it and get the same answer: false when the call
 // is over (a wait ran out here or elsewhere).
-__device__ __forceinline__ bool RoleWait(RoleCtx& c, int row, uint64_t value, uint32_t kind, int window) {
-  uint64_t* words = FlagRow(Ctl(*c.w.peers, c.w.rank), row, c.cta);
+__device__ __forceinline__ bool RoleWait(RoleCtx& c, int row, uint64_t flag_window, uint64_t value, uint32_t kind, int window) {
+  uint64_t* words = FlagRow(Ctl(*c.w.peers, c.w.rank), row, c.cta, flag_window);
   const int slot = static_cast<int>(c.round & 1u);
   ++c.round;
   if (c.nthr == 1) {
@@ -108,13 +121,16 @@ __device__ __forceinline__ bool RoleWait(RoleCtx& c, int row, uint64_t value, ui
 
 // Publishes `value` in `row` at every rank (this rank included).  Everything
 // the group wrote before is ordered ahead of the flag.
-__device__ __forceinline__ void RolePost(RoleCtx& c, int row, uint64_t value) {
+__device__ __forceinline__ void RolePost(RoleCtx& c, int row, uint64_t flag_window, uint64_t value) {
   if (c.nthr == 1) {
-    for (int q = 0; q < c.w.world_size; ++q) StReleaseSys(FlagRow(Ctl(*c.w.peers, q), row, c.cta) + c.w.rank, value);
+    // One fence for all ranks' flags (a release per flag would wait for the
+    // previous flag's acknowledgement every time).
+    FenceSys();
+    for (int q = 0; q < c.w.world_size; ++q) StRelaxedSys(FlagRow(Ctl(*c.w.peers, q), row, c.cta, flag_window) + c.w.rank, value);
     return;
   }
   GroupSync(c.bar_id, c.nthr);
-  if (c.tid < c.w.world_size) StReleaseSys(FlagRow(Ctl(*c.w.peers, c.tid), row, c.cta) + c.w.rank, value);
+  if (c.tid < c.w.world_size) StReleaseSys(FlagRow(Ctl(*c.w.peers, c.tid), row, c.cta, flag_window) + c.w.rank, value);
 }
 
 // ---- copies in registers (with the conversion between buffer and wire type) ----
@@ -252,14 +268,14 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
   __shared__ StagedParams p;
   __shared__ uint64_t s_seq;
   __shared__ int s_stop;
-  __shared__ int s_role_stop[3][2];
+  __shared__ int s_role_stop[4][2];
   __shared__ uint64_t s_full[2][kBulkDepth];
   {
     const uint32_t* src = (emu != nullptr) ? reinterpret_cast<const uint32_t*>(emu + blockIdx.y) : reinterpret_cast<const uint32_t*>(&p0);
     for (unsigned i = threadIdx.x; i < sizeof(StagedParams) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(&p)[i] = src[i];
     if (threadIdx.x == 0) {
       s_stop = 0;
-      for (int r = 0; r < 3; ++r) s_role_stop[r][0] = s_role_stop[r][1] = 0;
+      for (int r = 0; r < 4; ++r) s_role_stop[r][0] = s_role_stop[r][1] = 0;
       for (int r = 0; r < 2; ++r)
         for (int s = 0; s < kBulkDepth; ++s) MbarInit(&s_full[r][s], 1);
       MbarInitFence();
@@ -291,23 +307,29 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
   c.round = 0;
 
   const int warp = threadIdx.x / 32;
-  if (warp < 4) {
+  const int load_warps = tma ? kLoadWarpsBulk : kLoadWarpsRegs;
+  const int store_warps = tma ? kStoreWarpsBulk : kStoreWarpsRegs;
+  if (warp < load_warps) {
     // ------------------------------------------------------------ loader
     c.role = kRoleLoad;
     c.bar_id = kBarLoad;
     c.tid = threadIdx.x;
-    c.nthr = tma ? 1 : kLoadThreads;
-    if (c.tid < c.nthr) {
+    // With bulk copies lane 0 moves the data; the other lanes of the warp share the flag waits and posts.
+    c.nthr = 32 * load_warps;
+    const bool mover = !tma || c.tid == 0;
+    {
       BulkRing ring{smem, s_full[0], 0};
       for (uint64_t k = 0; k < windows; ++k) {
-        const int j = static_cast<int>(k & 1);
+        const int j = static_cast<int>(k % kStagedBuffers);
         const uint64_t v0 = k * full_nv;
         const uint64_t nv = total_nv - v0 < full_nv ? total_nv - v0 : full_nv;
         // The input buffer is free once every rank has reduced the window that used it before.
-        if (k >= 2 && !RoleWait(c, kRowReduced, base | (k - 1), kWaitBarrier, static_cast<int>(k))) break;
+        if (k >= kStagedBuffers &&
+            !RoleWait(c, kRowReduced, k - kStagedBuffers, base | (k - kStagedBuffers + 1), kWaitBarrier, static_cast<int>(k)))
+          break;
         unsigned char* win = p.peers.arena[me] + p.in_off[j];
         const unsigned char* user = static_cast<const unsigned char*>(p.sendbuf) + v0 * 16 * VT;
-        if (tma) {
+        if (tma && mover) {
           unsigned char* dst[kMaxRanks];
           const unsigned char* src[kMaxRanks];
           uint64_t bytes[kMaxRanks];
@@ -320,38 +342,39 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
           }
           FenceProxyAsyncAll();
           if (!BulkCopyPieces(ring, dst, src, bytes, ws)) {
+            // Reported here; the warp leaves together at its next wait.
             ReportFailure(c.w, kStatusWaitTimeout, kWaitData, me, static_cast<int>(k), 0, 0);
             BroadcastAbort(c.w);
             s_stop = 1;
-            break;
           }
           FenceProxyAsyncAll();
-        } else {
+        } else if (!tma) {
           for (int s = 0; s < ws; ++s) {
             uint64_t b, e;
             WindowPart(full_nv, nv, s, ws, cta, ncta, &b, &e);
             CastIn<T, W>(reinterpret_cast<uint4*>(win), reinterpret_cast<const uint4*>(user), b, e, c.tid, c.nthr);
           }
         }
-        RolePost(c, kRowInReady, base | (k + 1));
+        RolePost(c, kRowInReady, k, base | (k + 1));
       }
     }
-  } else if (warp < 8) {
+  } else if (warp < load_warps + store_warps) {
     // ------------------------------------------------------------ storer
     c.role = kRoleStore;
     c.bar_id = kBarStore;
-    c.tid = threadIdx.x - kLoadThreads;
-    c.nthr = tma ? 1 : kStoreThreads;
-    if (c.tid < c.nthr) {
+    c.tid = threadIdx.x - 32 * load_warps;
+    c.nthr = 32 * store_warps;
+    const bool mover = !tma || c.tid == 0;
+    {
       BulkRing ring{smem + static_cast<size_t>(kBulkDepth) * kBulkChunk, s_full[1], 0};
       for (uint64_t k = 0; k < windows; ++k) {
-        const int j = static_cast<int>(k & 1);
+        const int j = static_cast<int>(k % kStagedBuffers);
         const uint64_t v0 = k * full_nv;
         const uint64_t nv = total_nv - v0 < full_nv ? total_nv - v0 : full_nv;
-        if (!RoleWait(c, kRowReduced, base | (k + 1), kWaitBarrier, static_cast<int>(k))) break;
+        if (!RoleWait(c, kRowReduced, k, base | (k + 1), kWaitBarrier, static_cast<int>(k))) break;
         const unsigned char* win = p.peers.arena[me] + p.out_off[j];
         unsigned char* user = static_cast<unsigned char*>(p.recvbuf) + v0 * 16 * VT;
-        if (tma) {
+        if (tma && mover) {
           unsigned char* dst[kMaxRanks];
           const unsigned char* src[kMaxRanks];
           uint64_t bytes[kMaxRanks];
@@ -366,39 +389,45 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
           // visible by the flags just acquired); the copy engine reads it.
           FenceProxyAsyncAll();
           if (!BulkCopyPieces(ring, dst, src, bytes, ws)) {
+            // Reported here; the warp leaves together at its next wait.
             ReportFailure(c.w, kStatusWaitTimeout, kWaitData, me, static_cast<int>(k), 0, 0);
             BroadcastAbort(c.w);
             s_stop = 1;
-            break;
           }
           FenceProxyAsyncAll();
-        } else {
+        } else if (!tma) {
           for (int s = 0; s < ws; ++s) {
             uint64_t b, e;
             WindowPart(full_nv, nv, s, ws, cta, ncta, &b, &e);
             CastOut<T, W>(reinterpret_cast<uint4*>(user), reinterpret_cast<const uint4*>(win), b, e, c.tid, c.nthr);
           }
         }
-        RolePost(c, kRowOutFree, base | (k + 1));
+        RolePost(c, kRowOutFree, k, base | (k + 1));
       }
     }
   } else {
     // ----------------------------------------------------------- reducer
-    c.role = kRoleReduce;
-    c.bar_id = kBarReduce;
-    c.tid = threadIdx.x - kLoadThreads - kStoreThreads;
-    c.nthr = kReduceThreads;
+    // Two groups (even and odd warps of the reducers) take the windows in turn.
+    const int rwarp = warp - load_warps - store_warps, rwarps = kStagedThreads / 32 - load_warps - store_warps;
+    const int sub = rwarp & 1;
+    const int reduce_threads = 32 * ((rwarps + 1 - sub) / 2);
+    c.role = kRoleReduce + sub;
+    c.bar_id = kBarReduce + sub;
+    c.tid = (rwarp >> 1) * 32 + static_cast<int>(threadIdx.x % 32);
+    c.nthr = reduce_threads;
     const bool do_scale = p.scale != 1.0;
     DeviceTraceRec* trace = (p.trace != nullptr && p.trace_capacity > 0) ? p.trace + static_cast<size_t>(cta) * p.trace_capacity : nullptr;
-    for (uint64_t k = 0; k < windows; ++k) {
-      const int j = static_cast<int>(k & 1);
+    for (uint64_t k = static_cast<uint64_t>(sub); k < windows; k += 2) {
+      const int j = static_cast<int>(k % kStagedBuffers);
       const uint64_t v0 = k * full_nv;
       const uint64_t nv = total_nv - v0 < full_nv ? total_nv - v0 : full_nv;
       // Every rank's input window k is filled (which also says that every rank
       // runs this call, hence is done with whatever used the pool before) ...
-      if (!RoleWait(c, kRowInReady, base | (k + 1), kWaitData, static_cast<int>(k))) break;
+      if (!RoleWait(c, kRowInReady, k, base | (k + 1), kWaitData, static_cast<int>(k))) break;
       // ... and every rank has emptied the output buffer this window reuses.
-      if (k >= 2 && !RoleWait(c, kRowOutFree, base | (k - 1), kWaitCredit, static_cast<int>(k))) break;
+      if (k >= kStagedBuffers &&
+          !RoleWait(c, kRowOutFree, k - kStagedBuffers, base | (k - kStagedBuffers + 1), kWaitCredit, static_cast<int>(k)))
+        break;
       if (trace != nullptr && c.tid == 0 && k < static_cast<uint64_t>(p.trace_capacity)) trace[k].t_wait_done = GlobalTimerNs();
       uint64_t b, e;
       WindowPart(full_nv, nv, me, ws, cta, ncta, &b, &e);
@@ -406,16 +435,16 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
         constexpr int kU = 4;
         const unsigned char* mi = p.peers.mc_arena + p.in_off[j];
         unsigned char* mo = p.peers.mc_arena + p.out_off[j];
-        for (uint64_t i = b + c.tid; i < e; i += static_cast<uint64_t>(kReduceThreads) * kU) {
+        for (uint64_t i = b + c.tid; i < e; i += static_cast<uint64_t>(reduce_threads) * kU) {
           uint4 v[kU];
 #pragma unroll
           for (int u = 0; u < kU; ++u) {
-            const uint64_t idx = i + static_cast<uint64_t>(u) * kReduceThreads;
+            const uint64_t idx = i + static_cast<uint64_t>(u) * reduce_threads;
             if (idx < e) v[u] = Multimem<W>::LdReduce(mi + idx * 16);
           }
 #pragma unroll
           for (int u = 0; u < kU; ++u) {
-            const uint64_t idx = i + static_cast<uint64_t>(u) * kReduceThreads;
+            const uint64_t idx = i + static_cast<uint64_t>(u) * reduce_threads;
             if (idx < e) {
               if (do_scale) {
                 AW acc[P];
@@ -437,9 +466,9 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
                                  for (int q = 0; q < kMaxRanks; ++q)
                                    if (q < ws) St16(arenas[q] + out_off + idx * 16, r);
                                },
-                               static_cast<unsigned>(c.tid), kReduceThreads);
+                               static_cast<unsigned>(c.tid), static_cast<unsigned>(reduce_threads));
       }
-      RolePost(c, kRowReduced, base | (k + 1));
+      RolePost(c, kRowReduced, k, base | (k + 1));
       if (trace != nullptr && c.tid == 0 && k < static_cast<uint64_t>(p.trace_capacity)) trace[k].t_done = GlobalTimerNs();
     }
   }

@@ -2,9 +2,12 @@
 // p2p_sendrecv.cu): a waiter thread that runs ahead and waits for the flags of
 // the coming steps, data warps that stream step after step without a CTA-wide
 // barrier, and a poster thread that follows behind, fences the data warps'
-// stores and publishes the step's flags.  Two counters in shared memory carry
-// the hand-over: steps ready (written by the waiter) and (data warp, step)
-// pairs done.  All spins are bounded.
+// stores and publishes the step's flags.  Counters in shared memory carry the
+// hand-over: steps ready (written by the waiter) and, per data warp, steps
+// done.  (One shared count of finished (warp, step) pairs would not do: the
+// data warps are not in lock-step, and a warp that is two steps ahead would
+// stand in for one that has not finished the step being published.)  All
+// spins are bounded.
 #pragma once
 
 #include <cstdint>
@@ -14,11 +17,19 @@
 namespace ibcomm {
 namespace dev {
 
+constexpr int kMaxDataWarps = 16;
+
 struct RoleSync {
-  unsigned ready;  // steps whose flags have arrived (written by the waiter)
-  unsigned done;   // (data warp, step) pairs whose stores have been issued
-  int stop;        // a wait gave up or a self-check failed: everybody leaves
+  unsigned ready;                // steps whose flags have arrived (written by the waiter)
+  unsigned done[kMaxDataWarps];  // per data warp: steps whose stores it has issued
+  int stop;                      // a wait gave up or a self-check failed: everybody leaves
 };
+
+__device__ __forceinline__ void RoleSyncInit(RoleSync* s) {
+  s->ready = 0;
+  for (int i = 0; i < kMaxDataWarps; ++i) s->done[i] = 0;
+  s->stop = 0;
+}
 
 __device__ __forceinline__ unsigned SmemU32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ unsigned LdAcquireShared(const unsigned* p) {
@@ -46,6 +57,13 @@ __device__ __forceinline__ bool SpinShared(const unsigned* counter, unsigned tar
       return false;
     }
   }
+}
+
+// Spins until every one of the `warps` data warps has finished `target` steps.
+__device__ __forceinline__ bool SpinAllWarpsDone(RoleSync* sync, int warps, unsigned target, uint64_t timeout_ns) {
+  for (int w = 0; w < warps; ++w)
+    if (!SpinShared(&sync->done[w], target, sync, timeout_ns)) return false;
+  return true;
 }
 
 }  // namespace dev

@@ -404,7 +404,16 @@ bool Communicator::SendPoll(int dest_rank) {
   Endpoint& ep = eps_[static_cast<size_t>(dest_rank)];
 #ifdef USE_CUDA
   if (ep.dev_send_outstanding) {
-    if (!DeviceContextSendPoll(device_.get(), dest_rank)) return false;
+    // A send whose kernel reported a failure is over all the same: the next
+    // one must not be refused as "still outstanding".
+    bool done;
+    try {
+      done = DeviceContextSendPoll(device_.get(), dest_rank);
+    } catch (...) {
+      ep.dev_send_outstanding = false;
+      throw;
+    }
+    if (!done) return false;
     ep.dev_send_outstanding = false;
     return true;
   }
@@ -421,7 +430,14 @@ bool Communicator::RecvPoll(int src_rank) {
   Endpoint& ep = eps_[static_cast<size_t>(src_rank)];
 #ifdef USE_CUDA
   if (ep.dev_recv_outstanding) {
-    if (!DeviceContextRecvPoll(device_.get(), src_rank)) return false;
+    bool done;
+    try {
+      done = DeviceContextRecvPoll(device_.get(), src_rank);
+    } catch (...) {
+      ep.dev_recv_outstanding = false;
+      throw;
+    }
+    if (!done) return false;
     ep.dev_recv_outstanding = false;
     return true;
   }
@@ -513,8 +529,8 @@ void Communicator::SendWait(int dest_rank) {
   Endpoint& ep = eps_[static_cast<size_t>(dest_rank)];
 #ifdef USE_CUDA
   if (ep.dev_send_outstanding) {
+    ep.dev_send_outstanding = false;  // over when the wait returns, failed or not
     DeviceContextSendWait(device_.get(), dest_rank);
-    ep.dev_send_outstanding = false;
     return;
   }
 #endif
@@ -528,8 +544,8 @@ void Communicator::RecvWait(int src_rank) {
   Endpoint& ep = eps_[static_cast<size_t>(src_rank)];
 #ifdef USE_CUDA
   if (ep.dev_recv_outstanding) {
+    ep.dev_recv_outstanding = false;  // over when the wait returns, failed or not
     DeviceContextRecvWait(device_.get(), src_rank);
-    ep.dev_recv_outstanding = false;
     return;
   }
 #endif
@@ -542,6 +558,16 @@ void Communicator::Bcast(void* buf, size_t len, int root) {
   CheckPeer(root, "Bcast");
   if (my_rank_ < 0) IBCOMM_FAIL(INVALID_ARGUMENT, "Bcast: call RegisterMyself first.\n");
   if (world_size_ == 1) return;
+#ifdef USE_CUDA
+  // Device buffers on a box with NVSwitch multicast: the root writes every
+  // piece once and the switch delivers it to all ranks.  (Every rank takes the
+  // same decision: it depends on the box, the length and the alignment, and
+  // the ranks pass buffers of the same kind.)
+  if (len != 0 && DeviceContextIsDevicePointer(buf)) {
+    PrepareMemoryPool();
+    if (DeviceContextBcast(device_.get(), buf, len, root)) return;
+  }
+#endif
   if (my_rank_ == root) {
     for (size_t r = 0; r < world_size_; ++r)
       if (static_cast<int>(r) != root) Send(static_cast<int>(r), buf, len, false);

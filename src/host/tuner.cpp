@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "ibcomm/device_context.h"
+#include "ibcomm/tunables.h"
 
 namespace ibcomm {
 
@@ -62,8 +63,10 @@ int ChooseChannels(Algo algo, size_t bytes, int world_size, int max_channels) {
   int ch;
   switch (algo) {
     case Algo::kOneShot:
-      // One CTA per 32 KiB keeps the flag fan-out small at the latency end.
-      ch = static_cast<int>(std::min<size_t>(16, (bytes + (32u << 10) - 1) / (32u << 10)));
+      // One CTA per 32 KiB keeps the flag fan-out small at the latency end; a
+      // CTA sustains about 10 GB/s of peer stores, so megabyte messages get
+      // up to 96 of them.
+      ch = static_cast<int>(std::min<size_t>(96, (bytes + (32u << 10) - 1) / (32u << 10)));
       break;
     case Algo::kNvls:
       // The switch does the math; 32-64 CTAs saturate it (more only add
@@ -84,6 +87,18 @@ int ChooseChannels(Algo algo, size_t bytes, int world_size, int max_channels) {
     }
   }
   return std::max(1, std::min(ch, max_channels));
+}
+
+// Largest message of ordinary buffers that goes one-shot.  A one-shot call
+// moves (ws - 1) S per direction against the two-shot's 2 S (ws - 1) / ws but
+// needs one synchronisation instead of three; with two ranks the byte counts
+// are equal and only the slot size limits it.
+static size_t OneShotLimit(int world_size) {
+  const int knob = Tunable("IBCOMM_ONESHOT_MAX_KIB", 0);
+  if (knob > 0) return static_cast<size_t>(knob) << 10;
+  if (world_size <= 2) return 16u << 20;
+  if (world_size <= 4) return 2u << 20;
+  return 1u << 20;
 }
 
 TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, bool zero_copy, int max_channels) {
@@ -111,16 +126,17 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
       // ranks): one push per peer wins while the fan-out is small.
       a = bytes <= (world_size > 4 ? (16u << 10) : (512u << 10)) ? Algo::kOneShot : Algo::kDirect;
     }
-  } else if (bytes <= (512u << 10)) {
+  } else if (bytes <= OneShotLimit(world_size)) {
     a = Algo::kOneShot;  // ordinary buffers: one push per peer beats three staged phases
-  } else if (nvls_available && world_size > 2 && bytes <= (64u << 20)) {
-    a = Algo::kNvls;  // staged through the pool inside the kernel
-  } else if (bytes <= (32u << 20)) {
+  } else if (nvls_available && world_size > 2) {
+    a = Algo::kNvls;  // through the pool, pipelined inside the kernel (staged_kernel.cu)
+  } else if (world_size > 2 && bytes <= (32u << 20)) {
     a = Algo::kDirect;  // staged; two synchronisation steps
   } else {
-    // Large messages in ordinary memory: the chunk-pipelined programs keep
-    // their staging inside the transfer.  Halving/doubling needs fewer steps.
-    a = util::GetExpOfTwo(static_cast<uint64_t>(world_size)) != 0 ? Algo::kRabenseifner : Algo::kRing;
+    // Large messages in ordinary memory without the switch, and two ranks: the
+    // chunk-pipelined programs keep their staging inside the transfer.
+    // Halving/doubling needs fewer steps.
+    a = (world_size > 2 && util::GetExpOfTwo(static_cast<uint64_t>(world_size)) != 0) ? Algo::kRabenseifner : Algo::kRing;
   }
   int ch = ChooseChannels(a, bytes, world_size, max_channels);
   // Staged switch path: the copies in and out of the pool run on the same

@@ -129,16 +129,20 @@ bool RunAllreduce(int ws, int ncta, uint64_t n, uint64_t cap_elems) {
 }
 
 // ---- pipelined staged two-shot (staged_kernel.cu) ----
-// One thread per (rank, CTA, role): loader, reducer, storer.  Two input and
-// two output windows per rank; three flag rows per (rank, CTA, source).  The
-// waits and posts are the kernel's: loader k waits reduced >= k-1, reducer k
-// waits in_ready >= k+1 and out_free >= k-1, storer k waits reduced >= k+1.
+// One thread per (rank, CTA, role): loader, reducer A (even windows), reducer
+// B (odd windows), storer.  Three input and three output windows per rank;
+// four flag rows per (rank, CTA, source): in_ready, reduced (even windows),
+// reduced (odd windows), out_free.  The waits and posts are the kernel's:
+// loader k waits reduced >= k-2 (the window that used the buffer three
+// windows ago), reducer k waits in_ready >= k+1 and out_free >= k-2, storer k
+// waits reduced >= k+1.
+constexpr int kBufs = 3;
 struct PipeWorld {
   int ws, ncta;
-  std::vector<std::vector<int64_t>> in[2], out[2];
-  std::vector<std::atomic<uint64_t>> row[3];  // 0 in_ready, 1 reduced, 2 out_free
+  std::vector<std::vector<int64_t>> in[kBufs], out[kBufs];
+  std::vector<std::atomic<uint64_t>> row[4];  // 0 in_ready, 1 reduced even, 2 reduced odd, 3 out_free
   PipeWorld(int ws_, int ncta_, size_t window) : ws(ws_), ncta(ncta_) {
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < kBufs; ++j) {
       in[j].assign(ws_, std::vector<int64_t>(window, -7));
       out[j].assign(ws_, std::vector<int64_t>(window, -7));
     }
@@ -147,6 +151,7 @@ struct PipeWorld {
       for (auto& f : r) f.store(0);
     }
   }
+  static int ReducedRow(uint64_t window) { return 1 + static_cast<int>(window & 1); }
   std::atomic<uint64_t>& Flag(int which, int rank, int cta, int src) { return row[which][(static_cast<size_t>(rank) * ncta + cta) * ws + src]; }
   void WaitAll(int which, int rank, int cta, uint64_t v) {
     for (int q = 0; q < ws; ++q)
@@ -157,25 +162,27 @@ struct PipeWorld {
   }
 };
 
+// role: 0 loader, 1 reducer A, 2 reducer B, 3 storer.
 void PipeRole(PipeWorld* w, int role, uint64_t seq, int rank, int cta, const std::vector<int64_t>& send, std::vector<int64_t>* recv,
               uint64_t total_nv, uint64_t full_nv) {
   const int ws = w->ws, ncta = w->ncta;
   const uint64_t base = seq << 32;
   const uint64_t windows = (total_nv + full_nv - 1) / full_nv;
-  for (uint64_t k = 0; k < windows; ++k) {
-    const int j = static_cast<int>(k & 1);
+  const bool reducer = role == 1 || role == 2;
+  for (uint64_t k = reducer ? static_cast<uint64_t>(role - 1) : 0; k < windows; k += reducer ? 2 : 1) {
+    const int j = static_cast<int>(k % kBufs);
     const uint64_t v0 = k * full_nv, nv = std::min(full_nv, total_nv - v0);
     if (role == 0) {
-      if (k >= 2) w->WaitAll(1, rank, cta, base | (k - 1));
+      if (k >= kBufs) w->WaitAll(PipeWorld::ReducedRow(k - kBufs), rank, cta, base | (k - kBufs + 1));
       for (int s = 0; s < ws; ++s) {
         uint64_t b, e;
         WindowPart(full_nv, nv, s, ws, cta, ncta, &b, &e);
         for (uint64_t i = b * kVec; i < e * kVec; ++i) w->in[j][rank][i] = send[v0 * kVec + i];
       }
       w->PostAll(0, rank, cta, base | (k + 1));
-    } else if (role == 1) {
+    } else if (reducer) {
       w->WaitAll(0, rank, cta, base | (k + 1));
-      if (k >= 2) w->WaitAll(2, rank, cta, base | (k - 1));
+      if (k >= kBufs) w->WaitAll(3, rank, cta, base | (k - kBufs + 1));
       uint64_t b, e;
       WindowPart(full_nv, nv, rank, ws, cta, ncta, &b, &e);
       for (uint64_t i = b * kVec; i < e * kVec; ++i) {
@@ -183,15 +190,15 @@ void PipeRole(PipeWorld* w, int role, uint64_t seq, int rank, int cta, const std
         for (int q = 0; q < ws; ++q) acc += w->in[j][q][i];
         for (int q = 0; q < ws; ++q) w->out[j][q][i] = acc;
       }
-      w->PostAll(1, rank, cta, base | (k + 1));
+      w->PostAll(PipeWorld::ReducedRow(k), rank, cta, base | (k + 1));
     } else {
-      w->WaitAll(1, rank, cta, base | (k + 1));
+      w->WaitAll(PipeWorld::ReducedRow(k), rank, cta, base | (k + 1));
       for (int s = 0; s < ws; ++s) {
         uint64_t b, e;
         WindowPart(full_nv, nv, s, ws, cta, ncta, &b, &e);
         for (uint64_t i = b * kVec; i < e * kVec; ++i) (*recv)[v0 * kVec + i] = w->out[j][rank][i];
       }
-      w->PostAll(2, rank, cta, base | (k + 1));
+      w->PostAll(3, rank, cta, base | (k + 1));
     }
   }
 }
@@ -212,7 +219,7 @@ bool RunPipelined(int ws, int ncta, uint64_t n_vec, uint64_t cap_elems) {
       std::fill(recv[r].begin(), recv[r].end(), -1);
       std::vector<std::thread> t;
       for (int c = 0; c < ncta; ++c)
-        for (int role = 0; role < 3; ++role) t.emplace_back(PipeRole, &w, role, seq, r, c, std::cref(send[r]), &recv[r], n_vec, full_nv);
+        for (int role = 0; role < 4; ++role) t.emplace_back(PipeRole, &w, role, seq, r, c, std::cref(send[r]), &recv[r], n_vec, full_nv);
       for (auto& x : t) x.join();
       for (uint64_t i = 0; i < n; ++i)
         if (recv[r][i] != Sum(ws, i)) ++bad;

@@ -217,19 +217,45 @@ def case_sendrecv(comm):
     """Device buffers through the mailbox kernels; ring of neighbours plus a broadcast."""
     comm.device_info(connect=True)
     to, frm = (RANK + 1) % WS, (RANK - 1) % WS
-    for nbytes in (4, 1000, 256 << 10, (3 << 20) + 17):
-        out = torch.full((nbytes,), RANK + 1, dtype=torch.uint8, device="cuda")
-        out[-1] = 77
+    for nbytes in (0, 4, 1000, 256 << 10, (3 << 20) + 17, (40 << 20) + 48):
+        # Payload: a byte pattern that depends on the position and on the sender; compared in full.
+        pos = torch.arange(nbytes, device="cuda", dtype=torch.int64)
+        out = ((pos * 7 + RANK * 13) % 251).to(torch.uint8)
         inn = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
         comm.send(to, out, blocking=False)
         comm.recv(frm, inn, blocking=True)
         comm.send_wait(to)
-        if int(inn[0]) != frm + 1 or int(inn[-1]) != 77:
-            print(f"rank {RANK}: sendrecv {nbytes} mismatch", file=sys.stderr)
+        if not torch.equal(inn, ((pos * 7 + frm * 13) % 251).to(torch.uint8)):
+            bad = (inn != ((pos * 7 + frm * 13) % 251).to(torch.uint8)).nonzero().flatten()
+            print(f"rank {RANK}: sendrecv {nbytes} mismatch at {bad[:4].tolist()} ({bad.numel()} bytes)", file=sys.stderr)
             return 1
-    t = torch.full((4096,), float(RANK), device="cuda")
-    comm.bcast(t, root=WS - 1)
-    if not torch.all(t == float(WS - 1)):
+    # an odd (only byte-aligned) view takes the byte path
+    base_o = torch.arange(100001, device="cuda", dtype=torch.int64).remainder(199).to(torch.uint8)
+    base_i = torch.zeros(100003, dtype=torch.uint8, device="cuda")
+    comm.send(to, base_o[1:], blocking=False)
+    comm.recv(frm, base_i[3:], blocking=True)
+    comm.send_wait(to)
+    if not torch.equal(base_i[3:], base_o[1:]):
+        print(f"rank {RANK}: unaligned sendrecv mismatch", file=sys.stderr)
+        return 1
+    # Broadcasts: through the switch where the box has multicast (lengths that are multiples of 16, several
+    # slots' worth, changing roots so that every rank's slot credits are exercised), by sends otherwise
+    # (a length that is not a multiple of 16) - and from a buffer that is only byte-aligned.
+    for it, (nbytes, root) in enumerate(((16384, WS - 1), (20 << 20, 0), (20 << 20, WS - 1), (1 << 20, 1 % WS), (1000, 0), (48 << 20, 0))):
+        pos = torch.arange(nbytes, device="cuda", dtype=torch.int64)
+        want = ((pos * 3 + root * 17 + it) % 253).to(torch.uint8)
+        t = want.clone() if RANK == root else torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        comm.bcast(t, root=root)
+        if not torch.equal(t, want):
+            print(f"rank {RANK}: bcast {nbytes} from {root} mismatch", file=sys.stderr)
+            return 1
+    base = torch.zeros(4096 + 1, dtype=torch.uint8, device="cuda")
+    view = base[1:]
+    if RANK == 0:
+        view.copy_(torch.arange(4096, device="cuda").remainder(101).to(torch.uint8))
+    comm.bcast(view, root=0)
+    if not torch.equal(view, torch.arange(4096, device="cuda").remainder(101).to(torch.uint8)):
+        print(f"rank {RANK}: unaligned bcast mismatch", file=sys.stderr)
         return 1
     # host buffers still travel over the host transport
     hs = torch.full((1000,), float(RANK))
@@ -354,6 +380,202 @@ def case_leave(comm):
     return 1
 
 
+def case_pipelined(comm):
+    """Ordinary (unmapped) buffers through the pipelined staged kernel: lengths of one and of many
+    windows, both copy modes, in place, and fp32 with a 16-bit wire (which every rank must round alike)."""
+    info = comm.device_info(connect=True)
+    rc = 0
+    algos = ["direct"] + (["nvls"] if info["nvls"] else [])
+    for algo in algos:
+        for tma in (1, 0):
+            ar.utils.set_tunable("IBCOMM_STAGED_TMA", tma)
+            for n in (4 * WS, 1 << 16, 8 << 20, 40_000_000):
+                x = seeded(n, torch.float32, RANK, seed=3)
+                y = torch.empty_like(x)
+                comm.allreduce(x, y, algo=algo, scale=0.5, sync=True)
+                if not close(y, expected(n, torch.float32, 0.5, seed=3), torch.float32):
+                    print(f"rank {RANK}: pipelined {algo} tma={tma} n={n} mismatch", file=sys.stderr)
+                    rc = 1
+            x = seeded(20_000_000, torch.float32, RANK, seed=4)
+            for _ in range(3):  # back to back, no host synchronisation in between
+                comm.allreduce(x, algo=algo, scale=1.0 / WS)
+            torch.cuda.synchronize()
+            comm.check()
+            want = expected(20_000_000, torch.float32, 1.0 / WS, seed=4)  # the mean of equal values is the value
+            if not close(x, want, torch.float32):
+                print(f"rank {RANK}: pipelined in-place {algo} tma={tma} mismatch", file=sys.stderr)
+                rc = 1
+        ar.utils.set_tunable("IBCOMM_STAGED_TMA", -1)
+        for wire in (torch.bfloat16, torch.float16):
+            n = 10_000_000
+            x = seeded(n, torch.float32, RANK, seed=8)
+            y = torch.empty_like(x)
+            comm.allreduce(x, y, algo=algo, wire=wire, scale=1.0 / WS, sync=True)
+            if not close(y, expected(n, torch.float32, 1.0 / WS, seed=8), torch.float32, wire=wire):
+                print(f"rank {RANK}: {algo} with {wire} wire mismatch", file=sys.stderr)
+                rc = 1
+            # all ranks hold the same bits
+            digest = y.view(torch.int32).sum(dtype=torch.int64).reshape(1).double().repeat(8)
+            total = digest.clone()
+            comm.allreduce(total, algo="oneshot", sync=True)
+            if abs(float(total[0].item()) - WS * float(digest[0].item())) > 0.5:
+                print(f"rank {RANK}: {algo} with {wire} wire: ranks differ", file=sys.stderr)
+                rc = 1
+    return rc
+
+
+def case_hybrid(comm):
+    """The hybrid two-shot (part of the message reduced in the switch, the rest by peer loads, in one kernel)."""
+    info = comm.device_info(connect=True)
+    if not info["nvls"]:
+        return 0
+    rc = 0
+    n = (16 << 20) + 5
+    a = comm.symmetric_empty(n, torch.float32)
+    b = comm.symmetric_empty(n, torch.float32)
+    try:
+        for pct, sw, di in ((25, 48, 96), (10, 96, 16), (90, 8, 100), (50, 1, 1)):
+            ar.utils.set_tunable("IBCOMM_NVLS_HYBRID", pct)
+            ar.utils.set_tunable("IBCOMM_NVLS_HYBRID_SWITCH_CTAS", sw)
+            ar.utils.set_tunable("IBCOMM_NVLS_HYBRID_DIRECT_CTAS", di)
+            for it in range(2):
+                a.copy_(seeded(n, torch.float32, RANK, seed=it + pct))
+                comm.allreduce(a, b, algo="nvls", scale=1.0 / WS, sync=True)
+                if comm.device_info()["last_channels"] != sw + di:
+                    print(f"rank {RANK}: the hybrid kernel did not run ({comm.device_info()})", file=sys.stderr)
+                    rc = 1
+                if not close(b, expected(n, torch.float32, 1.0 / WS, seed=it + pct), torch.float32):
+                    print(f"rank {RANK}: hybrid {pct}% out-of-place mismatch", file=sys.stderr)
+                    rc = 1
+                comm.allreduce(a, algo="nvls", sync=True)  # in place
+                if not close(a, expected(n, torch.float32, 1.0, seed=it + pct), torch.float32):
+                    print(f"rank {RANK}: hybrid {pct}% in-place mismatch", file=sys.stderr)
+                    rc = 1
+    finally:
+        for k in ("IBCOMM_NVLS_HYBRID", "IBCOMM_NVLS_HYBRID_SWITCH_CTAS", "IBCOMM_NVLS_HYBRID_DIRECT_CTAS"):
+            ar.utils.set_tunable(k, -1)
+    return rc
+
+
+def case_p2p_errors(comm):
+    """Device Send/Recv failure paths on two ranks; nothing faults, every wait is bounded."""
+    comm.device_info(connect=True)
+    other = 1 - RANK
+    # (1) a receive without a matching send runs out of time on rank 1 ...
+    if RANK == 1:
+        comm.set_timeout_ms(500)
+        buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+        try:
+            comm.recv(0, buf, blocking=True)
+            print("rank 1: the unmatched receive returned", file=sys.stderr)
+            return 1
+        except ar.IbcommError as e:
+            if e.code != ar.TRANSPORT_ERROR:
+                return 1
+        comm.set_timeout_ms(10000)
+    comm.barrier()
+    # ... and the other direction (its own counters) still works afterwards.
+    out = torch.full((1 << 20,), 7 + RANK, dtype=torch.uint8, device="cuda")
+    inn = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    if RANK == 1:
+        comm.send(0, out, blocking=True)
+    else:
+        comm.recv(1, inn, blocking=True)
+        if not torch.all(inn == 8):
+            print("rank 0: message after the timed-out receive is wrong", file=sys.stderr)
+            return 1
+    comm.barrier()
+    # (2) length mismatch: 1000 bytes sent, 2000 expected.
+    if RANK == 1:
+        comm.send(0, out[:1000], blocking=True)
+    else:
+        try:
+            comm.recv(1, inn[:2000], blocking=True)
+            print("rank 0: the mismatched receive returned", file=sys.stderr)
+            return 1
+        except ar.IbcommError as e:
+            if e.code != ar.TRANSPORT_ERROR or "length mismatch" not in str(e):
+                print(f"rank 0: unexpected error {e}", file=sys.stderr)
+                return 1
+    comm.barrier()
+    # (3) both sides counted one piece for that message, so the next one lines up.
+    if RANK == 1:
+        comm.send(0, out[:5000], blocking=True)
+    else:
+        comm.recv(1, inn[:5000], blocking=True)
+        if not torch.all(inn[:5000] == 8):
+            return 1
+    return 0
+
+
+def case_overlap(comm):
+    """Collectives on a side stream next to a compute stream that is kept busy."""
+    import time
+    comm.device_info(connect=True)
+    n = 8 << 20
+    side = torch.cuda.Stream()
+    a = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    xs = [seeded(n, torch.float32, RANK, seed=s) for s in range(4)]
+    ys = [torch.empty_like(x) for x in xs]
+    sym = comm.symmetric_empty(n, torch.float32)
+    sym.copy_(xs[0])
+    torch.cuda.synchronize()
+    comm.barrier()
+    t0 = time.time()
+    for rep in range(3):
+        for _ in range(40):
+            a @ a  # compute stream: a few hundred microseconds each
+        with torch.cuda.stream(side):
+            for i, algo in enumerate(("ring", "rabenseifner", "direct", "auto")):
+                comm.allreduce(xs[i], ys[i], algo=algo, scale=1.0 / WS, stream=side)
+            comm.allreduce(sym, algo="auto", scale=1.0, stream=side)
+        for _ in range(40):
+            a @ a
+    torch.cuda.synchronize()
+    elapsed = time.time() - t0
+    comm.check()
+    for i in range(4):
+        if not close(ys[i], expected(n, torch.float32, 1.0 / WS, seed=i), torch.float32):
+            print(f"rank {RANK}: overlap result {i} mismatch", file=sys.stderr)
+            return 1
+    if elapsed > 4.0:  # far below the 5 s wait limit the test sets: nothing waited for a CTA that never ran
+        print(f"rank {RANK}: collectives next to compute took {elapsed:.2f} s", file=sys.stderr)
+        return 1
+    return 0
+
+
+def case_leave_subset(comm):
+    """A rank leaves between steps; the survivors see the error, form a smaller communicator and go on."""
+    x = torch.ones(1 << 16, device="cuda")
+    comm.allreduce(x, algo="ring", sync=True)
+    if not torch.all(x == float(WS)):
+        return 1
+    if RANK == WS - 1:
+        torch.cuda.synchronize()
+        return 0
+    comm.set_timeout_ms(1000)
+    try:
+        comm.allreduce(x, algo="ring", sync=True)
+        return 1
+    except ar.IbcommError as e:
+        if e.code != ar.TRANSPORT_ERROR:
+            return 1
+    survivors = list(range(WS - 1))
+    sub = ar.Communicator.from_env(tag="after", ranks=survivors)
+    rc = 0
+    for algo in ("ring", "rabenseifner", "direct", "oneshot", "auto"):
+        n = 1 << 15 if algo == "oneshot" else 1 << 20
+        y = torch.full((n,), float(RANK + 1), device="cuda")
+        sub.allreduce(y, algo=algo, sync=True)
+        if not torch.all(y == float(sum(r + 1 for r in survivors))):
+            print(f"rank {RANK}: survivors' {algo} allreduce is wrong", file=sys.stderr)
+            rc = 1
+    torch.cuda.synchronize()
+    sub.barrier()
+    sub.close()
+    return rc
+
+
 def main():
     case = sys.argv[1]
     ngpu = torch.cuda.device_count()
@@ -364,7 +586,7 @@ def main():
     comm = ar.Communicator.from_env()
     rc = globals()[f"case_{case}"](comm)
     torch.cuda.synchronize()
-    if case != "leave":
+    if case not in ("leave", "leave_subset"):
         comm.barrier()
     comm.close()
     return rc

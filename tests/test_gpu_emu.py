@@ -253,7 +253,7 @@ def test_error_codes():
     with pytest.raises(ar.IbcommError) as e:
         w.allreduce(a, None, algo="ring")
     assert e.value.code == ar.NOT_SUPPORTED  # fewer elements than ranks
-    big = [torch.zeros(1 << 20, device="cuda") for _ in range(2)]
+    big = [torch.zeros((16 << 20) // 4 + 4, device="cuda") for _ in range(2)]  # one vector more than a two-rank slot holds
     with pytest.raises(ar.IbcommError) as e:
         w.allreduce(big, None, algo="oneshot")
     assert e.value.code == ar.INVALID_ARGUMENT  # beyond the one-shot slot
@@ -393,3 +393,52 @@ def test_tester_binary_emulated(bins):
     assert p.returncode == 1
     p = subprocess.run([bins["allreduce_tester"], "--emulate", "2", "ring", "4", "1", "np"], stderr=subprocess.PIPE)
     assert p.returncode == 4
+
+
+def _tester(bins, args, env=None, timeout=600):
+    import os
+    import subprocess
+    p = subprocess.run([bins["allreduce_tester"], *args], env=dict(os.environ, **(env or {})), stdout=subprocess.PIPE,
+                       stderr=subprocess.PIPE, text=True, timeout=timeout)
+    return p.returncode, p.stderr
+
+
+def test_chunk_size_on_the_device_path(bins):
+    # The reference's chunk-size cases (tests/allreduce_test.py:180-225) on device buffers: 4 emulated ranks,
+    # 1 KiB of ints, IBCOMM_CHUNKSIZE 4..128 bytes -> 0; 0..3, -128 and "1k" -> invalid argument.
+    for algo in ("ring", "rabenseifner"):
+        for chunk in (4, 8, 16, 32, 64, 128):
+            code, err = _tester(bins, ["--emulate", "4", algo, "1k", "i*np+p", "i*np*np+np*(np-1)/2"], {"IBCOMM_CHUNKSIZE": str(chunk)})
+            assert code == 0, (algo, chunk, err)
+    for chunk in ("0", "1", "2", "3", "-128", "1k"):
+        code, _ = _tester(bins, ["--emulate", "4", "ring", "1k", "1", "np"], {"IBCOMM_CHUNKSIZE": chunk})
+        assert code == ar.INVALID_ARGUMENT, chunk
+
+
+@pytest.mark.parametrize("algo", ["rabenseifner", "ring"])
+def test_staging_offsets_that_are_not_vector_aligned(algo):
+    # Short messages cut chunk boundaries at arbitrary elements: a range can then be 16-byte aligned in the
+    # user buffer and not in the (narrower) staging slot, or the other way round; such slices take the
+    # element-by-element path.  Lengths and views chosen to hit both.
+    for ws in (3, 4):
+        w = world(ws)
+        for wire in (torch.bfloat16, torch.float16):
+            for n in (1000, 2521):
+                ins = make_inputs(ws, n, torch.float32, seed=n)
+                outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+                w.allreduce(ins, outs, algo=algo, wire=wire)
+                check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws, wire=wire)
+        base = make_inputs(ws, 2521 + 4, torch.float16, seed=2)
+        ins = [t[4:] for t in base]  # 8-byte offset in a 16-bit type
+        outs = [torch.zeros(2521 + 4, device="cuda", dtype=torch.float16)[4:] for _ in range(ws)]
+        w.allreduce(ins, outs, algo=algo)
+        check(outs, reference(ins, 1.0, torch.float16), torch.float16, ws)
+
+
+@pytest.mark.slow
+def test_aging_on_the_device_path(bins):
+    # The reference's ageing case (tests/allreduce_test.py:227-235): 100 ring and 100 Rabenseifner allreduces
+    # back to back on device buffers, 4 ranks (emulated here; 32 MiB each).
+    for algo in ("ring", "rabenseifner"):
+        code, err = _tester(bins, ["--emulate", "4", "--iters", "100", algo, "32M", "i*np+p", "i*np*np+np*(np-1)/2"])
+        assert code == 0, (algo, err)

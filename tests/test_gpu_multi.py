@@ -133,3 +133,62 @@ def test_tester_binary_on_gpus(bins):
                "i*np+p", "i*np*np+np*(np-1)/2"]
         p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
         assert p.returncode == 0, p.stderr[-2000:]
+
+
+@needs2
+@pytest.mark.parametrize("np_", [n for n in (2, 4, 8) if n <= NGPU])
+def test_pipelined_staged_two_shot(bins, np_):
+    # Ordinary buffers through the pipelined kernel (switch and direct), several windows, 16-bit wire.
+    code, err = run(bins, np_, "pipelined")
+    assert code == 0, err
+
+
+@needs2
+@pytest.mark.parametrize("np_", [n for n in (2, 4, 8) if n <= NGPU])
+def test_hybrid_switch_plus_direct(bins, np_):
+    code, err = run(bins, np_, "hybrid")
+    assert code == 0, err
+
+
+@needs2
+def test_device_send_recv_errors_leave_the_communicator_usable(bins):
+    # A receive that nothing matches runs into its wait limit; a receive posted for another length than
+    # the message reports the mismatch; messages of other pairs and later messages still work.
+    code, err = run(bins, 2, "p2p_errors")
+    assert code == 0, err
+
+
+@needs2
+def test_collective_next_to_compute(bins):
+    # Allreduces on a side stream while a matmul loop keeps the compute stream busy (what
+    # GradientBuckets.overlap_with_backward does): must finish well inside the wait limit.
+    code, err = run(bins, min(NGPU, 4), "overlap", env={"IBCOMM_TIMEOUT_MS": "5000"})
+    assert code == 0, err
+
+
+@pytest.mark.skipif(NGPU < 3, reason="needs at least three GPUs")
+def test_survivors_continue_on_gpus(bins):
+    # After a rank has left between steps the others get the transport error, build a communicator over
+    # the remaining ranks and carry on with device allreduces.  NVLS off (see test_rank_leaving_is_detected).
+    code, err = run(bins, min(NGPU, 4), "leave_subset", env={"IBCOMM_DISABLE_NVLS": "1", "NCCL_NVLS_ENABLE": "0"})
+    assert code == 0, err
+
+
+@needs2
+def test_chunk_size_on_real_gpus(bins):
+    for chunk in (4, 32, 128):
+        cmd = ["timeout", "120s", bins["ibcomm_run"], "-np", "2", "-x", f"IBCOMM_CHUNKSIZE={chunk}", bins["allreduce_tester"],
+               "--device", "cuda", "ring", "1k", "i*np+p", "i*np*np+np*(np-1)/2"]
+        p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        assert p.returncode == 0, p.stderr[-2000:]
+
+
+@needs2
+@pytest.mark.slow
+def test_aging_on_real_gpus(bins):
+    np_ = min(NGPU, 4)
+    for algo in ("ring", "rabenseifner"):
+        cmd = ["timeout", "600s", bins["ibcomm_run"], "-np", str(np_), bins["allreduce_tester"], "--device", "cuda", "--iters", "100",
+               algo, "128M", "i*np+p", "i*np*np+np*(np-1)/2"]
+        p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        assert p.returncode == 0, p.stderr[-2000:]

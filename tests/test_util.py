@@ -134,10 +134,12 @@ def test_algorithm_table():
     assert ca(256 * MiB, 4)[0] == "nvls"
     assert ca(256 * MiB, 2)[0] == "direct"                       # two ranks: 1.0 S per direction beats 1.5 S
     assert ca(256 * MiB, 8, nvls=False)[0] == "direct"           # registered buffers, or no multicast
-    assert ca(256 * MiB, 8, mapped=False)[0] == "rabenseifner"   # ordinary buffers, power-of-two ranks
-    assert ca(256 * MiB, 6, mapped=False)[0] == "ring"
-    assert ca(8 * MiB, 8, mapped=False)[0] == "nvls"             # staged through the pool inside the kernel
+    assert ca(256 * MiB, 8, mapped=False)[0] == "nvls"           # ordinary buffers: through the pool, pipelined in the kernel
+    assert ca(256 * MiB, 8, nvls=False, mapped=False)[0] == "rabenseifner"   # no switch, power-of-two ranks
+    assert ca(256 * MiB, 6, nvls=False, mapped=False)[0] == "ring"
+    assert ca(8 * MiB, 8, mapped=False)[0] == "nvls"
     assert ca(256 << 10, 8, mapped=False)[0] == "oneshot"
+    assert ca(4 * MiB, 2, mapped=False)[0] == "oneshot"          # two ranks: one push each is all the traffic there is
     for ws in range(2, 9):
         for nb in (4, 4096, MiB, 64 * MiB, 1 << 30):
             for nvls in (False, True):
