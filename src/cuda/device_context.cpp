@@ -696,7 +696,9 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   if (multimem && (mc_ == nullptr || !NvlsSupportsDType(wire))) return false;
   // Six windows (three in, three out) in the pool and the work region behind
   // it (the two are adjacent and one collective runs at a time).
-  const uint64_t quarter = (layout_.pool_bytes + layout_.work_bytes) / 6 / 4096 * 4096;
+  int buffers = Tunable("IBCOMM_STAGED_BUFFERS", 3);
+  buffers = std::max(3, std::min(buffers, kStagedMaxBuffers));
+  const uint64_t quarter = (layout_.pool_bytes + layout_.work_bytes) / static_cast<uint64_t>(2 * buffers) / 4096 * 4096;
   if (quarter < 4096) return false;
   StagedParams p;
   memset(&p, 0, sizeof(p));
@@ -721,9 +723,10 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   const int max_window = Tunable("IBCOMM_STAGED_WINDOW_KIB", 0);  // experiment knob: smaller windows
   if (max_window > 0) cap_bytes = std::min<uint64_t>(cap_bytes, static_cast<uint64_t>(max_window) << 10);
   p.window_elems = TwoShotWindowElems(n, cap_bytes / wsize, wsize, ws_, ctas);
-  for (int j = 0; j < 3; ++j) {
+  p.buffers = buffers;
+  for (int j = 0; j < buffers; ++j) {
     p.in_off[j] = layout_.pool_offset + static_cast<uint64_t>(j) * quarter;
-    p.out_off[j] = layout_.pool_offset + static_cast<uint64_t>(3 + j) * quarter;
+    p.out_off[j] = layout_.pool_offset + static_cast<uint64_t>(buffers + j) * quarter;
   }
   p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
   p.status = rr_.d_status;

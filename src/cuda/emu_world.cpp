@@ -125,7 +125,9 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
   const size_t wsize = DTypeSize(wire);
   if (algo == Algo::kDirect && (wire != dtype || m.direct_staging == 2)) {
     // The pipelined staged kernel (what ordinary buffers and 16-bit wires get on several GPUs).
-    const uint64_t quarter = (m.layout.pool_bytes + m.layout.work_bytes) / 6 / 4096 * 4096;
+    int buffers = Tunable("IBCOMM_STAGED_BUFFERS", 3);
+    buffers = std::max(3, std::min(buffers, kStagedMaxBuffers));
+    const uint64_t quarter = (m.layout.pool_bytes + m.layout.work_bytes) / static_cast<uint64_t>(2 * buffers) / 4096 * 4096;
     if (!all_aligned || (n * wsize) % 16 != 0 || quarter < 4096)
       IBCOMM_FAIL(NOT_SUPPORTED, "The pipelined staged two-shot needs 16-byte aligned buffers of whole 16-byte wire vectors.\n");
     int ch = channels > 0 ? channels : ChooseChannels(Algo::kDirect, n * wsize, m.ws, kMaxChannels);
@@ -147,9 +149,10 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
       p.len_elements = n;
       p.scale = scale;
       p.window_elems = TwoShotWindowElems(n, quarter / wsize, wsize, m.ws, ch);
-      for (int j = 0; j < 3; ++j) {
+      p.buffers = buffers;
+      for (int j = 0; j < buffers; ++j) {
         p.in_off[j] = m.layout.pool_offset + static_cast<uint64_t>(j) * quarter;
-        p.out_off[j] = m.layout.pool_offset + static_cast<uint64_t>(3 + j) * quarter;
+        p.out_off[j] = m.layout.pool_offset + static_cast<uint64_t>(buffers + j) * quarter;
       }
       p.timeout_ns = timeout_ns;
       p.status = rr.d_status;

@@ -91,6 +91,7 @@ cudaError_t LaunchHybridKernel(const HybridParams& h, int blocks, cudaStream_t s
 // CTA four warp groups work on up to four windows at the same time (copy in /
 // two reducers over NVLink / copy out), three buffers of each kind.  At most
 // 128 CTAs.
+constexpr int kStagedMaxBuffers = 6;
 struct StagedParams {
   int32_t rank;
   int32_t world_size;
@@ -104,8 +105,10 @@ struct StagedParams {
   uint64_t len_elements; // a whole number of 16-byte wire vectors
   double scale;
   uint64_t window_elems; // elements per window (a whole number of vectors per rank and CTA)
-  uint64_t in_off[3];    // byte offsets of the three input windows inside every arena
-  uint64_t out_off[3];   // ... and of the three output windows
+  uint64_t in_off[kStagedMaxBuffers];    // byte offsets of the input windows inside every arena
+  uint64_t out_off[kStagedMaxBuffers];   // ... and of the output windows
+  int32_t buffers;       // windows of each kind in use (3 .. kStagedMaxBuffers)
+  int32_t pad0_;
   uint64_t timeout_ns;
   DeviceStatus* status;
   uint32_t* doorbell;

@@ -66,7 +66,6 @@ constexpr int kStagedThreads = 512;
 constexpr int kLoadWarpsBulk = 1, kStoreWarpsBulk = 1;
 constexpr int kLoadWarpsRegs = 3, kStoreWarpsRegs = 3;
 constexpr int kBarLoad = 1, kBarStore = 2, kBarReduce = 3;  // named barriers of the groups (0 is __syncthreads); reducer B uses kBarReduce + 1
-constexpr int kStagedBuffers = 3;     // input windows, and output windows, in the pool
 constexpr int kStagedMaxCtas = 128;   // the odd windows' "reduced" flags live in bar[cta + 128]
 constexpr uint32_t kBulkChunk = 16384;  // bytes per bulk copy
 constexpr int kBulkDepth = 6;           // stages per copy group
@@ -291,6 +290,9 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
   const uint64_t windows = full_nv == 0 ? 0 : (total_nv + full_nv - 1) / full_nv;
   const bool tma = p.use_tma != 0 && sizeof(T) == sizeof(W);
   const uint64_t base = seq << 32;
+  // Input windows, and output windows, in the pool: at least three (two being
+  // reduced, one being filled or emptied); more give the copies more time.
+  const uint64_t kStagedBuffers = static_cast<uint64_t>(p.buffers < 3 ? 3 : (p.buffers > kStagedMaxBuffers ? kStagedMaxBuffers : p.buffers));
 
   RoleCtx c;
   c.w.peers = &p.peers;
