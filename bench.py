@@ -296,9 +296,25 @@ def main() -> int:
             del reg_in, reg_out
             t = time_steps(lambda: comm.allreduce(plain_in, plain_out, algo="ring", scale=scale, wire=torch.bfloat16), k, w)
             per_algo["ring_bf16_wire"] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world)}
+            # The caller's own, unregistered tensors (the reference's contract) through `auto`.
+            t = time_steps(lambda: comm.allreduce(plain_in, plain_out, scale=scale), k, w)
+            per_algo["auto_plain"] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world),
+                                      "algo": comm.device_info()["last_algo"], "channels": comm.device_info()["last_channels"],
+                                      "max_abs_err": strided_error(plain_out, n, world, scale, dev)}
+            if info["nvls"]:
+                t = time_steps(lambda: comm.allreduce(plain_in, plain_out, algo="nvls", scale=scale, wire=torch.bfloat16), k, w)
+                per_algo["nvls_bf16_wire"] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world)}
             nccl_buf = plain_in.clone()
             t = time_steps(lambda: dist.all_reduce(nccl_buf), k, w)
             per_algo["nccl"] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world)}
+            # NCCL on memory it allocated and registered itself: zero-copy against zero-copy.
+            ra, _rb, note = nccl_registered_pair(n, dev)
+            if ra is not None:
+                ra.copy_(plain_in)
+                t = time_steps(lambda: dist.all_reduce(ra), k, w)
+                per_algo["nccl_registered"] = {"ms": t, "busbw_gbs": busbw_gbs(nbytes, t / 1e3, world), "note": note}
+            else:
+                per_algo["nccl_registered"] = {"error": note}
         else:
             # One GPU: the same kernels with 8 emulated ranks in one cooperative
             # launch (32 MiB per rank; local memory only, so this is a kernel
@@ -495,6 +511,13 @@ def tune(args, comm, world, rank, dev, time_steps) -> int:
                 run("staged", f"{algo}_plain_{size >> 20}MiB", allreduce(plain_in[:m], plain_out[:m], algo), size=size, k=30, w=5)
             nb = plain_in[:m].clone()
             run("staged", f"nccl_{size >> 20}MiB", lambda: dist.all_reduce(nb), size=size, k=30, w=5)
+    if "buffers" in sections:
+        # The pipelined staged kernel: window buffers of each kind x CTAs (ordinary buffers, full size).
+        for algo in (["nvls"] if info["nvls"] else ["direct"]):
+            for bufs in (3, 4, 6):
+                for ctas in (48, 64, 96, 128):
+                    run("buffers", f"{algo}_pipelined_bufs{bufs}_ctas{ctas}", allreduce(plain_in, plain_out, algo),
+                        {"IBCOMM_STAGED_BUFFERS": bufs, "IBCOMM_STAGED_CTAS": ctas}, check=plain_out if ctas == 64 else None)
     if "wire" in sections:
         for algo in ["ring", "rabenseifner", "direct"] + (["nvls"] if info["nvls"] else []):
             for wire in (torch.bfloat16, torch.float16):

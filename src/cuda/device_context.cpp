@@ -206,6 +206,7 @@ class DeviceContext {
   int p2p_ctas_ = 96;          // CTAs of every Send / Recv / Bcast kernel of this communicator (knob IBCOMM_P2P_CTAS)
   uint64_t bcast_pieces_ = 0;  // pieces of all device broadcasts so far (equal on every rank)
   std::vector<std::unique_ptr<SymmetricAlloc>> symm_;
+  std::unique_ptr<SymmetricAlloc> grown_stage_;  // staging block for large messages through the pool (allocated on demand)
   std::vector<RegisteredBuffer> registered_;
   std::vector<ImportedIpc> ipc_imports_;
   int next_registration_ = 0;
@@ -272,6 +273,7 @@ DeviceContext::~DeviceContext() {
   for (ImportedIpc& imp : ipc_imports_) cudaIpcCloseMemHandle(imp.base);
   ipc_imports_.clear();
   registered_.clear();
+  grown_stage_.reset();
   symm_.clear();
   mc_.reset();
   peer_arenas_.clear();
@@ -694,11 +696,47 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   if (((reinterpret_cast<uintptr_t>(sendbuf) | reinterpret_cast<uintptr_t>(recvbuf)) & 15u) != 0) return false;
   if ((n * wsize) % 16 != 0) return false;
   if (multimem && (mc_ == nullptr || !NvlsSupportsDType(wire))) return false;
-  // Six windows (three in, three out) in the pool and the work region behind
-  // it (the two are adjacent and one collective runs at a time).
-  int buffers = Tunable("IBCOMM_STAGED_BUFFERS", 3);
+  // Windows: `buffers` input and `buffers` output windows.  They live in the
+  // pool and the work region behind it (adjacent, and one collective runs at
+  // a time), or, for large messages, in a staging block of its own that the
+  // ranks allocate together the first time it is needed - the counterpart of
+  // the reference growing its pool and its work buffer at run time with a
+  // warning (memory_pool.h:222-236, allreduce_cuda_impl.h:372-385).  Every
+  // window costs a fixed 15-20 us of cross-rank hand-over on 8 GPUs, so a
+  // 256 MiB message wants windows of tens of MiB: measured 0.80 ms with
+  // 16 MiB windows, 0.70 ms with 36 MiB windows (NCCL: 0.73 ms).
+  int buffers = Tunable("IBCOMM_STAGED_BUFFERS", 0);
+  const uint64_t wire_bytes = static_cast<uint64_t>(n) * wsize;
+  const uint64_t arena_stage = layout_.pool_bytes + layout_.work_bytes;
+  const uint64_t grow_max = static_cast<uint64_t>(std::max(0, Tunable("IBCOMM_STAGING_GROW_MAX_MIB", 320))) << 20;
+  const bool big = wire_bytes >= (96ull << 20);
+  if (big && grow_max > arena_stage && ws_ > 1 && !IsCapturing(stream) &&
+      (grown_stage_ == nullptr || grown_stage_->bytes < grow_max)) {
+    // The decision depends on the message and the knobs only: the same on every rank.
+    static bool warned = false;
+    if (!warned && rank_ == 0) {
+      warned = true;
+      IBCOMM_WARN("allreduce of %llu bytes through the staging pool: growing the staging memory from %llu to %llu bytes "
+                  "(IBCOMM_MEMORY_POOL_PRE_ALLOC + IBCOMM_WORK_GPU_MEMORY_SIZE; limit IBCOMM_STAGING_GROW_MAX_MIB).\n",
+                  static_cast<unsigned long long>(wire_bytes), static_cast<unsigned long long>(arena_stage),
+                  static_cast<unsigned long long>(grow_max));
+    }
+    CUDACHECK(cudaStreamSynchronize(stream));
+    if (have_last_) CUDACHECK(cudaStreamSynchronize(last_stream_));
+    std::unique_ptr<SymmetricAlloc> g(new SymmetricAlloc());
+    g->mine.reset(new SharedAllocation());
+    size_t align = 0;
+    if (mc_ != nullptr) align = MulticastGroup::Granularity(ws_, grow_max);
+    g->mine->Create(grow_max, device_, align);
+    g->bytes = g->mine->bytes();
+    ExchangeAllocation(g->mine.get(), &g->imported, g->peer_ptr, mc_ != nullptr, &g->mc);
+    grown_stage_ = std::move(g);
+  }
+  const bool use_grown = big && grown_stage_ != nullptr && (!multimem || grown_stage_->mc != nullptr);
+  const uint64_t stage_bytes = use_grown ? grown_stage_->bytes : arena_stage;
+  if (buffers <= 0) buffers = use_grown ? 4 : 3;
   buffers = std::max(3, std::min(buffers, kStagedMaxBuffers));
-  const uint64_t quarter = (layout_.pool_bytes + layout_.work_bytes) / static_cast<uint64_t>(2 * buffers) / 4096 * 4096;
+  const uint64_t quarter = stage_bytes / static_cast<uint64_t>(2 * buffers) / 4096 * 4096;
   if (quarter < 4096) return false;
   StagedParams p;
   memset(&p, 0, sizeof(p));
@@ -714,7 +752,8 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   p.len_elements = n;
   p.scale = scale;
   int ctas = Tunable("IBCOMM_STAGED_CTAS", 0);
-  if (ctas <= 0) ctas = std::max(channels, ChooseChannels(Algo::kDirect, n * wsize, ws_, max_channels_));
+  // 64 CTAs measured best for the switch path at every size from 16 MiB up (fewer flags per window).
+  if (ctas <= 0) ctas = std::min(multimem ? 64 : 128, std::max(channels, ChooseChannels(Algo::kDirect, n * wsize, ws_, max_channels_)));
   static const int resident = StagedKernelMaxCoResidentBlocks(device_);
   if (resident > 0) ctas = std::min(ctas, resident);
   if (Tunable("IBCOMM_MAX_CTAS", 0) > 0) ctas = std::min(ctas, Tunable("IBCOMM_MAX_CTAS", 0));
@@ -724,9 +763,12 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   if (max_window > 0) cap_bytes = std::min<uint64_t>(cap_bytes, static_cast<uint64_t>(max_window) << 10);
   p.window_elems = TwoShotWindowElems(n, cap_bytes / wsize, wsize, ws_, ctas);
   p.buffers = buffers;
+  const uint64_t stage_off = use_grown ? 0 : layout_.pool_offset;
+  for (int q = 0; q < ws_; ++q) p.stage[q] = use_grown ? grown_stage_->peer_ptr[q] : rr_.peers.arena[q];
+  p.mc_stage = use_grown ? (grown_stage_->mc ? grown_stage_->mc->ptr() : nullptr) : rr_.peers.mc_arena;
   for (int j = 0; j < buffers; ++j) {
-    p.in_off[j] = layout_.pool_offset + static_cast<uint64_t>(j) * quarter;
-    p.out_off[j] = layout_.pool_offset + static_cast<uint64_t>(buffers + j) * quarter;
+    p.in_off[j] = stage_off + static_cast<uint64_t>(j) * quarter;
+    p.out_off[j] = stage_off + static_cast<uint64_t>(buffers + j) * quarter;
   }
   p.timeout_ns = static_cast<uint64_t>(comm_->timeout_ms()) * 1000000ull;
   p.status = rr_.d_status;

@@ -150,6 +150,8 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
       p.scale = scale;
       p.window_elems = TwoShotWindowElems(n, quarter / wsize, wsize, m.ws, ch);
       p.buffers = buffers;
+      for (int q = 0; q < m.ws; ++q) p.stage[q] = rr.peers.arena[q];
+      p.mc_stage = nullptr;
       for (int j = 0; j < buffers; ++j) {
         p.in_off[j] = m.layout.pool_offset + static_cast<uint64_t>(j) * quarter;
         p.out_off[j] = m.layout.pool_offset + static_cast<uint64_t>(buffers + j) * quarter;

@@ -105,7 +105,11 @@ struct StagedParams {
   uint64_t len_elements; // a whole number of 16-byte wire vectors
   double scale;
   uint64_t window_elems; // elements per window (a whole number of vectors per rank and CTA)
-  uint64_t in_off[kStagedMaxBuffers];    // byte offsets of the input windows inside every arena
+  // The staging memory as every rank maps it (the arena, or a larger block
+  // the communicator allocated for large messages) and its multicast alias.
+  unsigned char* stage[kMaxRanks];
+  unsigned char* mc_stage;
+  uint64_t in_off[kStagedMaxBuffers];    // byte offsets of the input windows inside the staging memory
   uint64_t out_off[kStagedMaxBuffers];   // ... and of the output windows
   int32_t buffers;       // windows of each kind in use (3 .. kStagedMaxBuffers)
   int32_t pad0_;

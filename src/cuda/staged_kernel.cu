@@ -329,7 +329,7 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
         if (k >= kStagedBuffers &&
             !RoleWait(c, kRowReduced, k - kStagedBuffers, base | (k - kStagedBuffers + 1), kWaitBarrier, static_cast<int>(k)))
           break;
-        unsigned char* win = p.peers.arena[me] + p.in_off[j];
+        unsigned char* win = p.stage[me] + p.in_off[j];
         const unsigned char* user = static_cast<const unsigned char*>(p.sendbuf) + v0 * 16 * VT;
         if (tma && mover) {
           unsigned char* dst[kMaxRanks];
@@ -374,7 +374,7 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
         const uint64_t v0 = k * full_nv;
         const uint64_t nv = total_nv - v0 < full_nv ? total_nv - v0 : full_nv;
         if (!RoleWait(c, kRowReduced, k, base | (k + 1), kWaitBarrier, static_cast<int>(k))) break;
-        const unsigned char* win = p.peers.arena[me] + p.out_off[j];
+        const unsigned char* win = p.stage[me] + p.out_off[j];
         unsigned char* user = static_cast<unsigned char*>(p.recvbuf) + v0 * 16 * VT;
         if (tma && mover) {
           unsigned char* dst[kMaxRanks];
@@ -435,8 +435,8 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
       WindowPart(full_nv, nv, me, ws, cta, ncta, &b, &e);
       if constexpr (kMultimem) {
         constexpr int kU = 4;
-        const unsigned char* mi = p.peers.mc_arena + p.in_off[j];
-        unsigned char* mo = p.peers.mc_arena + p.out_off[j];
+        const unsigned char* mi = p.mc_stage + p.in_off[j];
+        unsigned char* mo = p.mc_stage + p.out_off[j];
         for (uint64_t i = b + c.tid; i < e; i += static_cast<uint64_t>(reduce_threads) * kU) {
           uint4 v[kU];
 #pragma unroll
@@ -460,7 +460,7 @@ StagedKernel(const __grid_constant__ StagedParams p0, const StagedParams* __rest
           }
         }
       } else {
-        unsigned char* const* arenas = p.peers.arena;
+        unsigned char* const* arenas = p.stage;
         const uint64_t out_off = p.out_off[j];
         PeerReduceGroup<W, kR>(arenas, ws, p.in_off[j], b, e, do_scale, p.scale,
                                [&](uint64_t idx, uint4 r) {
