@@ -881,6 +881,10 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
     plain_in.copy_(torch.rand(nmax, dtype=torch.float32, device=dev, generator=g) * 2 - 1)
     sym_in.copy_(plain_in)
     nccl_buf = torch.empty(nmax, dtype=torch.float32, device=dev)
+    nccl_reg = None
+    if world > 1:
+        nccl_reg, _unused, nccl_reg_note = nccl_registered_pair(nmax, dev)
+        del _unused
     registered = False
     if world > 1:
         reg_in, reg_out = plain_in.clone(), torch.empty_like(plain_in)
@@ -930,6 +934,10 @@ def sweep(args, comm, world, rank, dev, time_steps, barrier) -> int:
             t = time_steps(lambda: dist.all_reduce(nccl_buf[:n]), steps, warm)
             rows.append({"bytes": size, "algo": "nccl", "us": t * 1e3, "busbw_gbs": busbw_gbs(size, t / 1e3, world),
                          "algbw_gbs": size / (t / 1e3) / 1e9, "n_gpus": world})
+            if nccl_reg is not None:
+                t = time_steps(lambda: dist.all_reduce(nccl_reg[:n]), steps, warm)
+                rows.append({"bytes": size, "algo": "nccl_registered", "us": t * 1e3, "busbw_gbs": busbw_gbs(size, t / 1e3, world),
+                             "algbw_gbs": size / (t / 1e3) / 1e9, "n_gpus": world})
         size *= 2
     if rank == 0:
         os.makedirs(os.path.dirname(out_path) or ".", exist_ok=True)
