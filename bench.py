@@ -67,14 +67,14 @@ def parse_args():
     ap.add_argument("--no-extras", action="store_true", help="skip per-algorithm and NCCL measurements")
     ap.add_argument("--tune", default=None, metavar="SECTIONS",
                     help="sweep the kernels' knobs inside ONE process launch and write JSON lines to --out; comma-separated "
-                         "sections of: hybrid, staged, wire, exec, small, nccl (default with an empty string: all)")
+                         "sections of: hybrid, staged, mid, buffers, wire, exec, small, nccl (default with an empty string: all)")
     ap.add_argument("--p2p", action="store_true",
                     help="time device Send/Recv between ranks 0 and 1 (1 MiB .. 1 GiB) against NCCL send/recv")
     ap.add_argument("--world-sizes", action="store_true",
                     help="time ring, Rabenseifner, auto and NCCL at 64 MiB on every world size 2..N (sub-communicators of this launch)")
     ap.add_argument("--kernel-case", default=None,
                     choices=["copy", "exec_ring_emu8", "exec_rabenseifner_emu8", "oneshot_emu8", "direct_emu8",
-                             "reduce_scatter_emu8", "all_gather_emu8"],
+                             "staged_emu8", "reduce_scatter_emu8", "all_gather_emu8"],
                     help="run one small single-GPU case of one kernel (for ncu captures) and print its time")
     return ap.parse_args()
 
@@ -511,6 +511,25 @@ def tune(args, comm, world, rank, dev, time_steps) -> int:
                 run("staged", f"{algo}_plain_{size >> 20}MiB", allreduce(plain_in[:m], plain_out[:m], algo), size=size, k=30, w=5)
             nb = plain_in[:m].clone()
             run("staged", f"nccl_{size >> 20}MiB", lambda: dist.all_reduce(nb), size=size, k=30, w=5)
+    if "mid" in sections:
+        # Medium messages in ordinary buffers: window size of the pipelined staged kernel against the
+        # zero-copy kernels (the floor), the op programs and NCCL.
+        algos = ["direct"] + (["nvls"] if info["nvls"] else [])
+        for size in (32 << 20, 64 << 20, 128 << 20):
+            m = size // 4
+            if m > n:
+                continue
+            for algo in algos:
+                run("mid", f"{algo}_zero_copy_{size >> 20}MiB", allreduce(sym_in[:m], sym_out[:m], algo), size=size, k=30, w=5)
+                for kib in (0, 2048, 4096, 8192):
+                    for ctas in (64, 128):
+                        run("mid", f"{algo}_window{kib}KiB_ctas{ctas}_{size >> 20}MiB", allreduce(plain_in[:m], plain_out[:m], algo),
+                            {"IBCOMM_STAGED_WINDOW_KIB": kib, "IBCOMM_STAGED_CTAS": ctas}, size=size, k=30, w=5,
+                            check=plain_out[:m] if kib == 4096 and ctas == 64 else None)
+            for algo in ("auto", "ring", "rabenseifner"):
+                run("mid", f"{algo}_plain_{size >> 20}MiB", allreduce(plain_in[:m], plain_out[:m], algo), size=size, k=30, w=5)
+            nb = plain_in[:m].clone()
+            run("mid", f"nccl_{size >> 20}MiB", lambda: dist.all_reduce(nb), size=size, k=30, w=5)
     if "buffers" in sections:
         # The pipelined staged kernel: window buffers of each kind x CTAs (ordinary buffers, full size).
         for algo in (["nvls"] if info["nvls"] else ["direct"]):
@@ -723,7 +742,9 @@ def kernel_case(args, comm, dev, time_steps) -> int:
     else:
         emu = ar.EmuWorld(8)
         algo = {"exec_ring_emu8": "ring", "exec_rabenseifner_emu8": "rabenseifner", "oneshot_emu8": "oneshot",
-                "direct_emu8": "direct"}[case]
+                "direct_emu8": "direct", "staged_emu8": "direct"}[case]
+        if case == "staged_emu8":
+            emu.set_direct_staging(2)  # the pipelined staged kernel: copy in, peer reduce and copy out overlap
         m = (16 << 10) if algo == "oneshot" else (8 << 20)  # elements per rank: 64 KiB or 32 MiB
         ins = [torch.rand(m, device=dev) for _ in range(8)]
         outs = [torch.empty(m, device=dev) for _ in range(8)]

@@ -935,7 +935,14 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
     // multicast object: zero-copy for the direct algorithm only.  With a
     // 16-bit wire every buffer goes through the pool (that is where the
     // 16-bit copy lives), mapped or not.
-    const bool mapped = !compressed && (symmetric || (FindPeerMapped(sendbuf, bytes, unused) && FindPeerMapped(recvbuf, bytes, unused)));
+    bool mapped = !compressed && (symmetric || (FindPeerMapped(sendbuf, bytes, unused) && FindPeerMapped(recvbuf, bytes, unused)));
+    // From 256 MiB on, the switch path through the pool (1 + 1/ws of the
+    // message per direction, pipelined copies) beats peer loads on registered
+    // buffers in place (2 (ws-1)/ws of it): 1303 against 1444 us at 512 MiB on
+    // 8 GPUs.  Such buffers are then treated as ordinary ones.
+    if (mapped && !symmetric && nvls_ok && staged_shape && ws_ > 2 &&
+        bytes >= (static_cast<size_t>(Tunable("IBCOMM_REGISTERED_SWITCH_MIB", 256)) << 20))
+      mapped = false;
     TunerChoice c = ChooseAlgorithm(bytes, ws_, nvls_ok && (symmetric || !mapped), mapped, max_channels_);
     algo = c.algo;
     channels = c.channels;
