@@ -22,6 +22,8 @@
 #include "ibcomm/communicator.h"
 #ifdef USE_CUDA
 #include <cuda_runtime.h>
+
+#include "ibcomm/memory_pool.h"
 #endif
 
 namespace {
@@ -64,8 +66,44 @@ size_t CountBad(const std::vector<float>& out, int ws, double scale) {
 
 }  // namespace
 
+#ifdef USE_CUDA
+// The staging pool with pinned blocks and CUDA streams: six slots in flight,
+// each copied to the device on the stream it was handed out with; six at once
+// need a second block (four slots each) and two streams beyond the first four.
+int PoolOnDevice() {
+  constexpr size_t kSlot = 256u << 10;
+  ibcomm::MemoryPool<ibcomm::PinnedBlockAllocator, ibcomm::CudaStreams> pool(1 << 20, 4);
+  auto ctl = pool.GetController(kSlot);
+  unsigned char* dev = nullptr;
+  if (cudaMalloc(&dev, 6 * kSlot) != cudaSuccess) return 3;
+  std::vector<ibcomm::Memory*> out;
+  for (int i = 0; i < 6; ++i) {
+    ibcomm::Memory* m = ctl.getMemory();
+    memset(m->ptr(), 0x10 + i, kSlot);
+    cudaMemcpyAsync(dev + i * kSlot, m->ptr(), kSlot, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(m->stream()));
+    out.push_back(m);
+  }
+  int bad = 0;
+  for (int i = 0; i < 6; ++i) {
+    if (cudaStreamSynchronize(static_cast<cudaStream_t>(out[i]->stream())) != cudaSuccess) ++bad;
+    ctl.returnMemory(out[i]);
+  }
+  std::vector<unsigned char> back(6 * kSlot);
+  if (cudaMemcpy(back.data(), dev, back.size(), cudaMemcpyDeviceToHost) != cudaSuccess) ++bad;
+  for (int i = 0; i < 6; ++i)
+    if (back[i * kSlot] != 0x10 + i || back[(i + 1) * kSlot - 1] != 0x10 + i) ++bad;
+  cudaFree(dev);
+  if (pool.num_blocks() != 2 || pool.num_streams() != 6 || ctl.vacant_slots() != 8) ++bad;
+  printf(bad == 0 ? "pool OK\n" : "pool FAILED\n");
+  return bad == 0 ? 0 : 1;
+}
+#endif
+
 int main(int argc, char** argv) {
   const std::string device = argc > 1 ? argv[1] : "cpu";
+#ifdef USE_CUDA
+  if (device == "pool") return PoolOnDevice();
+#endif
   const int ws = argc > 2 ? atoi(argv[2]) : 2;
   if (ws < 1 || ws > 8 || (device != "cpu" && device != "cuda")) {
     fprintf(stderr, "usage: threads_test cpu|cuda <ranks 1..8>\n");

@@ -1,11 +1,13 @@
 // Unit tests of the host utilities: the size parser tables and the
 // power-of-two gate (cases of the reference's tests/unittest.cpp:12-71, with
 // the current function name), the partitioner, the expression compiler and the
-// error policy.
+// error policy, and the staging pool's lease, order and growth (the contract of
+// the reference's memory_pool.h:111-121,222-243).
 #include <cstring>
 
 #include "ibcomm/communicator.h"
 #include "ibcomm/expr.h"
+#include "ibcomm/memory_pool.h"
 #include "mini_test.h"
 
 using util::parse_number;
@@ -156,6 +158,72 @@ MINI_TEST(TraceNull) {
   std::vector<struct timespec> v;
   util::trace(&v);
   CHECK_EQ(v.size(), size_t(1));
+  ibcomm::SetErrorPolicy(ibcomm::ErrorPolicy::kExit);
+}
+
+MINI_TEST(MemoryPoolLeaseAndOrder) {
+  ibcomm::SetErrorPolicy(ibcomm::ErrorPolicy::kThrow);
+  ibcomm::MemoryPool<> pool(4096, 2);
+  CHECK_EQ(pool.num_blocks(), size_t(1));
+  {
+    auto c = pool.GetController(1024);
+    CHECK_EQ(c.total_slots(), size_t(4));
+    int code = 0;
+    try {
+      auto second = pool.GetController(1024);
+    } catch (const ibcomm::Error& e) {
+      code = e.code();
+    }
+    CHECK_EQ(code, 4);  // one controller at a time
+    ibcomm::Memory* a = c.getMemory();
+    ibcomm::Memory* b = c.getMemory();
+    CHECK_EQ(a->offset(), size_t(0));
+    CHECK_EQ(b->offset(), size_t(1024));
+    CHECK_TRUE(a->stream() != nullptr && b->stream() != nullptr && a->stream() != b->stream());
+    // A third slot needs a third stream: the pool creates one.
+    ibcomm::Memory* d = c.getMemory();
+    CHECK_EQ(pool.num_streams(), size_t(3));
+    CHECK_TRUE(d->stream() != a->stream() && d->stream() != b->stream());
+    // First in, first out: the slot and the stream that came back first go out after the untouched ones.
+    ibcomm::StreamHandle sa = a->stream();
+    c.returnMemory(a);
+    CHECK_TRUE(a->stream() == nullptr);
+    ibcomm::Memory* e = c.getMemory();
+    CHECK_EQ(e->offset(), size_t(3072));
+    CHECK_TRUE(e->stream() == sa);
+    ibcomm::Memory* f = nullptr;
+    c.returnMemory(b);
+    f = c.getMemory();
+    CHECK_TRUE(f == a);
+    CHECK_THROWS(c.returnMemory(nullptr), ibcomm::Error);
+    std::memset(f->ptr(), 0x5a, 1024);  // the slot is real memory
+  }
+  CHECK_TRUE(!pool.controller_in_use());
+  auto again = pool.GetController(4096);  // released by the destructor
+  CHECK_EQ(again.total_slots(), size_t(1));
+  ibcomm::SetErrorPolicy(ibcomm::ErrorPolicy::kExit);
+}
+
+MINI_TEST(MemoryPoolGrowsAndValidates) {
+  ibcomm::SetErrorPolicy(ibcomm::ErrorPolicy::kThrow);
+  ibcomm::MemoryPool<> pool(8192, 8);
+  auto c = pool.GetController(4096);
+  ibcomm::Memory* m[5];
+  for (int i = 0; i < 5; ++i) m[i] = c.getMemory();
+  CHECK_EQ(pool.num_blocks(), size_t(3));  // 2 slots per block, 5 slots handed out
+  CHECK_EQ(c.total_slots(), size_t(6));
+  CHECK_TRUE(m[2]->block() != m[0]->block() && m[4]->block() != m[2]->block());
+  for (int i = 0; i < 5; ++i) c.returnMemory(m[i]);
+  CHECK_EQ(c.vacant_slots(), size_t(6));
+  auto moved = std::move(c);  // the lease moves with the controller
+  CHECK_TRUE(pool.controller_in_use());
+  CHECK_EQ(moved.vacant_slots(), size_t(6));
+  CHECK_THROWS(ibcomm::MemoryPool<>(2, 1), ibcomm::Error);
+  CHECK_THROWS(ibcomm::MemoryPool<>(4096, 0), ibcomm::Error);
+  CHECK_THROWS(ibcomm::MemoryPool<>(4096, 1025), ibcomm::Error);
+  ibcomm::MemoryPool<> small(4096, 1);
+  CHECK_THROWS(small.GetController(8192), ibcomm::Error);
+  CHECK_TRUE(!small.controller_in_use());
   ibcomm::SetErrorPolicy(ibcomm::ErrorPolicy::kExit);
 }
 

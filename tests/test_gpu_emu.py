@@ -442,3 +442,13 @@ def test_aging_on_the_device_path(bins):
     for algo in ("ring", "rabenseifner"):
         code, err = _tester(bins, ["--emulate", "4", "--iters", "100", algo, "32M", "i*np+p", "i*np*np+np*(np-1)/2"])
         assert code == 0, (algo, err)
+
+
+def test_staging_pool_with_pinned_blocks_and_cuda_streams(bins):
+    # include/ibcomm/memory_pool.h under USE_CUDA: the exclusive controller hands out pinned slots paired with
+    # real streams, grows by a block and by streams when six slots are out at once (tests/cpp/threads_test.cpp).
+    import subprocess
+    p = subprocess.run(["timeout", "120s", bins["threads_test_cuda"], "pool"], stdout=subprocess.PIPE,
+                       stderr=subprocess.PIPE, text=True)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert "pool OK" in p.stdout
