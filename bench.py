@@ -67,7 +67,7 @@ def parse_args():
     ap.add_argument("--no-extras", action="store_true", help="skip per-algorithm and NCCL measurements")
     ap.add_argument("--tune", default=None, metavar="SECTIONS",
                     help="sweep the kernels' knobs inside ONE process launch and write JSON lines to --out; comma-separated "
-                         "sections of: hybrid, staged, mid, buffers, wire, exec, small, nccl (default with an empty string: all)")
+                         "sections of: hybrid, staged, mid, execmid, buffers, wire, exec, small, nccl (default with an empty string: all)")
     ap.add_argument("--p2p", action="store_true",
                     help="time device Send/Recv between ranks 0 and 1 (1 MiB .. 1 GiB) against NCCL send/recv")
     ap.add_argument("--world-sizes", action="store_true",
@@ -530,6 +530,27 @@ def tune(args, comm, world, rank, dev, time_steps) -> int:
                 run("mid", f"{algo}_plain_{size >> 20}MiB", allreduce(plain_in[:m], plain_out[:m], algo), size=size, k=30, w=5)
             nb = plain_in[:m].clone()
             run("mid", f"nccl_{size >> 20}MiB", lambda: dist.all_reduce(nb), size=size, k=30, w=5)
+    if "pipe" in sections:
+        # What bounds a window of the pipelined staged kernel: buffers in the cycle, bulk copies against
+        # register copies, window size (64 MiB message, ordinary buffers).
+        size = 64 << 20
+        m = size // 4
+        for algo in (["nvls"] if info["nvls"] and world > 2 else ["direct"]):
+            for kib in (1024, 2048, 4096, 8192, 0):
+                for bufs in (3, 6):
+                    for tma in (1, 0):
+                        run("pipe", f"{algo}_window{kib}KiB_bufs{bufs}_tma{tma}", allreduce(plain_in[:m], plain_out[:m], algo),
+                            {"IBCOMM_STAGED_WINDOW_KIB": kib, "IBCOMM_STAGED_BUFFERS": bufs, "IBCOMM_STAGED_TMA": tma},
+                            size=size, k=20, w=4)
+    if "execmid" in sections:
+        # The op programs at medium sizes: CTAs x threads per CTA (per-op overhead against parallelism).
+        for size in (16 << 20, 64 << 20):
+            m = size // 4
+            for algo in ("ring", "rabenseifner"):
+                for threads in (512, 256):
+                    for ch in (32, 64, 96, 128, 148, 256):
+                        run("execmid", f"{algo}_t{threads}_ch{ch}_{size >> 20}MiB", allreduce(plain_in[:m], plain_out[:m], algo),
+                            {"IBCOMM_EXEC_THREADS": threads, "IBCOMM_EXEC_CHANNELS": ch}, size=size, k=30, w=5)
     if "buffers" in sections:
         # The pipelined staged kernel: window buffers of each kind x CTAs (ordinary buffers, full size).
         for algo in (["nvls"] if info["nvls"] else ["direct"]):

@@ -114,24 +114,30 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
   Algo a;
   if (zero_copy) {
     // Buffers every peer maps (symmetric memory): nothing is staged.
-    if (bytes <= (16u << 10)) {
+    if (world_size <= 2) {
+      // Two ranks: one push each is all the traffic an allreduce needs, and it
+      // takes one synchronisation instead of three (12-23 us up to 4 MiB
+      // against 13-25 us for the two-shot kernels); above, peer loads in
+      // place.  The switch path moves 1.5 S per direction against 1.0 S and
+      // loses at every size.
+      a = bytes <= (4u << 20) ? Algo::kOneShot : Algo::kDirect;
+    } else if (bytes <= (16u << 10)) {
       a = Algo::kOneShot;
-    } else if (nvls_available && (world_size > 2 || bytes <= (4u << 20))) {
-      // In-switch reduction: 1 + 1/ws of the message per direction.  With two
-      // ranks that is 1.5 S against the direct algorithm's 1.0 S, so large
-      // messages go direct there.
-      a = Algo::kNvls;
+    } else if (nvls_available) {
+      a = Algo::kNvls;  // in-switch reduction: 1 + 1/ws of the message per direction
     } else {
-      // Peer-mapped without the switch (registered buffers, no multicast, two
-      // ranks): one push per peer wins while the fan-out is small.
+      // Peer-mapped without the switch (registered buffers, no multicast):
+      // one push per peer wins while the fan-out is small.
       a = bytes <= (world_size > 4 ? (16u << 10) : (512u << 10)) ? Algo::kOneShot : Algo::kDirect;
     }
   } else if (bytes <= OneShotLimit(world_size)) {
     a = Algo::kOneShot;  // ordinary buffers: one push per peer beats three staged phases
   } else if (nvls_available && world_size > 2) {
     a = Algo::kNvls;  // through the pool, pipelined inside the kernel (staged_kernel.cu)
-  } else if (world_size > 2 && bytes <= (32u << 20)) {
-    a = Algo::kDirect;  // staged; two synchronisation steps
+  } else if (bytes <= (world_size > 2 ? (32u << 20) : (128u << 20))) {
+    // Staged direct two-shot, pipelined inside the kernel.  Two ranks, 32 MiB:
+    // 89 us against the ring program's 134 us (NCCL 80); 128 MiB: 252 against 257.
+    a = Algo::kDirect;
   } else {
     // Large messages in ordinary memory without the switch, and two ranks: the
     // chunk-pipelined programs keep their staging inside the transfer.
