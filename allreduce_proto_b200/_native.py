@@ -85,6 +85,7 @@ def _declare(lib) -> None:
         "ibcomm_get_device_info": [vp, i, C.POINTER(DeviceInfo)],
         "ibcomm_set_timer_base": [vp],
         "ibcomm_dump_trace": [vp],
+        "ibcomm_staged_timeline": [vp, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_size_t)],
         "ibcomm_emu_create": [i, sz, sz, C.POINTER(vp)],
         "ibcomm_emu_destroy": [vp],
         "ibcomm_emu_allreduce": [vp, i, i, C.POINTER(vp), C.POINTER(vp), sz, dbl, i, i, vp, i],

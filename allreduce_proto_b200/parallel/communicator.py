@@ -380,3 +380,20 @@ class Communicator:
 
     def dump_trace(self) -> None:
         check(_native.lib().ibcomm_dump_trace(self._h))
+
+    def staged_timeline(self) -> dict:
+        """Per-role device stamps of the last allreduce that ran the pipelined staged kernel with tracing on
+        (``IBCOMM_TRACE=1``), CTA 0, in microseconds from the call's first stamp.  Per window: ``reduce`` =
+        (waits satisfied, last store issued, window published), ``load`` = (input buffer free, input window
+        published), ``store`` = (window reduced on every rank, output buffer released).  Empty without a trace."""
+        cap = 8 * 128
+        buf = (C.c_uint64 * cap)()
+        words = C.c_size_t(0)
+        check(_native.lib().ibcomm_staged_timeline(self._h, buf, cap, C.byref(words)))
+        w = min(int(words.value), cap) // 8
+        us = [v / 1e3 for v in buf[:8 * w]]
+        pair = lambda role, k: (us[2 * (role * w + k)], us[2 * (role * w + k) + 1])  # noqa: E731
+        return {"windows": w,
+                "reduce": [(pair(0, k)[0], pair(3, k)[0], pair(0, k)[1]) for k in range(w)],
+                "load": [pair(1, k) for k in range(w)],
+                "store": [pair(2, k) for k in range(w)]}

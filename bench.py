@@ -531,17 +531,27 @@ def tune(args, comm, world, rank, dev, time_steps) -> int:
             nb = plain_in[:m].clone()
             run("mid", f"nccl_{size >> 20}MiB", lambda: dist.all_reduce(nb), size=size, k=30, w=5)
     if "pipe" in sections:
-        # What bounds a window of the pipelined staged kernel: buffers in the cycle, bulk copies against
-        # register copies, window size (64 MiB message, ordinary buffers).
-        size = 64 << 20
-        m = size // 4
-        for algo in (["nvls"] if info["nvls"] and world > 2 else ["direct"]):
-            for kib in (1024, 2048, 4096, 8192, 0):
-                for bufs in (3, 6):
-                    for tma in (1, 0):
-                        run("pipe", f"{algo}_window{kib}KiB_bufs{bufs}_tma{tma}", allreduce(plain_in[:m], plain_out[:m], algo),
-                            {"IBCOMM_STAGED_WINDOW_KIB": kib, "IBCOMM_STAGED_BUFFERS": bufs, "IBCOMM_STAGED_TMA": tma},
-                            size=size, k=20, w=4)
+        # Shapes of the pipelined staged kernel on ordinary buffers: roles in every block or in blocks of
+        # their own, windows of each kind, groups per role, poster warps, bulk copies against register copies.
+        algo = "nvls" if info["nvls"] and world > 2 else "direct"
+        shapes = [("roles_in_every_block_bufs3", {"IBCOMM_STAGED_SPLIT": 0, "IBCOMM_STAGED_BUFFERS": 3})]
+        for bufs, lg, rg in ((3, 1, 2), (4, 2, 2), (6, 1, 2), (6, 2, 2), (6, 3, 2)):
+            for posters in (0, 1):
+                for tma in (1, 0):
+                    shapes.append((f"split_bufs{bufs}_groups{lg}_{rg}_{lg}_posters{posters}_tma{tma}",
+                                   {"IBCOMM_STAGED_SPLIT": 1, "IBCOMM_STAGED_BUFFERS": bufs, "IBCOMM_STAGED_LOAD_GROUPS": lg,
+                                    "IBCOMM_STAGED_REDUCE_GROUPS": rg, "IBCOMM_STAGED_STORE_GROUPS": lg,
+                                    "IBCOMM_STAGED_POSTERS": posters, "IBCOMM_STAGED_TMA": tma}))
+        for size in (64 << 20, 256 << 20):
+            m = size // 4
+            if m > n:
+                continue
+            for name, knobs in shapes:
+                run("pipe", f"{algo}_{name}_{size >> 20}MiB", allreduce(plain_in[:m], plain_out[:m], algo), knobs, size=size, k=20, w=4,
+                    check=plain_out[:m] if name.endswith("posters1_tma1") and name.startswith("split_bufs6_groups3") else None)
+            run("pipe", f"{algo}_zero_copy_{size >> 20}MiB", allreduce(sym_in[:m], sym_out[:m], algo), size=size, k=20, w=4)
+            nb = plain_in[:m].clone()
+            run("pipe", f"nccl_{size >> 20}MiB", lambda: dist.all_reduce(nb), size=size, k=20, w=4)
     if "execmid" in sections:
         # The op programs at medium sizes: CTAs x threads per CTA (per-op overhead against parallelism).
         for size in (16 << 20, 64 << 20):

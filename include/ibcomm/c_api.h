@@ -98,6 +98,10 @@ int ibcomm_get_device_info(ibcomm_comm* c, int connect, ibcomm_device_info* out)
 
 int ibcomm_set_timer_base(ibcomm_comm* c);
 int ibcomm_dump_trace(ibcomm_comm* c);
+/* Per-role stamps of the last traced call of the pipelined staged kernel (needs IBCOMM_TRACE=1): collects the
+ * device trace, copies at most `capacity_words` words to `out` and stores the number available in `*words`
+ * (8 x windows: pairs of nanoseconds from the first stamp; reducers, loader, storer, reducers' last store). */
+int ibcomm_staged_timeline(ibcomm_comm* c, uint64_t* out, size_t capacity_words, size_t* words);
 
 /* Several ranks emulated on one GPU (single cooperative launch per collective). */
 int ibcomm_emu_create(int num_ranks, size_t pool_bytes, size_t work_bytes, ibcomm_emu** out);

@@ -55,6 +55,13 @@ void DeviceContextRecvWait(DeviceContext* d, int src);
 // same on every rank): the caller then falls back to sends.
 bool DeviceContextBcast(DeviceContext* d, void* buf, size_t len, int root);
 void DeviceContextCollectTrace(DeviceContext* d, Tracer* tracer);
+// Per-role stamps of the last traced call of the pipelined staged kernel (CTA
+// 0), in nanoseconds from the call's first stamp: for W windows, 4 W pairs -
+// reducers (waits satisfied, window published), loader (input buffer free,
+// input window published), storer (window reduced everywhere, output buffer
+// released), reducers again (last store issued, 0).  Copies at most
+// `capacity_words` words and returns the number available (8 W, or 0).
+size_t DeviceContextStagedTimeline(DeviceContext* d, uint64_t* out, size_t capacity_words);
 
 // Introspection for bindings and tests.
 struct DeviceInfo {

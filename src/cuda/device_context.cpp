@@ -133,6 +133,7 @@ class DeviceContext {
   int RegisterBuffer(void* ptr, size_t bytes);
   void DeregisterBuffer(int id);
   void CollectTrace(Tracer* tracer);
+  const std::vector<uint64_t>& StagedTimeline() const { return staged_timeline_; }
   DeviceInfo Info() const;
   void SetMaxChannels(int c) { max_channels_ = c > 0 ? std::min(c, kMaxChannels) : std::min(env::ReadNumCudaStream(), kMaxChannels); }
 
@@ -217,8 +218,10 @@ class DeviceContext {
   struct PendingTrace {
     int channels;
     int ops;
+    int roles = 0;  // staged kernel: the other roles' stamps follow in three more ranges of `roles` records
     struct timespec host_launch;
   };
+  std::vector<uint64_t> staged_timeline_;  // last traced staged call, CTA 0: 4 x windows x (t_wait_done, t_done), ns from the first stamp
   std::deque<PendingTrace> pending_trace_;
   std::vector<std::pair<double, double>> trace_wait_, trace_done_;  // (start_ns, dur_ns) relative to base
   Tracer* tracer_ = nullptr;
@@ -734,7 +737,12 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   }
   const bool use_grown = big && grown_stage_ != nullptr && (!multimem || grown_stage_->mc != nullptr);
   const uint64_t stage_bytes = use_grown ? grown_stage_->bytes : arena_stage;
-  if (buffers <= 0) buffers = use_grown ? 4 : 3;
+  // Copy roles in blocks of their own (see the kernel): twice the blocks, all co-resident.
+  static const int resident = StagedKernelMaxCoResidentBlocks(device_);
+  const int cap = Tunable("IBCOMM_MAX_CTAS", 0);
+  const bool split = Tunable("IBCOMM_STAGED_SPLIT", 1) != 0 && resident >= 4 && (cap <= 0 || cap >= 2);
+  // Windows of 16-27 MiB measured best on 2 and 8 B200: three of each kind in the arena's 96 MiB, six in the grown block.
+  if (buffers <= 0) buffers = use_grown ? (split ? 6 : 4) : 3;
   buffers = std::max(3, std::min(buffers, kStagedMaxBuffers));
   const uint64_t quarter = stage_bytes / static_cast<uint64_t>(2 * buffers) / 4096 * 4096;
   if (quarter < 4096) return false;
@@ -754,15 +762,26 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   int ctas = Tunable("IBCOMM_STAGED_CTAS", 0);
   // 64 CTAs measured best for the switch path at every size from 16 MiB up (fewer flags per window).
   if (ctas <= 0) ctas = std::min(multimem ? 64 : 128, std::max(channels, ChooseChannels(Algo::kDirect, n * wsize, ws_, max_channels_)));
-  static const int resident = StagedKernelMaxCoResidentBlocks(device_);
   if (resident > 0) ctas = std::min(ctas, resident);
-  if (Tunable("IBCOMM_MAX_CTAS", 0) > 0) ctas = std::min(ctas, Tunable("IBCOMM_MAX_CTAS", 0));
-  ctas = std::max(1, std::min(ctas, 128));  // the kernel keeps a second row of flags at CTA index + 128
+  ctas = std::max(1, std::min(ctas, 128));  // two reducer groups' flag rows must fit the control page
+  if (split) ctas = std::max(1, std::min(ctas, resident / 2));
+  if (cap > 0) ctas = std::max(1, std::min(ctas, split ? cap / 2 : cap));
   uint64_t cap_bytes = quarter;
   const int max_window = Tunable("IBCOMM_STAGED_WINDOW_KIB", 0);  // experiment knob: smaller windows
   if (max_window > 0) cap_bytes = std::min<uint64_t>(cap_bytes, static_cast<uint64_t>(max_window) << 10);
   p.window_elems = TwoShotWindowElems(n, cap_bytes / wsize, wsize, ws_, ctas);
   p.buffers = buffers;
+  p.split_ctas = split ? 1 : 0;
+  // Groups per role (split mode): their flag rows must fit the control page.
+  auto groups = [&](const char* knob, int dflt) {
+    int g = std::max(1, std::min(Tunable(knob, dflt), 4));
+    while (g > 1 && g * ctas > kMaxChannels) --g;
+    return g;
+  };
+  p.load_groups = groups("IBCOMM_STAGED_LOAD_GROUPS", 1);
+  p.reduce_groups = groups("IBCOMM_STAGED_REDUCE_GROUPS", 2);
+  p.store_groups = groups("IBCOMM_STAGED_STORE_GROUPS", 1);
+  p.posters = Tunable("IBCOMM_STAGED_POSTERS", 0) != 0 ? 1 : 0;
   const uint64_t stage_off = use_grown ? 0 : layout_.pool_offset;
   for (int q = 0; q < ws_; ++q) p.stage[q] = use_grown ? grown_stage_->peer_ptr[q] : rr_.peers.arena[q];
   p.mc_stage = use_grown ? (grown_stage_->mc ? grown_stage_->mc->ptr() : nullptr) : rr_.peers.mc_arena;
@@ -775,8 +794,12 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   p.doorbell = rr_.d_doorbell;
   const uint64_t windows = (n + p.window_elems - 1) / p.window_elems;
   p.trace = BeginDeviceTrace(ctas, static_cast<int>(std::min<uint64_t>(windows, 1u << 20)), &p.trace_capacity);
+  if (p.trace != nullptr && 4 * windows <= static_cast<uint64_t>(p.trace_capacity)) {
+    p.trace_roles = static_cast<int32_t>(windows);
+    pending_trace_.back().roles = p.trace_roles;
+  }
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
-  CUDACHECK(LaunchStagedKernel(p, nullptr, 1, ctas, stream));
+  CUDACHECK(LaunchStagedKernel(p, nullptr, 1, split ? 2 * ctas : ctas, stream));
   ++kernel_launches_;
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
   staged_channels_ = ctas;
@@ -1301,6 +1324,14 @@ void DeviceContext::CollectTrace(Tracer* tracer) {
   const struct timespec& base = tracer->base();
   const double launch_ns = (static_cast<double>(pt.host_launch.tv_sec - base.tv_sec) * 1e9) +
                            static_cast<double>(pt.host_launch.tv_nsec - base.tv_nsec);
+  if (pt.roles > 0) {
+    staged_timeline_.assign(static_cast<size_t>(8 * pt.roles), 0);
+    for (int i = 0; i < 4 * pt.roles; ++i) {
+      const DeviceTraceRec& r = recs[static_cast<size_t>(i)];
+      staged_timeline_[static_cast<size_t>(2 * i)] = r.t_wait_done >= t0 ? r.t_wait_done - t0 : 0;
+      staged_timeline_[static_cast<size_t>(2 * i + 1)] = r.t_done >= t0 ? r.t_done - t0 : 0;
+    }
+  }
   // Channel 0 is representative; all channels run the same program.
   uint64_t prev = t0;
   for (int i = 0; i < pt.ops; ++i) {
@@ -1346,6 +1377,12 @@ void DeviceContextSendWait(DeviceContext* d, int dest) { d->SendWait(dest); }
 void DeviceContextRecvWait(DeviceContext* d, int src) { d->RecvWait(src); }
 bool DeviceContextBcast(DeviceContext* d, void* buf, size_t len, int root) { return d->Bcast(buf, len, root); }
 void DeviceContextCollectTrace(DeviceContext* d, Tracer* tracer) { d->CollectTrace(tracer); }
+size_t DeviceContextStagedTimeline(DeviceContext* d, uint64_t* out, size_t capacity_words) {
+  const std::vector<uint64_t>& t = d->StagedTimeline();
+  const size_t n = std::min(capacity_words, t.size());
+  for (size_t i = 0; i < n; ++i) out[i] = t[i];
+  return t.size();
+}
 DeviceInfo DeviceContextInfo(DeviceContext* d) { return d->Info(); }
 void DeviceContextSetMaxChannels(DeviceContext* d, int channels) { d->SetMaxChannels(channels); }
 void DeviceContextCheck(DeviceContext* d) { d->Check(); }

@@ -125,6 +125,8 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
   const size_t wsize = DTypeSize(wire);
   if (algo == Algo::kDirect && (wire != dtype || m.direct_staging == 2)) {
     // The pipelined staged kernel (what ordinary buffers and 16-bit wires get on several GPUs).
+    // Copy roles in blocks of their own: twice the blocks, all of them co-resident with every rank's.
+    const bool split = Tunable("IBCOMM_STAGED_SPLIT", 1) != 0 && m.staged_max_blocks / m.ws >= 2;
     int buffers = Tunable("IBCOMM_STAGED_BUFFERS", 3);
     buffers = std::max(3, std::min(buffers, kStagedMaxBuffers));
     const uint64_t quarter = (m.layout.pool_bytes + m.layout.work_bytes) / static_cast<uint64_t>(2 * buffers) / 4096 * 4096;
@@ -132,6 +134,7 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
       IBCOMM_FAIL(NOT_SUPPORTED, "The pipelined staged two-shot needs 16-byte aligned buffers of whole 16-byte wire vectors.\n");
     int ch = channels > 0 ? channels : ChooseChannels(Algo::kDirect, n * wsize, m.ws, kMaxChannels);
     ch = std::max(1, std::min(std::min(ch, 128), std::max(1, m.staged_max_blocks / m.ws)));
+    if (split) ch = std::max(1, std::min(ch, m.staged_max_blocks / m.ws / 2));
     std::vector<StagedParams> ps(static_cast<size_t>(m.ws));
     for (int r = 0; r < m.ws; ++r) {
       StagedParams& p = ps[static_cast<size_t>(r)];
@@ -150,6 +153,11 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
       p.scale = scale;
       p.window_elems = TwoShotWindowElems(n, quarter / wsize, wsize, m.ws, ch);
       p.buffers = buffers;
+      p.split_ctas = split ? 1 : 0;
+      p.load_groups = std::max(1, std::min(Tunable("IBCOMM_STAGED_LOAD_GROUPS", 1), 4));
+      p.reduce_groups = std::max(1, std::min(Tunable("IBCOMM_STAGED_REDUCE_GROUPS", 2), 4));
+      p.store_groups = std::max(1, std::min(Tunable("IBCOMM_STAGED_STORE_GROUPS", 1), 4));
+      p.posters = Tunable("IBCOMM_STAGED_POSTERS", 0) != 0 ? 1 : 0;
       for (int q = 0; q < m.ws; ++q) p.stage[q] = rr.peers.arena[q];
       p.mc_stage = nullptr;
       for (int j = 0; j < buffers; ++j) {
@@ -163,7 +171,7 @@ void EmuWorld::Allreduce(Algo algo, DType dtype, const std::vector<const void*>&
     }
     void* d = m.Params(ps.size() * sizeof(StagedParams));
     CUDACHECK(cudaMemcpyAsync(d, ps.data(), ps.size() * sizeof(StagedParams), cudaMemcpyHostToDevice, stream));
-    CUDACHECK(LaunchStagedKernel(ps[0], static_cast<const StagedParams*>(d), m.ws, ch, stream));
+    CUDACHECK(LaunchStagedKernel(ps[0], static_cast<const StagedParams*>(d), m.ws, split ? 2 * ch : ch, stream));
     m.last_channels = ch;
   } else if (algo == Algo::kDirect) {
     // The two-shot kernel with peer loads and stores.  All ranks' buffers live

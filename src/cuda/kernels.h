@@ -112,13 +112,20 @@ struct StagedParams {
   uint64_t in_off[kStagedMaxBuffers];    // byte offsets of the input windows inside the staging memory
   uint64_t out_off[kStagedMaxBuffers];   // ... and of the output windows
   int32_t buffers;       // windows of each kind in use (3 .. kStagedMaxBuffers)
-  int32_t pad0_;
+  int32_t split_ctas;    // 1: the grid is 2 n blocks, [0, n) reduce and [n, 2n) copy; 0: every block does both
   uint64_t timeout_ns;
   DeviceStatus* status;
   uint32_t* doorbell;
   DeviceTraceRec* trace;   // [CTA][trace_capacity]: per window, when the reduce could start and when it was done
   int32_t trace_capacity;  // 0 = tracing off
-  int32_t pad_;
+  // W > 0: the other roles stamp too, W = number of windows, 4 W <= trace_capacity.  Records [W, 2W): the
+  // loader (input buffer free, input window published), [2W, 3W): the storer (window reduced everywhere,
+  // output buffer released), [3W, 4W): t_wait_done = the reducers' last store issued (before the fence).
+  int32_t trace_roles;
+  // Split mode: groups per role (1 .. 4) that take the windows in turn.  groups x reducing blocks <= 256
+  // (a group has flag rows of its own).
+  int32_t load_groups, reduce_groups, store_groups;
+  int32_t posters;  // split mode: a poster warp per reducer group fences and publishes behind the data warps
 };
 cudaError_t LaunchStagedKernel(const StagedParams& p, const StagedParams* emu, int emu_ranks, int blocks, cudaStream_t stream);
 // Largest grid of the staged kernel that is co-resident on `device` (0 on error).

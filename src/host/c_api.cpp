@@ -432,6 +432,20 @@ int ibcomm_dump_trace(ibcomm_comm* c) {
     c->comm.DumpTrace();
   });
 }
+int ibcomm_staged_timeline(ibcomm_comm* c, uint64_t* out, size_t capacity_words, size_t* words) {
+  return Guard([&] {
+    NeedHandle(c);
+    *words = 0;
+#ifdef USE_CUDA
+    if (c->comm.device() != nullptr) {
+      ibcomm::DeviceContextCollectTrace(c->comm.device(), &c->comm.tracer());
+      *words = ibcomm::DeviceContextStagedTimeline(c->comm.device(), out, capacity_words);
+    }
+#else
+    (void)out; (void)capacity_words;
+#endif
+  });
+}
 
 int ibcomm_emu_create(int num_ranks, size_t pool_bytes, size_t work_bytes, ibcomm_emu** out) {
   return Guard([&] {

@@ -129,60 +129,61 @@ bool RunAllreduce(int ws, int ncta, uint64_t n, uint64_t cap_elems) {
 }
 
 // ---- pipelined staged two-shot (staged_kernel.cu) ----
-// One thread per (rank, CTA, role): loader, reducer A (even windows), reducer
-// B (odd windows), storer.  Three input and three output windows per rank;
-// four flag rows per (rank, CTA, source): in_ready, reduced (even windows),
-// reduced (odd windows), out_free.  The waits and posts are the kernel's:
-// loader k waits reduced >= k-2 (the window that used the buffer three
-// windows ago), reducer k waits in_ready >= k+1 and out_free >= k-2, storer k
-// waits reduced >= k+1.
-constexpr int kBufs = 3;
+// One thread per (rank, CTA, role, group): loaders, reducers, storers; a role's
+// groups take the windows in turn.  `bufs` input and `bufs` output windows per
+// rank; flag rows per (group, rank, CTA, source) of three kinds: in_ready,
+// reduced, out_free.  The waits and posts are the kernel's: loader k waits
+// reduced >= k-bufs+1 (the window that used the buffer before), reducer k
+// waits in_ready >= k+1 and out_free >= k-bufs+1, storer k waits reduced >= k+1.
 struct PipeWorld {
-  int ws, ncta;
-  std::vector<std::vector<int64_t>> in[kBufs], out[kBufs];
-  std::vector<std::atomic<uint64_t>> row[4];  // 0 in_ready, 1 reduced even, 2 reduced odd, 3 out_free
-  PipeWorld(int ws_, int ncta_, size_t window) : ws(ws_), ncta(ncta_) {
-    for (int j = 0; j < kBufs; ++j) {
-      in[j].assign(ws_, std::vector<int64_t>(window, -7));
-      out[j].assign(ws_, std::vector<int64_t>(window, -7));
-    }
-    for (auto& r : row) {
-      r = std::vector<std::atomic<uint64_t>>(static_cast<size_t>(ws_) * ncta_ * ws_);
-      for (auto& f : r) f.store(0);
+  int ws, ncta, bufs;
+  int groups[3];  // per kind of row: 0 in_ready (loader groups), 1 reduced (reducer groups), 2 out_free (storer groups)
+  std::vector<std::vector<std::vector<int64_t>>> in, out;  // [buffer][rank][element]
+  std::vector<std::atomic<uint64_t>> row[3];               // [group][rank][cta][source rank]
+  PipeWorld(int ws_, int ncta_, size_t window, int bufs_, int lg, int rg, int sg) : ws(ws_), ncta(ncta_), bufs(bufs_), groups{lg, rg, sg} {
+    in.assign(bufs_, std::vector<std::vector<int64_t>>(ws_, std::vector<int64_t>(window, -7)));
+    out = in;
+    for (int k = 0; k < 3; ++k) {
+      row[k] = std::vector<std::atomic<uint64_t>>(static_cast<size_t>(groups[k]) * ws_ * ncta_ * ws_);
+      for (auto& f : row[k]) f.store(0);
     }
   }
-  static int ReducedRow(uint64_t window) { return 1 + static_cast<int>(window & 1); }
-  std::atomic<uint64_t>& Flag(int which, int rank, int cta, int src) { return row[which][(static_cast<size_t>(rank) * ncta + cta) * ws + src]; }
-  void WaitAll(int which, int rank, int cta, uint64_t v) {
+  // Window k's words of one kind live in the rows of group k % groups: the
+  // groups of a role finish their windows in any order, a row's values only grow.
+  std::atomic<uint64_t>& Flag(int kind, uint64_t window, int rank, int cta, int src) {
+    const size_t g = static_cast<size_t>(window % static_cast<uint64_t>(groups[kind]));
+    return row[kind][((g * ws + rank) * ncta + cta) * ws + src];
+  }
+  void WaitAll(int kind, uint64_t window, int rank, int cta, uint64_t v) {
     for (int q = 0; q < ws; ++q)
-      while (Flag(which, rank, cta, q).load(std::memory_order_acquire) < v) std::this_thread::yield();
+      while (Flag(kind, window, rank, cta, q).load(std::memory_order_acquire) < v) std::this_thread::yield();
   }
-  void PostAll(int which, int rank, int cta, uint64_t v) {
-    for (int q = 0; q < ws; ++q) Flag(which, q, cta, rank).store(v, std::memory_order_release);
+  void PostAll(int kind, uint64_t window, int rank, int cta, uint64_t v) {
+    for (int q = 0; q < ws; ++q) Flag(kind, window, q, cta, rank).store(v, std::memory_order_release);
   }
 };
 
-// role: 0 loader, 1 reducer A, 2 reducer B, 3 storer.
-void PipeRole(PipeWorld* w, int role, uint64_t seq, int rank, int cta, const std::vector<int64_t>& send, std::vector<int64_t>* recv,
-              uint64_t total_nv, uint64_t full_nv) {
+// role: 0 loader, 1 reducer, 2 storer; `group` of the role's `w->groups[role]` groups takes windows
+// group, group + groups, ...  (StagedKernel: the groups are warps of a block, or of two blocks in split mode).
+void PipeRole(PipeWorld* w, int role, int group, uint64_t seq, int rank, int cta, const std::vector<int64_t>& send,
+              std::vector<int64_t>* recv, uint64_t total_nv, uint64_t full_nv) {
   const int ws = w->ws, ncta = w->ncta;
-  const uint64_t base = seq << 32;
+  const uint64_t base = seq << 32, bufs = static_cast<uint64_t>(w->bufs);
   const uint64_t windows = (total_nv + full_nv - 1) / full_nv;
-  const bool reducer = role == 1 || role == 2;
-  for (uint64_t k = reducer ? static_cast<uint64_t>(role - 1) : 0; k < windows; k += reducer ? 2 : 1) {
-    const int j = static_cast<int>(k % kBufs);
+  for (uint64_t k = static_cast<uint64_t>(group); k < windows; k += static_cast<uint64_t>(w->groups[role])) {
+    const int j = static_cast<int>(k % bufs);
     const uint64_t v0 = k * full_nv, nv = std::min(full_nv, total_nv - v0);
     if (role == 0) {
-      if (k >= kBufs) w->WaitAll(PipeWorld::ReducedRow(k - kBufs), rank, cta, base | (k - kBufs + 1));
+      if (k >= bufs) w->WaitAll(1, k - bufs, rank, cta, base | (k - bufs + 1));
       for (int s = 0; s < ws; ++s) {
         uint64_t b, e;
         WindowPart(full_nv, nv, s, ws, cta, ncta, &b, &e);
         for (uint64_t i = b * kVec; i < e * kVec; ++i) w->in[j][rank][i] = send[v0 * kVec + i];
       }
-      w->PostAll(0, rank, cta, base | (k + 1));
-    } else if (reducer) {
-      w->WaitAll(0, rank, cta, base | (k + 1));
-      if (k >= kBufs) w->WaitAll(3, rank, cta, base | (k - kBufs + 1));
+      w->PostAll(0, k, rank, cta, base | (k + 1));
+    } else if (role == 1) {
+      w->WaitAll(0, k, rank, cta, base | (k + 1));
+      if (k >= bufs) w->WaitAll(2, k - bufs, rank, cta, base | (k - bufs + 1));
       uint64_t b, e;
       WindowPart(full_nv, nv, rank, ws, cta, ncta, &b, &e);
       for (uint64_t i = b * kVec; i < e * kVec; ++i) {
@@ -190,25 +191,25 @@ void PipeRole(PipeWorld* w, int role, uint64_t seq, int rank, int cta, const std
         for (int q = 0; q < ws; ++q) acc += w->in[j][q][i];
         for (int q = 0; q < ws; ++q) w->out[j][q][i] = acc;
       }
-      w->PostAll(PipeWorld::ReducedRow(k), rank, cta, base | (k + 1));
+      w->PostAll(1, k, rank, cta, base | (k + 1));
     } else {
-      w->WaitAll(PipeWorld::ReducedRow(k), rank, cta, base | (k + 1));
+      w->WaitAll(1, k, rank, cta, base | (k + 1));
       for (int s = 0; s < ws; ++s) {
         uint64_t b, e;
         WindowPart(full_nv, nv, s, ws, cta, ncta, &b, &e);
         for (uint64_t i = b * kVec; i < e * kVec; ++i) (*recv)[v0 * kVec + i] = w->out[j][rank][i];
       }
-      w->PostAll(3, rank, cta, base | (k + 1));
+      w->PostAll(2, k, rank, cta, base | (k + 1));
     }
   }
 }
 
-bool RunPipelined(int ws, int ncta, uint64_t n_vec, uint64_t cap_elems) {
+bool RunPipelined(int ws, int ncta, uint64_t n_vec, uint64_t cap_elems, int bufs = 3, int lg = 1, int rg = 2, int sg = 1) {
   const uint64_t n = n_vec * kVec;
   const uint64_t window = TwoShotWindowElems(n, cap_elems, 16 / kVec, ws, ncta);
   const uint64_t full_nv = window / kVec;
   if (full_nv == 0) return true;
-  PipeWorld w(ws, ncta, window);
+  PipeWorld w(ws, ncta, window, bufs, lg, rg, sg);
   std::vector<std::vector<int64_t>> send(ws, std::vector<int64_t>(n)), recv(ws, std::vector<int64_t>(n, -1));
   for (int r = 0; r < ws; ++r)
     for (uint64_t i = 0; i < n; ++i) send[r][i] = Value(r, i);
@@ -219,7 +220,9 @@ bool RunPipelined(int ws, int ncta, uint64_t n_vec, uint64_t cap_elems) {
       std::fill(recv[r].begin(), recv[r].end(), -1);
       std::vector<std::thread> t;
       for (int c = 0; c < ncta; ++c)
-        for (int role = 0; role < 4; ++role) t.emplace_back(PipeRole, &w, role, seq, r, c, std::cref(send[r]), &recv[r], n_vec, full_nv);
+        for (int role = 0; role < 3; ++role)
+          for (int g = 0; g < w.groups[role]; ++g)
+            t.emplace_back(PipeRole, &w, role, g, seq, r, c, std::cref(send[r]), &recv[r], n_vec, full_nv);
       for (auto& x : t) x.join();
       for (uint64_t i = 0; i < n; ++i)
         if (recv[r][i] != Sum(ws, i)) ++bad;
@@ -229,8 +232,8 @@ bool RunPipelined(int ws, int ncta, uint64_t n_vec, uint64_t cap_elems) {
   for (int r = 0; r < ws; ++r) ranks.emplace_back(rank_body, r);
   for (auto& t : ranks) t.join();
   if (bad.load() != 0)
-    fprintf(stderr, "pipelined ws=%d ncta=%d nvec=%llu window=%llu: %d wrong elements\n", ws, ncta,
-            static_cast<unsigned long long>(n_vec), static_cast<unsigned long long>(window), bad.load());
+    fprintf(stderr, "pipelined ws=%d ncta=%d nvec=%llu window=%llu bufs=%d groups=%d/%d/%d: %d wrong elements\n", ws, ncta,
+            static_cast<unsigned long long>(n_vec), static_cast<unsigned long long>(window), bufs, lg, rg, sg, bad.load());
   return bad.load() == 0;
 }
 
@@ -550,6 +553,13 @@ MINI_TEST(PipelinedStagedProtocol) {
     for (int ncta : {1, 2, 3})
       for (uint64_t nvec : {uint64_t(1), uint64_t(9), uint64_t(64), uint64_t(65), uint64_t(200), uint64_t(513)})
         CHECK_TRUE(RunPipelined(ws, ncta, nvec, 256));
+  // Split mode: several groups per role, up to six windows of each kind.
+  for (int ws : {2, 3})
+    for (int bufs : {3, 4, 6})
+      for (int lg : {1, 3, 4})
+        for (int rg : {1, 2, 3})
+          for (uint64_t nvec : {uint64_t(9), uint64_t(200), uint64_t(1100)})
+            CHECK_TRUE(RunPipelined(ws, 2, nvec, 256, bufs, lg, rg, lg == 4 ? 2 : 3));
 }
 
 MINI_TEST(HybridSplitProtocol) {

@@ -355,8 +355,26 @@ def case_trace(comm):
     x = seeded(1 << 20, torch.float32, RANK)
     for algo in ("ring", "rabenseifner"):
         comm.allreduce(x.clone(), algo=algo, sync=True)
+    # The pipelined staged kernel stamps per role and window: an ordinary tensor of three windows
+    # (the staging is cut to 1 MiB windows for this), then the stamps must tell the story in order.
+    ar.utils.set_tunable("IBCOMM_STAGED_WINDOW_KIB", 1024)
+    y = seeded(3 << 18, torch.float32, RANK)
+    comm.allreduce(y, algo="direct", sync=True)
+    ar.utils.set_tunable("IBCOMM_STAGED_WINDOW_KIB", -1)
+    t = comm.staged_timeline()
+    rc = 0
+    if t["windows"] != 3:
+        print(f"rank {RANK}: staged timeline has {t['windows']} windows, expected 3", file=sys.stderr)
+        rc = 1
+    for k in range(t["windows"]):
+        start, stored, published = t["reduce"][k]
+        # (a role stamps after it has published, so the next role's stamp may come a moment earlier)
+        if not (t["load"][k][1] <= start + 5.0 and start <= stored <= published and published <= t["store"][k][0] + 5.0
+                and t["store"][k][0] <= t["store"][k][1]):
+            print(f"rank {RANK}: staged timeline out of order at window {k}: {t}", file=sys.stderr)
+            rc = 1
     comm.dump_trace()
-    return 0
+    return rc
 
 
 def case_leave(comm):

@@ -149,13 +149,16 @@ def test_direct_two_shot(ws):
     w.set_direct_staging(0)
 
 
+@pytest.mark.parametrize("split", [1, 0])
 @pytest.mark.parametrize("ws", [2, 3, 4, 8])
-def test_pipelined_staged_two_shot(ws):
-    # The pipelined kernel for buffers that go through the pool (loader, reducer and storer warps of a CTA on
-    # three windows at once).  2 MiB of staging = four windows of 512 KiB, so the larger messages take many
-    # windows (the last one short); copies by the bulk copy engine and, with the knob off, in registers.
+def test_pipelined_staged_two_shot(ws, split):
+    # The pipelined kernel for buffers that go through the pool (loader, reducer and storer warps on three
+    # windows at once; the copy roles in blocks of their own, or, with the knob off, in every block).  2 MiB of
+    # staging = four windows of 512 KiB, so the larger messages take many windows (the last one short); copies
+    # by the bulk copy engine and, with the knob off, in registers.
     w = world(ws, 1 << 20, 1 << 20)
     w.set_direct_staging(2)
+    ar.utils.set_tunable("IBCOMM_STAGED_SPLIT", split)
     try:
         for tma in (1, 0):
             ar.utils.set_tunable("IBCOMM_STAGED_TMA", tma)
@@ -181,43 +184,87 @@ def test_pipelined_staged_two_shot(ws):
             check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
     finally:
         ar.utils.set_tunable("IBCOMM_STAGED_TMA", -1)
+        ar.utils.set_tunable("IBCOMM_STAGED_SPLIT", -1)
         w.set_direct_staging(0)
 
 
+@pytest.mark.parametrize("shape", [(6, 3, 2, 3, 1), (4, 2, 3, 2, 0), (6, 4, 2, 2, 1), (3, 1, 1, 1, 1)])
+@pytest.mark.parametrize("ws", [2, 4])
+def test_pipelined_staged_groups_and_posters(ws, shape):
+    # Split mode with several groups per role (window k belongs to group k mod groups, each group with flag
+    # rows of its own) and poster warps behind the reducer groups; many short windows so that every group
+    # takes several, the last one short.
+    bufs, lg, rg, sg, posters = shape
+    knobs = {"IBCOMM_STAGED_SPLIT": 1, "IBCOMM_STAGED_BUFFERS": bufs, "IBCOMM_STAGED_LOAD_GROUPS": lg,
+             "IBCOMM_STAGED_REDUCE_GROUPS": rg, "IBCOMM_STAGED_STORE_GROUPS": sg, "IBCOMM_STAGED_POSTERS": posters}
+    w = world(ws, 1 << 20, 1 << 20)
+    w.set_direct_staging(2)
+    for k, v in knobs.items():
+        ar.utils.set_tunable(k, v)
+    try:
+        for tma in (1, 0):
+            ar.utils.set_tunable("IBCOMM_STAGED_TMA", tma)
+            for n in (8 * ws, 65536 + 8, (1 << 20) + 12344, 3 << 20):
+                ins = make_inputs(ws, n, torch.float32, seed=n + ws)
+                outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+                for _ in range(2):  # back to back, no host synchronisation in between
+                    w.allreduce(ins, outs, algo="direct", scale=0.25, sync=False)
+                torch.cuda.synchronize()
+                check(outs, reference(ins, 0.25, torch.float32), torch.float32, ws)
+        ins = make_inputs(ws, 1 << 20, torch.float32, seed=9)
+        outs = [torch.zeros(1 << 20, device="cuda") for _ in range(ws)]
+        w.allreduce(ins, outs, algo="direct", wire=torch.bfloat16)
+        check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws, wire=torch.bfloat16)
+    finally:
+        for k in list(knobs) + ["IBCOMM_STAGED_TMA"]:
+            ar.utils.set_tunable(k, -1)
+        w.set_direct_staging(0)
+
+
+@pytest.mark.parametrize("split", [1, 0])
 @pytest.mark.parametrize("wire", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("ws", [2, 4, 8])
-def test_two_shot_with_16_bit_wire(ws, wire):
+def test_two_shot_with_16_bit_wire(ws, wire, split):
     # fp32 buffers, 16-bit values in the pool and on the wire, fp32 sums: the direct two-shot through the
     # pipelined kernel.  Every rank must end up with the same bits.
     w = world(ws, 1 << 20, 1 << 20)
-    for n in (8 * ws, 65536, 300000, (1 << 20) + 8):
-        ins = make_inputs(ws, n, torch.float32, seed=n)
-        outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
-        w.allreduce(ins, outs, algo="direct", wire=wire, scale=1.0 / ws)
-        check(outs, reference(ins, 1.0 / ws, torch.float32), torch.float32, ws, wire=wire)
-        for o in outs[1:]:
-            assert torch.equal(o, outs[0])
+    ar.utils.set_tunable("IBCOMM_STAGED_SPLIT", split)
+    try:
+        for n in (8 * ws, 65536, 300000, (1 << 20) + 8):
+            ins = make_inputs(ws, n, torch.float32, seed=n)
+            outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+            w.allreduce(ins, outs, algo="direct", wire=wire, scale=1.0 / ws)
+            check(outs, reference(ins, 1.0 / ws, torch.float32), torch.float32, ws, wire=wire)
+            for o in outs[1:]:
+                assert torch.equal(o, outs[0])
+    finally:
+        ar.utils.set_tunable("IBCOMM_STAGED_SPLIT", -1)
 
 
-def test_pipelined_staged_wait_runs_out():
+@pytest.mark.parametrize("split", [1, 0])
+def test_pipelined_staged_wait_runs_out(split):
     # A rank that takes no part: the others' loaders, reducers and storers give up after the limit, the kernel
     # returns, the status names the wait, and the world stays usable.
     ws = 4
     w = ar.EmuWorld(ws, 1 << 20, 1 << 20)
     w.set_direct_staging(2)
     w.set_timeout_ms(200)
-    n = 1 << 16
-    ins = make_inputs(ws, n, torch.float32)
-    outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
-    w.set_silent_rank(1)
-    with pytest.raises(ar.IbcommError) as e:
+    ar.utils.set_tunable("IBCOMM_STAGED_SPLIT", split)
+    try:
+        n = 1 << 16
+        ins = make_inputs(ws, n, torch.float32)
+        outs = [torch.zeros(n, device="cuda") for _ in range(ws)]
+        w.set_silent_rank(1)
+        with pytest.raises(ar.IbcommError) as e:
+            w.allreduce(ins, outs, algo="direct")
+        assert e.value.code == ar.TRANSPORT_ERROR
+        assert w.last_status()["code"] in (1, 2)
+        w.set_silent_rank(-1)
+        w.set_timeout_ms(5000)
         w.allreduce(ins, outs, algo="direct")
-    assert e.value.code == ar.TRANSPORT_ERROR
-    assert w.last_status()["code"] in (1, 2)
-    w.set_silent_rank(-1)
-    w.set_timeout_ms(5000)
-    w.allreduce(ins, outs, algo="direct")
-    check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+        check(outs, reference(ins, 1.0, torch.float32), torch.float32, ws)
+    finally:
+        ar.utils.set_tunable("IBCOMM_STAGED_SPLIT", -1)
 
 
 def test_unaligned_buffers_take_the_scalar_path():
