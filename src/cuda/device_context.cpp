@@ -661,6 +661,18 @@ void DeviceContext::RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, 
 
 int DeviceContext::ClampChannels(Algo algo, int channels) {
   int limit;
+  if (algo == Algo::kRing && Tunable("IBCOMM_EXEC_CHANNELS", 0) <= 0) {
+    // One 512-thread block per SM at most.  Beyond that the executor runs two
+    // 256-thread blocks per SM, whose three data warps per op make a ring step
+    // twice as slow at medium sizes (64 MiB: 53-65 us per step on 3-6 ranks
+    // with 170-256 channels against 28-29 us on 7-8 ranks with 128-146), for
+    // 3 % at 256 MiB on 8 GPUs and a gain on 2.
+    static const int sms = [this] {
+      int n = 0;
+      return cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device_) == cudaSuccess ? n : 0;
+    }();
+    if (sms > 0) channels = std::min(channels, sms);
+  }
   if (algo == Algo::kRing || algo == Algo::kRabenseifner) {
     const int threads = ExecKernelThreadsFor(channels);
     auto it = exec_resident_.find(threads);
