@@ -134,13 +134,13 @@ TunerChoice ChooseAlgorithm(size_t bytes, int world_size, bool nvls_available, b
     a = Algo::kOneShot;  // ordinary buffers: one push per peer beats three staged phases
   } else if (nvls_available && world_size > 2) {
     a = Algo::kNvls;  // through the pool, pipelined inside the kernel (staged_kernel.cu)
-  } else if (bytes <= (world_size > 2 ? (32u << 20) : (128u << 20))) {
-    // Staged direct two-shot, pipelined inside the kernel.  Two ranks, 32 MiB:
-    // 89 us against the ring program's 134 us (NCCL 80); 128 MiB: 252 against 257.
-    a = Algo::kDirect;
+  } else if (world_size > 2 && bytes <= (32u << 20)) {
+    a = Algo::kDirect;  // staged direct two-shot, pipelined inside the kernel
   } else {
     // Large messages in ordinary memory without the switch, and two ranks: the
-    // chunk-pipelined programs keep their staging inside the transfer.
+    // chunk-pipelined programs keep their staging inside the transfer (two
+    // ranks, one 512-thread block per SM: 89 / 137 / 238 / 440 us at 32 / 64 /
+    // 128 / 256 MiB against the staged direct kernel's 98 / 154 / 264 / 462).
     // Halving/doubling needs fewer steps.
     a = (world_size > 2 && util::GetExpOfTwo(static_cast<uint64_t>(world_size)) != 0) ? Algo::kRabenseifner : Algo::kRing;
   }

@@ -141,7 +141,8 @@ def test_algorithm_table():
     assert ca(256 << 10, 8, mapped=False)[0] == "oneshot"
     assert ca(4 * MiB, 2, mapped=False)[0] == "oneshot"          # two ranks: one push each is all the traffic there is
     assert ca(2 * MiB, 2)[0] == "oneshot" and ca(8 * MiB, 2)[0] == "direct"
-    assert ca(64 * MiB, 2, mapped=False)[0] == "direct"          # staged and pipelined inside the kernel
+    assert ca(64 * MiB, 2, mapped=False)[0] == "ring"            # two ranks: the ring is one exchange each way
+    assert ca(16 * MiB, 4, nvls=False, mapped=False)[0] == "direct"   # staged and pipelined inside the kernel
     assert ca(256 * MiB, 2, mapped=False)[0] == "ring"
     for ws in range(2, 9):
         for nb in (4, 4096, MiB, 64 * MiB, 1 << 30):
