@@ -37,7 +37,8 @@ class IbcommError(RuntimeError):
 class DeviceInfo(C.Structure):
     _fields_ = [("device", C.c_int), ("nvls", C.c_int), ("share_mode", C.c_int), ("last_algo", C.c_int),
                 ("last_channels", C.c_int), ("pad_", C.c_int), ("arena_bytes", C.c_uint64),
-                ("pool_bytes", C.c_uint64), ("work_bytes", C.c_uint64), ("calls", C.c_uint64), ("kernel_launches", C.c_uint64)]
+                ("pool_bytes", C.c_uint64), ("work_bytes", C.c_uint64), ("calls", C.c_uint64), ("kernel_launches", C.c_uint64),
+                ("switch_registrations", C.c_uint64)]
 
 
 class StatusReport(C.Structure):

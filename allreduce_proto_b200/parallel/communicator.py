@@ -372,7 +372,8 @@ class Communicator:
         return {"device": info.device, "nvls": bool(info.nvls), "share_mode": "vmm" if info.share_mode == 0 else "ipc",
                 "last_algo": ALGO_NAMES.get(info.last_algo, "copy"), "last_channels": info.last_channels,
                 "arena_bytes": info.arena_bytes, "pool_bytes": info.pool_bytes, "work_bytes": info.work_bytes,
-                "calls": info.calls, "kernel_launches": info.kernel_launches}
+                "calls": info.calls, "kernel_launches": info.kernel_launches,
+                "switch_registrations": info.switch_registrations}
 
     # -------------------------------------------------------------- tracing
     def set_timer_base(self) -> None:

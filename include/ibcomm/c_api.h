@@ -92,6 +92,7 @@ typedef struct {
   uint64_t work_bytes;
   uint64_t calls;
   uint64_t kernel_launches;
+  uint64_t switch_registrations; /* registered user buffers the switch kernels can use in place */
 } ibcomm_device_info;
 /* Connects the device path if necessary (collective on first use). */
 int ibcomm_get_device_info(ibcomm_comm* c, int connect, ibcomm_device_info* out);

@@ -75,6 +75,7 @@ struct DeviceInfo {
   int last_algo;       // Algo of the most recent allreduce
   int last_channels;
   uint64_t kernel_launches;  // kernels of this library launched so far
+  uint64_t switch_registrations;  // registered user buffers that are bound to the NVSwitch multicast
 };
 DeviceInfo DeviceContextInfo(DeviceContext* d);
 // Caps the channels a collective may use (0 = back to IBCOMM_NUM_CUDA_STREAM).

@@ -271,4 +271,44 @@ void MulticastGroup::BindAndMap(const SharedAllocation& mem, int device) {
   ptr_ = reinterpret_cast<unsigned char*>(va);
 }
 
+bool MulticastGroup::BindAddrAndMap(void* ptr, int device, std::string* why) {
+  const drv::Api* api = drv::Get();
+  if (api == nullptr || api->MulticastBindAddr == nullptr) {
+    *why = "the driver has no cuMulticastBindAddr";
+    return false;
+  }
+  CUresult r = api->MulticastBindAddr(mc_, 0, reinterpret_cast<CUdeviceptr>(ptr), bytes_, 0);
+  if (r != CUDA_SUCCESS) {
+    *why = std::string("cuMulticastBindAddr: ") + drv::ErrorString(r);
+    return false;
+  }
+  bound_ = true;
+  CUdeviceptr va = 0;
+  size_t gran = Granularity(num_devices_, bytes_);
+  if (gran < (2u << 20)) gran = 2u << 20;
+  r = api->MemAddressReserve(&va, bytes_, gran, 0, 0);
+  if (r != CUDA_SUCCESS) {
+    *why = std::string("cuMemAddressReserve: ") + drv::ErrorString(r);
+    return false;
+  }
+  r = api->MemMap(va, bytes_, 0, mc_, 0);
+  if (r != CUDA_SUCCESS) {
+    api->MemAddressFree(va, bytes_);
+    *why = std::string("cuMemMap: ") + drv::ErrorString(r);
+    return false;
+  }
+  ptr_ = reinterpret_cast<unsigned char*>(va);  // from here on Release() unmaps and frees
+  CUmemAccessDesc desc;
+  memset(&desc, 0, sizeof(desc));
+  desc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  desc.location.id = device;
+  desc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  r = api->MemSetAccess(va, bytes_, &desc, 1);
+  if (r != CUDA_SUCCESS) {
+    *why = std::string("cuMemSetAccess: ") + drv::ErrorString(r);
+    return false;
+  }
+  return true;
+}
+
 }  // namespace ibcomm

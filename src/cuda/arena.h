@@ -7,6 +7,8 @@
 // falls back to cudaMalloc + a CUDA IPC handle (no multicast then).
 #pragma once
 
+#include <string>
+
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -84,6 +86,12 @@ class MulticastGroup {
   void AddDevice(int device);
   // After EVERY rank has added its device: bind my memory, map the alias.
   void BindAndMap(const SharedAllocation& mem, int device);
+  // The same for `bytes()` bytes of existing device memory at `ptr` (any
+  // allocation of this device; address and size multiples of the
+  // granularity).  Not fatal: false, with a reason in `why`, when the driver
+  // refuses; the group is then unusable and must be released by every rank.
+  bool BindAddrAndMap(void* ptr, int device, std::string* why);
+  size_t bytes() const { return bytes_; }
   unsigned char* ptr() const { return ptr_; }
   bool valid() const { return ptr_ != nullptr; }
   void Release();

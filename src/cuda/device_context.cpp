@@ -48,6 +48,20 @@ struct RegisteredBuffer {
   size_t bytes = 0;
   unsigned char* peer_ptr[kMaxRanks] = {nullptr};
   unsigned long long peer_alloc[kMaxRanks] = {0};  // key of the peer's imported allocation
+  // With NVSwitch multicast: the granules around the buffer are bound to a
+  // multicast object of their own (every rank's at offset 0), so the switch
+  // kernels reduce and broadcast the buffer in place.  `mc_ptr` is the
+  // multicast alias of `ptr`.
+  std::shared_ptr<MulticastGroup> mc;
+  unsigned char* mc_ptr = nullptr;
+};
+
+// What the ranks tell each other before binding a registered buffer to a multicast object.
+struct RegisterMcMsg {
+  int32_t ok;
+  int32_t pad_;
+  uint64_t inner;  // offset of the buffer inside its first granule
+  uint64_t span;   // bytes of the granules that cover it
 };
 
 // One peer allocation opened with cudaIpcOpenMemHandle.  A process may open a
@@ -154,6 +168,8 @@ class DeviceContext {
   // Peer pointers of a buffer every rank has mapped (symmetric memory or a
   // registered buffer); false when the buffer is neither.
   bool FindPeerMapped(const void* p, size_t bytes, unsigned char** peer_ptr) const;
+  void BindRegisteredToSwitch(RegisteredBuffer* reg);
+  unsigned char* FindRegisteredMulticast(const void* p, size_t bytes) const;
   template <typename M> void ExchangeWithAll(const M& mine, std::vector<M>* all);
 
   void RunCopy(DType dtype, const void* sendbuf, void* recvbuf, size_t n, double scale, cudaStream_t stream);
@@ -599,9 +615,85 @@ int DeviceContext::RegisterBuffer(void* ptr, size_t bytes) {
     (void)cudaGetLastError();
     return -1;
   }
+  BindRegisteredToSwitch(&reg);
   reg.id = next_registration_++;
   registered_.push_back(reg);
   return reg.id;
+}
+
+// Collective (part of RegisterBuffer).  Binds the granules around the buffer
+// to a multicast object so that the switch kernels can work on it in place,
+// as they do on symmetric memory.  Needs: multicast on this box, the driver's
+// bind-by-address call, the buffer at the same offset inside its first
+// granule on every rank, and the granules inside the buffer's allocation.
+// Whatever is missing, on any rank, leaves the registration as it was
+// (peer-mapped only) on every rank.
+void DeviceContext::BindRegisteredToSwitch(RegisteredBuffer* reg) {
+  if (mc_ == nullptr || Tunable("IBCOMM_REGISTER_SWITCH", 1) == 0) return;  // the same on every rank
+  const drv::Api* api = drv::Get();
+  RegisterMcMsg mine;
+  memset(&mine, 0, sizeof(mine));
+  const uintptr_t p = reinterpret_cast<uintptr_t>(reg->ptr);
+  uintptr_t lo = 0;
+  if (api != nullptr && api->MulticastBindAddr != nullptr) {
+    size_t gran = MulticastGroup::Granularity(ws_, reg->bytes);
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (gran != 0 && api->MemGetAddressRange(&base, &size, static_cast<CUdeviceptr>(p)) == CUDA_SUCCESS) {
+      lo = p / gran * gran;
+      const uintptr_t hi = (p + reg->bytes + gran - 1) / gran * gran;
+      if (lo >= base && hi <= base + size) {
+        mine.ok = 1;
+        mine.inner = p - lo;
+        mine.span = hi - lo;
+      }
+    }
+  }
+  std::vector<RegisterMcMsg> all;
+  ExchangeWithAll(mine, &all);
+  for (const RegisterMcMsg& m : all)
+    if (m.ok == 0 || m.inner != mine.inner || m.span != mine.span) return;
+  const int timeout = std::max(comm_->timeout_ms(), 30000);
+  int ok = 1;
+  std::shared_ptr<MulticastGroup> group(new MulticastGroup());
+  if (rank_ == 0) {
+    int fd = group->CreateRoot(mine.span, ws_);
+    if (fd < 0) ok = 0;
+    for (int q = 1; q < ws_; ++q) fdch_[static_cast<size_t>(q)]->Send(&ok, sizeof(ok), fd);
+    if (fd >= 0) close(fd);
+  } else {
+    int fd = fdch_[0]->Recv(&ok, sizeof(ok), timeout);
+    if (ok) group->Import(fd, mine.span, ws_);
+  }
+  if (!ok) return;
+  group->AddDevice(device_);
+  comm_->Barrier();  // every device is in the object before anybody binds
+  std::string why;
+  int32_t bound = group->BindAddrAndMap(reinterpret_cast<void*>(lo), device_, &why) ? 1 : 0;
+  std::vector<int32_t> all_bound;
+  ExchangeWithAll(bound, &all_bound);
+  bool everybody = true;
+  for (int32_t v : all_bound) everybody = everybody && v != 0;
+  if (!everybody) {
+    static bool warned = false;
+    if (!bound && !warned) {
+      warned = true;
+      IBCOMM_WARN("registered buffer stays peer-mapped only, the switch cannot be used on it in place (%s).\n", why.c_str());
+    }
+    group->Release();
+    comm_->Barrier();
+    return;
+  }
+  reg->mc = group;
+  reg->mc_ptr = group->ptr() + mine.inner;
+}
+
+// The multicast alias of [p, p + bytes) when it lies in a registered buffer that is bound to the switch.
+unsigned char* DeviceContext::FindRegisteredMulticast(const void* p, size_t bytes) const {
+  const unsigned char* c = static_cast<const unsigned char*>(p);
+  for (const RegisteredBuffer& r : registered_)
+    if (r.mc_ptr != nullptr && c >= r.ptr && c + bytes <= r.ptr + r.bytes) return r.mc_ptr + (c - r.ptr);
+  return nullptr;
 }
 
 // Collective by contract: no rank may still run a collective on the buffer.
@@ -610,8 +702,13 @@ void DeviceContext::DeregisterBuffer(int id) {
     if (registered_[i].id != id) continue;
     CUDACHECK(cudaDeviceSynchronize());
     if (ws_ > 1) comm_->Barrier();  // the peers' kernels on this buffer are done, too
-    const RegisteredBuffer reg = registered_[i];
+    RegisteredBuffer reg = registered_[i];
     registered_.erase(registered_.begin() + static_cast<long>(i));
+    if (reg.mc) {
+      reg.mc->Release();  // unmaps the alias and unbinds this rank's memory
+      reg.mc.reset();
+      if (ws_ > 1) comm_->Barrier();
+    }
     for (int q = 0; q < ws_; ++q) {
       if (q == rank_ || reg.peer_ptr[q] == nullptr) continue;
       for (size_t k = 0; k < ipc_imports_.size(); ++k) {
@@ -844,8 +941,15 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, DType wire, const voi
   // The direct variant also takes buffers the peers mapped by registration.
   unsigned char* reg_in[kMaxRanks];
   unsigned char* reg_out[kMaxRanks];
-  bool rin = !multimem && sin == nullptr && FindPeerMapped(sendbuf, bytes, reg_in);
-  bool rout = !multimem && sout == nullptr && FindPeerMapped(recvbuf, bytes, reg_out);
+  bool rin = sin == nullptr && FindPeerMapped(sendbuf, bytes, reg_in);
+  bool rout = sout == nullptr && FindPeerMapped(recvbuf, bytes, reg_out);
+  // ... and the switch variant those that registration could bind to a multicast object.
+  unsigned char* const rmc_in = multimem && rin ? FindRegisteredMulticast(sendbuf, bytes) : nullptr;
+  unsigned char* const rmc_out = multimem && rout ? FindRegisteredMulticast(recvbuf, bytes) : nullptr;
+  if (multimem) {
+    rin = rin && rmc_in != nullptr;
+    rout = rout && rmc_out != nullptr;
+  }
   // Registered buffers sit at different offsets on different ranks: all
   // ranks must come to the same decision, so every rank's pointer has to be
   // 16-byte aligned (the mappings' bases are), not only this rank's.
@@ -872,7 +976,7 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, DType wire, const voi
   p.stage_in = zin ? 0 : 1;
   p.stage_out = zout ? 0 : 1;
   if (zin && rin) {
-    p.mc_in = nullptr;
+    p.mc_in = rmc_in;
     p.local_in = reg_in[rank_];
     for (int q = 0; q < ws_; ++q) p.peer_in[q] = reg_in[q];
   } else if (zin) {
@@ -886,7 +990,7 @@ void DeviceContext::RunTwoShot(bool multimem, DType dtype, DType wire, const voi
     for (int q = 0; q < ws_; ++q) p.peer_in[q] = rr_.peers.arena[q] + layout_.pool_offset;
   }
   if (zout && rout) {
-    p.mc_out = nullptr;
+    p.mc_out = rmc_out;
     p.local_out = reg_out[rank_];
     for (int q = 0; q < ws_; ++q) p.peer_out[q] = reg_out[q];
   } else if (zout) {
@@ -964,7 +1068,10 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
   const bool nvls_ok = mc_ != nullptr && NvlsSupportsDType(wire) && (!compressed || staged_shape);
   int channels;
   if (algo == Algo::kAuto) {
-    const bool symmetric = FindSymmetric(sendbuf, bytes) != nullptr && FindSymmetric(recvbuf, bytes) != nullptr;
+    // "symmetric" for the choice: both buffers are mapped by the peers AND bound to the switch
+    // (symmetric memory, or registered buffers that registration could bind).
+    auto on_switch = [&](const void* b) { return FindSymmetric(b, bytes) != nullptr || FindRegisteredMulticast(b, bytes) != nullptr; };
+    const bool symmetric = on_switch(sendbuf) && on_switch(recvbuf);
     unsigned char* unused[kMaxRanks];
     // Registered buffers are mapped by the peers but not bound to the
     // multicast object: zero-copy for the direct algorithm only.  With a
@@ -995,7 +1102,8 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
                   static_cast<unsigned long long>(layout_.oneshot_slot_bytes), bytes);
     if (algo == Algo::kOneShot && compressed) IBCOMM_FAIL(NOT_SUPPORTED, "One-shot allreduce has no wire compression.\n");
     channels = ChooseChannels(algo, bytes, ws_, max_channels_);
-    if (algo == Algo::kNvls && !(FindSymmetric(sendbuf, bytes) != nullptr && FindSymmetric(recvbuf, bytes) != nullptr))
+    auto on_switch = [&](const void* b) { return FindSymmetric(b, bytes) != nullptr || FindRegisteredMulticast(b, bytes) != nullptr; };
+    if (algo == Algo::kNvls && !(on_switch(sendbuf) && on_switch(recvbuf)))
       channels = std::max(channels, ChooseChannels(Algo::kDirect, bytes, ws_, max_channels_));
   }
   {
@@ -1366,6 +1474,8 @@ DeviceInfo DeviceContext::Info() const {
   i.work_bytes = layout_.work_bytes;
   i.calls = calls_;
   i.kernel_launches = kernel_launches_;
+  i.switch_registrations = 0;
+  for (const RegisteredBuffer& r : registered_) i.switch_registrations += r.mc_ptr != nullptr ? 1 : 0;
   i.last_algo = last_algo_;
   i.last_channels = last_channels_;
   return i;

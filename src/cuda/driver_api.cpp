@@ -49,6 +49,7 @@ static void LoadAll() {
   mc &= Load("cuMulticastBindMem", &g_api.MulticastBindMem);
   mc &= Load("cuMulticastUnbind", &g_api.MulticastUnbind);
   mc &= Load("cuMulticastGetGranularity", &g_api.MulticastGetGranularity);
+  (void)Load("cuMulticastBindAddr", &g_api.MulticastBindAddr);
   g_multicast = ok && mc;
   g_api.loaded = ok;
 }

@@ -414,6 +414,7 @@ int ibcomm_get_device_info(ibcomm_comm* c, int connect, ibcomm_device_info* out)
     out->work_bytes = i.work_bytes;
     out->calls = i.calls;
     out->kernel_launches = i.kernel_launches;
+    out->switch_registrations = i.switch_registrations;
 #else
     (void)c; (void)connect; (void)out;
 #endif

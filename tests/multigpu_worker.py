@@ -159,6 +159,55 @@ def case_registered(comm):
     return rc
 
 
+def case_registered_switch(comm):
+    """Ordinary torch tensors that registration binds to the NVSwitch multicast: the switch kernel reduces and
+    broadcasts them in place.  Large tensors get allocations of their own, so they start on a granule on every
+    rank; where the box or the driver cannot bind them the registration stays peer-mapped and the case only
+    checks the results."""
+    info = comm.device_info(connect=True)
+    rc = 0
+    n = 12 << 20  # 48 MiB: an allocation of its own in the caching allocator
+    x = torch.empty(n, device="cuda")
+    y = torch.empty(n, device="cuda")
+    rx, ry = comm.register(x), comm.register(y)
+    if rx < 0 or ry < 0:
+        print(f"rank {RANK}: registration not available", file=sys.stderr)
+        return 1
+    bound = comm.device_info()["switch_registrations"]
+    if RANK == 0:
+        print(f"switch registrations: {bound} (nvls {info['nvls']})")
+    if info["nvls"] and bound not in (0, 2):
+        print(f"rank {RANK}: {bound} of 2 registrations bound to the switch", file=sys.stderr)
+        rc = 1
+    algos = ["auto", "direct"] + (["nvls"] if info["nvls"] else [])
+    for it, algo in enumerate(algos):
+        x.copy_(seeded(n, torch.float32, RANK, seed=it))
+        comm.allreduce(x, y, algo=algo, scale=1.0 / WS, sync=True)
+        used = comm.device_info()["last_algo"]
+        if algo == "auto" and bound == 2 and WS > 2 and used != "nvls":
+            print(f"rank {RANK}: switch-bound registered buffers ran {used}", file=sys.stderr)
+            rc = 1
+        if not close(y, expected(n, torch.float32, 1.0 / WS, seed=it), torch.float32):
+            print(f"rank {RANK}: registered ({algo}) mismatch", file=sys.stderr)
+            rc = 1
+        # in place on an aligned slice, and a sub-range of both buffers
+        comm.allreduce(x[1 << 20:], algo=algo, sync=True)
+        if not close(x[1 << 20:], expected(n, torch.float32, 1.0, seed=it)[1 << 20:], torch.float32):
+            print(f"rank {RANK}: registered in-place slice ({algo}) mismatch", file=sys.stderr)
+            rc = 1
+    comm.deregister(rx)
+    comm.deregister(ry)
+    if comm.device_info()["switch_registrations"] != 0:
+        print(f"rank {RANK}: registrations left bound after deregister", file=sys.stderr)
+        rc = 1
+    x.copy_(seeded(n, torch.float32, RANK, seed=9))
+    comm.allreduce(x, y, sync=True)
+    if not close(y, expected(n, torch.float32, 1.0, seed=9), torch.float32):
+        print(f"rank {RANK}: after deregistration mismatch", file=sys.stderr)
+        rc = 1
+    return rc
+
+
 def case_rsag(comm):
     """Reduce-scatter and all-gather: ordinary, registered and symmetric buffers; every algorithm the box has."""
     rc = 0

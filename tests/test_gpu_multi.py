@@ -73,6 +73,15 @@ def test_registered_user_buffers(bins):
 
 
 @needs2
+@pytest.mark.parametrize("np_", sorted({min(NGPU, 2), min(NGPU, 8)}))
+def test_registered_buffers_bound_to_the_switch(bins, np_):
+    # Registration binds ordinary tensors to the NVSwitch multicast where the driver allows it; the switch
+    # kernel then works on them in place.  Results are checked either way.
+    code, err = run(bins, np_, "registered_switch")
+    assert code == 0, err
+
+
+@needs2
 def test_staged_buffers_over_several_windows(bins):
     code, err = run(bins, min(NGPU, 4), "staged")
     assert code == 0, err
