@@ -185,7 +185,7 @@ class DeviceContext {
   // Caps a collective's CTAs at what the GPU holds at once (CTA b of this rank
   // waits for CTA b of the peers) and at IBCOMM_MAX_CTAS when set (a program
   // that overlaps collectives with compute leaves SMs to the compute).
-  int ClampChannels(Algo algo, int channels);
+  int ClampChannels(Algo algo, int channels, size_t bytes = 0);
   // Begins a device trace record of `records` entries per channel (no-op when tracing is off).
   DeviceTraceRec* BeginDeviceTrace(int channels, int records, int* capacity);
   void ExchangeAllocation(SharedAllocation* mine, std::vector<std::unique_ptr<SharedAllocation>>* imported,
@@ -756,14 +756,16 @@ void DeviceContext::RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, 
   IBCOMM_TRACE(*tracer_, kTraceIssueReduKernel);
 }
 
-int DeviceContext::ClampChannels(Algo algo, int channels) {
+int DeviceContext::ClampChannels(Algo algo, int channels, size_t bytes) {
   int limit;
-  if (algo == Algo::kRing && Tunable("IBCOMM_EXEC_CHANNELS", 0) <= 0) {
+  if ((algo == Algo::kRing || (algo == Algo::kRabenseifner && bytes < (256u << 20))) && Tunable("IBCOMM_EXEC_CHANNELS", 0) <= 0) {
     // One 512-thread block per SM at most.  Beyond that the executor runs two
-    // 256-thread blocks per SM, whose three data warps per op make a ring step
-    // twice as slow at medium sizes (64 MiB: 53-65 us per step on 3-6 ranks
-    // with 170-256 channels against 28-29 us on 7-8 ranks with 128-146), for
-    // 3 % at 256 MiB on 8 GPUs and a gain on 2.
+    // 256-thread blocks per SM, whose three data warps per op make a step
+    // slower at medium sizes (two ranks, 16 and 64 MiB: 256 channels take 113-175
+    // us where 64-148 take 72-82 and 134-150 us, ring and Rabenseifner alike;
+    // 64 MiB ring on 3-6 ranks: 53-65 us per step with 170-256 channels against
+    // 28-29 us on 7-8 ranks with 128-146).  Rabenseifner keeps 256 channels
+    // from 256 MiB on, where they measured 11 % ahead on 8 GPUs.
     static const int sms = [this] {
       int n = 0;
       return cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device_) == cudaSuccess ? n : 0;
@@ -1114,7 +1116,7 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
     const int forced = knob != nullptr ? Tunable(knob, 0) : 0;
     if (forced > 0) channels = std::min(forced, kMaxChannels);
   }
-  channels = ClampChannels(algo, channels);
+  channels = ClampChannels(algo, channels, bytes);
   OrderAfterPrevious(stream);
   switch (algo) {
     case Algo::kRing:
