@@ -74,7 +74,7 @@ def parse_args():
                     help="time ring, Rabenseifner, auto and NCCL at 64 MiB on every world size 2..N (sub-communicators of this launch)")
     ap.add_argument("--kernel-case", default=None,
                     choices=["copy", "exec_ring_emu8", "exec_rabenseifner_emu8", "oneshot_emu8", "direct_emu8",
-                             "staged_emu8", "reduce_scatter_emu8", "all_gather_emu8"],
+                             "staged_emu8", "reduce_scatter_emu8", "all_gather_emu8", "noalloc_emu8"],
                     help="run one small single-GPU case of one kernel (for ncu captures) and print its time")
     return ap.parse_args()
 
@@ -760,6 +760,27 @@ def kernel_case(args, comm, dev, time_steps) -> int:
         y = torch.empty_like(x)
         ms = time_steps(lambda: comm.allreduce(x, y, scale=0.5), args.steps, args.warmup)
         moved = 2 * n * 4
+    elif case == "noalloc_emu8":
+        # The allocation-free entry point (include/ibcomm/no_alloc.h): 8 emulated ranks x 32 KiB, its limit.
+        import ctypes as C
+
+        from allreduce_proto_b200 import _native
+        fn = _native.lib().ibcomm_emu_oneshot_allreduce_f32_noalloc
+        fn.restype = C.c_int
+        fn.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.c_size_t, C.c_float, C.c_void_p, C.c_char_p, C.c_size_t]
+        ins = [torch.rand(8192, device=dev) for _ in range(8)]
+        outs = [torch.empty(8192, device=dev) for _ in range(8)]
+        pin = (C.c_void_p * 8)(*[t.data_ptr() for t in ins])
+        pout = (C.c_void_p * 8)(*[t.data_ptr() for t in outs])
+        err = C.create_string_buffer(256)
+
+        def step():
+            if fn(pin, pout, 8, 8192, 0.125, C.c_void_p(torch.cuda.current_stream().cuda_stream), err, len(err)) != 0:
+                raise RuntimeError(err.value.decode())
+        ms = time_steps(step, args.steps, args.warmup)
+        want = torch.stack(ins).sum(0) * 0.125
+        assert torch.allclose(outs[3], want, rtol=1e-5, atol=1e-6)
+        moved = None
     elif case in ("reduce_scatter_emu8", "all_gather_emu8"):
         emu = ar.EmuWorld(8)
         m = 1 << 20  # elements per block: 32 MiB per rank in the full buffers
