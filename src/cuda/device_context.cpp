@@ -186,6 +186,7 @@ class DeviceContext {
   // waits for CTA b of the peers) and at IBCOMM_MAX_CTAS when set (a program
   // that overlaps collectives with compute leaves SMs to the compute).
   int ClampChannels(Algo algo, int channels, size_t bytes = 0);
+  int sm_count_ = -1;  // looked up on first use
   // Begins a device trace record of `records` entries per channel (no-op when tracing is off).
   DeviceTraceRec* BeginDeviceTrace(int channels, int records, int* capacity);
   void ExchangeAllocation(SharedAllocation* mine, std::vector<std::unique_ptr<SharedAllocation>>* imported,
@@ -766,11 +767,8 @@ int DeviceContext::ClampChannels(Algo algo, int channels, size_t bytes) {
     // 64 MiB ring on 3-6 ranks: 53-65 us per step with 170-256 channels against
     // 28-29 us on 7-8 ranks with 128-146).  Rabenseifner keeps 256 channels
     // from 256 MiB on, where they measured 11 % ahead on 8 GPUs.
-    static const int sms = [this] {
-      int n = 0;
-      return cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device_) == cudaSuccess ? n : 0;
-    }();
-    if (sms > 0) channels = std::min(channels, sms);
+    if (sm_count_ < 0 && cudaDeviceGetAttribute(&sm_count_, cudaDevAttrMultiProcessorCount, device_) != cudaSuccess) sm_count_ = 0;
+    if (sm_count_ > 0) channels = std::min(channels, sm_count_);
   }
   if (algo == Algo::kRing || algo == Algo::kRabenseifner) {
     const int threads = ExecKernelThreadsFor(channels);
