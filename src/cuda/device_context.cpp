@@ -759,14 +759,17 @@ void DeviceContext::RunOneShot(DType dtype, const void* sendbuf, void* recvbuf, 
 
 int DeviceContext::ClampChannels(Algo algo, int channels, size_t bytes) {
   int limit;
-  if ((algo == Algo::kRing || (algo == Algo::kRabenseifner && bytes < (256u << 20))) && Tunable("IBCOMM_EXEC_CHANNELS", 0) <= 0) {
+  if ((algo == Algo::kRing || algo == Algo::kRabenseifner) && (bytes < (256u << 20) || (algo == Algo::kRing && ws_ <= 2)) &&
+      Tunable("IBCOMM_EXEC_CHANNELS", 0) <= 0) {
     // One 512-thread block per SM at most.  Beyond that the executor runs two
     // 256-thread blocks per SM, whose three data warps per op make a step
     // slower at medium sizes (two ranks, 16 and 64 MiB: 256 channels take 113-175
     // us where 64-148 take 72-82 and 134-150 us, ring and Rabenseifner alike;
     // 64 MiB ring on 3-6 ranks: 53-65 us per step with 170-256 channels against
-    // 28-29 us on 7-8 ranks with 128-146).  Rabenseifner keeps 256 channels
-    // from 256 MiB on, where they measured 11 % ahead on 8 GPUs.
+    // 28-29 us on 7-8 ranks with 128-146).  From 256 MiB on both programs keep
+    // 256 channels on more than two ranks (Rabenseifner 11 % ahead on 8 GPUs,
+    // the ring 4 % on 8 and 8 % on 4); on two ranks the ring stays capped
+    // (441 against 464 us).
     if (sm_count_ < 0 && cudaDeviceGetAttribute(&sm_count_, cudaDevAttrMultiProcessorCount, device_) != cudaSuccess) sm_count_ = 0;
     if (sm_count_ > 0) channels = std::min(channels, sm_count_);
   }
@@ -851,7 +854,9 @@ bool DeviceContext::RunStaged(bool multimem, DType dtype, DType wire, const void
   const int cap = Tunable("IBCOMM_MAX_CTAS", 0);
   const bool split = Tunable("IBCOMM_STAGED_SPLIT", 1) != 0 && resident >= 4 && (cap <= 0 || cap >= 2);
   // Windows of 16-27 MiB measured best on 2 and 8 B200: three of each kind in the arena's 96 MiB, six in the grown block.
-  if (buffers <= 0) buffers = use_grown ? (split ? 6 : 4) : 3;
+  // In the grown block: the switch path wants the largest windows (4 GPUs, 256 MiB: 688 us with three of 53 MiB
+  // against 725 with six of 27 MiB), the peer-load path the smaller ones (2 GPUs: 465 against 509 us).
+  if (buffers <= 0) buffers = use_grown ? (multimem ? 3 : (split ? 6 : 4)) : 3;
   buffers = std::max(3, std::min(buffers, kStagedMaxBuffers));
   const uint64_t quarter = stage_bytes / static_cast<uint64_t>(2 * buffers) / 4096 * 4096;
   if (quarter < 4096) return false;
@@ -1082,7 +1087,8 @@ void DeviceContext::Allreduce(DType dtype, const void* sendbuf, void* recvbuf, s
     // message per direction, pipelined copies) beats peer loads on registered
     // buffers in place (2 (ws-1)/ws of it): 1303 against 1444 us at 512 MiB on
     // 8 GPUs.  Such buffers are then treated as ordinary ones.
-    if (mapped && !symmetric && nvls_ok && staged_shape && ws_ > 2 &&
+    // Only from seven ranks on: with four, peer loads in place move 1.5 S per direction and win (615 against 731 us).
+    if (mapped && !symmetric && nvls_ok && staged_shape && ws_ >= 7 &&
         bytes >= (static_cast<size_t>(Tunable("IBCOMM_REGISTERED_SWITCH_MIB", 256)) << 20))
       mapped = false;
     TunerChoice c = ChooseAlgorithm(bytes, ws_, nvls_ok && (symmetric || !mapped), mapped, max_channels_);
