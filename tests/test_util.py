@@ -106,6 +106,11 @@ def test_python_api_argument_checks():
         comm.allreduce(x, torch.empty(11))
     with pytest.raises(ValueError):
         comm.register(x)                          # registration is for CUDA tensors
+    assert comm.staged_timeline() == {"windows": 0, "reduce": [], "load": [], "store": []}   # nothing traced
+    ar.utils.set_tunable("IBCOMM_STAGED_BUFFERS", 5)
+    assert ar.utils.get_tunable("IBCOMM_STAGED_BUFFERS", 3) == 5
+    ar.utils.set_tunable("IBCOMM_STAGED_BUFFERS", -1)
+    assert ar.utils.get_tunable("IBCOMM_STAGED_BUFFERS", 3) == 3
     comm.close()
 
 
