@@ -137,6 +137,8 @@ bool RunAllreduce(int ws, int ncta, uint64_t n, uint64_t cap_elems) {
 // waits in_ready >= k+1 and out_free >= k-bufs+1, storer k waits reduced >= k+1.
 struct PipeWorld {
   int ws, ncta, bufs;
+  bool posters = false;  // a poster thread behind every reducer group publishes its windows
+  std::vector<std::atomic<uint32_t>> stored;  // [rank][cta][reducer group]: windows the group has handed to its poster
   int groups[3];  // per kind of row: 0 in_ready (loader groups), 1 reduced (reducer groups), 2 out_free (storer groups)
   std::vector<std::vector<std::vector<int64_t>>> in, out;  // [buffer][rank][element]
   std::vector<std::atomic<uint64_t>> row[3];               // [group][rank][cta][source rank]
@@ -147,7 +149,10 @@ struct PipeWorld {
       row[k] = std::vector<std::atomic<uint64_t>>(static_cast<size_t>(groups[k]) * ws_ * ncta_ * ws_);
       for (auto& f : row[k]) f.store(0);
     }
+    stored = std::vector<std::atomic<uint32_t>>(static_cast<size_t>(ws_) * ncta_ * rg);
+    for (auto& c : stored) c.store(0);
   }
+  std::atomic<uint32_t>& Stored(int rank, int cta, int group) { return stored[(static_cast<size_t>(rank) * ncta + cta) * groups[1] + group]; }
   // Window k's words of one kind live in the rows of group k % groups: the
   // groups of a role finish their windows in any order, a row's values only grow.
   std::atomic<uint64_t>& Flag(int kind, uint64_t window, int rank, int cta, int src) {
@@ -163,14 +168,28 @@ struct PipeWorld {
   }
 };
 
-// role: 0 loader, 1 reducer, 2 storer; `group` of the role's `w->groups[role]` groups takes windows
+// role: 0 loader, 1 reducer, 2 storer, 3 poster of a reducer group; `group` of the role's groups takes windows
 // group, group + groups, ...  (StagedKernel: the groups are warps of a block, or of two blocks in split mode).
 void PipeRole(PipeWorld* w, int role, int group, uint64_t seq, int rank, int cta, const std::vector<int64_t>& send,
               std::vector<int64_t>* recv, uint64_t total_nv, uint64_t full_nv) {
   const int ws = w->ws, ncta = w->ncta;
   const uint64_t base = seq << 32, bufs = static_cast<uint64_t>(w->bufs);
   const uint64_t windows = (total_nv + full_nv - 1) / full_nv;
-  for (uint64_t k = static_cast<uint64_t>(group); k < windows; k += static_cast<uint64_t>(w->groups[role])) {
+  const int role_groups = w->groups[role == 3 ? 1 : role];
+  if (role == 3) {
+    // The poster: waits until its group has issued the stores of window k (a counter in the block's shared
+    // memory, release / acquire), then publishes the window.  The calls of one rank follow each other in
+    // one thread per role, so the counter restarts with every call.
+    uint32_t seen = 0;
+    for (uint64_t k = static_cast<uint64_t>(group); k < windows; k += static_cast<uint64_t>(role_groups)) {
+      ++seen;
+      while (w->Stored(rank, cta, group).load(std::memory_order_acquire) < seen) std::this_thread::yield();
+      w->PostAll(1, k, rank, cta, base | (k + 1));
+    }
+    return;
+  }
+  uint32_t handed = 0;
+  for (uint64_t k = static_cast<uint64_t>(group); k < windows; k += static_cast<uint64_t>(role_groups)) {
     const int j = static_cast<int>(k % bufs);
     const uint64_t v0 = k * full_nv, nv = std::min(full_nv, total_nv - v0);
     if (role == 0) {
@@ -191,7 +210,8 @@ void PipeRole(PipeWorld* w, int role, int group, uint64_t seq, int rank, int cta
         for (int q = 0; q < ws; ++q) acc += w->in[j][q][i];
         for (int q = 0; q < ws; ++q) w->out[j][q][i] = acc;
       }
-      w->PostAll(1, k, rank, cta, base | (k + 1));
+      if (w->posters) w->Stored(rank, cta, group).store(++handed, std::memory_order_release);
+      else w->PostAll(1, k, rank, cta, base | (k + 1));
     } else {
       w->WaitAll(1, k, rank, cta, base | (k + 1));
       for (int s = 0; s < ws; ++s) {
@@ -204,12 +224,13 @@ void PipeRole(PipeWorld* w, int role, int group, uint64_t seq, int rank, int cta
   }
 }
 
-bool RunPipelined(int ws, int ncta, uint64_t n_vec, uint64_t cap_elems, int bufs = 3, int lg = 1, int rg = 2, int sg = 1) {
+bool RunPipelined(int ws, int ncta, uint64_t n_vec, uint64_t cap_elems, int bufs = 3, int lg = 1, int rg = 2, int sg = 1, bool posters = false) {
   const uint64_t n = n_vec * kVec;
   const uint64_t window = TwoShotWindowElems(n, cap_elems, 16 / kVec, ws, ncta);
   const uint64_t full_nv = window / kVec;
   if (full_nv == 0) return true;
   PipeWorld w(ws, ncta, window, bufs, lg, rg, sg);
+  w.posters = posters;
   std::vector<std::vector<int64_t>> send(ws, std::vector<int64_t>(n)), recv(ws, std::vector<int64_t>(n, -1));
   for (int r = 0; r < ws; ++r)
     for (uint64_t i = 0; i < n; ++i) send[r][i] = Value(r, i);
@@ -218,10 +239,12 @@ bool RunPipelined(int ws, int ncta, uint64_t n_vec, uint64_t cap_elems, int bufs
     // Three calls back to back; the ranks are not synchronised in between.
     for (uint64_t seq = 1; seq <= 3; ++seq) {
       std::fill(recv[r].begin(), recv[r].end(), -1);
+      for (int c = 0; c < ncta; ++c)
+        for (int g = 0; g < rg; ++g) w.Stored(r, c, g).store(0);
       std::vector<std::thread> t;
       for (int c = 0; c < ncta; ++c)
-        for (int role = 0; role < 3; ++role)
-          for (int g = 0; g < w.groups[role]; ++g)
+        for (int role = 0; role < (posters ? 4 : 3); ++role)
+          for (int g = 0; g < w.groups[role == 3 ? 1 : role]; ++g)
             t.emplace_back(PipeRole, &w, role, g, seq, r, c, std::cref(send[r]), &recv[r], n_vec, full_nv);
       for (auto& x : t) x.join();
       for (uint64_t i = 0; i < n; ++i)
@@ -559,7 +582,7 @@ MINI_TEST(PipelinedStagedProtocol) {
       for (int lg : {1, 3, 4})
         for (int rg : {1, 2, 3})
           for (uint64_t nvec : {uint64_t(9), uint64_t(200), uint64_t(1100)})
-            CHECK_TRUE(RunPipelined(ws, 2, nvec, 256, bufs, lg, rg, lg == 4 ? 2 : 3));
+            CHECK_TRUE(RunPipelined(ws, 2, nvec, 256, bufs, lg, rg, lg == 4 ? 2 : 3, (bufs + lg + rg) % 2 == 0));
 }
 
 MINI_TEST(HybridSplitProtocol) {
