@@ -187,6 +187,7 @@ class DeviceContext {
   // that overlaps collectives with compute leaves SMs to the compute).
   int ClampChannels(Algo algo, int channels, size_t bytes = 0);
   int sm_count_ = -1;  // looked up on first use
+  bool switch_bind_refused_ = false;  // some rank's driver refused to bind a registered buffer to the switch
   // Begins a device trace record of `records` entries per channel (no-op when tracing is off).
   DeviceTraceRec* BeginDeviceTrace(int channels, int records, int* capacity);
   void ExchangeAllocation(SharedAllocation* mine, std::vector<std::unique_ptr<SharedAllocation>>* imported,
@@ -630,7 +631,9 @@ int DeviceContext::RegisterBuffer(void* ptr, size_t bytes) {
 // Whatever is missing, on any rank, leaves the registration as it was
 // (peer-mapped only) on every rank.
 void DeviceContext::BindRegisteredToSwitch(RegisteredBuffer* reg) {
-  if (mc_ == nullptr || Tunable("IBCOMM_REGISTER_SWITCH", 1) == 0) return;  // the same on every rank
+  // (all three conditions are the same on every rank; a refusal by the driver is remembered, because it is a
+  // property of the driver and the allocator, not of the buffer)
+  if (mc_ == nullptr || switch_bind_refused_ || Tunable("IBCOMM_REGISTER_SWITCH", 1) == 0) return;
   const drv::Api* api = drv::Get();
   RegisterMcMsg mine;
   memset(&mine, 0, sizeof(mine));
@@ -683,6 +686,7 @@ void DeviceContext::BindRegisteredToSwitch(RegisteredBuffer* reg) {
     }
     group->Release();
     comm_->Barrier();
+    switch_bind_refused_ = true;
     return;
   }
   reg->mc = group;
